@@ -1,0 +1,137 @@
+/* gmlp.h — C ABI of libgmlp.so, the sm_100a (B200) gated-MLP kernel library.
+ *
+ * The library replaces the device side of matteobonotto/triton-gated-mlp's fused
+ * gated MLP. Each entry point names the reference interface it stands in for
+ * (paths are relative to the reference project's root).
+ *
+ * Conventions
+ *   - M = tokens (rows of x), K = hidden size, N = intermediate size, the letters
+ *     the reference uses (README.md:32-34). nn.Linear storage: W_gate, W_up are
+ *     [N, K]; W_down is [K, N]; every matrix is row-major with the row pitch
+ *     given in elements (a multiple of 8) and a 16-byte aligned base address.
+ *   - All pointers are DEVICE pointers owned by the caller. Nothing is allocated
+ *     or freed by the library and nothing is retained after a call returns.
+ *   - `stream` is a cudaStream_t passed as void*. Work is enqueued on it and the
+ *     call returns without synchronising. The caller makes the right device
+ *     current before calling.
+ *   - Return value: 0 on success, a negative gmlp_status_t otherwise; the text of
+ *     the last error of the calling thread is available from gmlp_last_error().
+ *     The library never throws, aborts or falls back to a CPU path.
+ *   - Device-side waits are bounded. A kernel that gives up a wait stores a
+ *     non-zero code in a per-device status word that gmlp_status_read() returns.
+ */
+#ifndef GMLP_H
+#define GMLP_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum gmlp_status_t {
+  GMLP_OK = 0,
+  GMLP_ERR_SHAPE = -1,    /* a dimension is <= 0, or K/N not a multiple of 8 */
+  GMLP_ERR_ALIGN = -2,    /* base address not 16-byte aligned or pitch not a multiple of 8 */
+  GMLP_ERR_DTYPE = -3,    /* dtype is not GMLP_BF16 / GMLP_FP16 */
+  GMLP_ERR_ARCH = -4,     /* current device is not compute capability 10.x */
+  GMLP_ERR_LAUNCH = -5,   /* CUDA reported an error while encoding descriptors or launching */
+  GMLP_ERR_ARG = -6,      /* NULL where a pointer is required, bad dropout_p, ... */
+  GMLP_ERR_SCRATCH = -7   /* scratch buffer too small */
+} gmlp_status_t;
+
+typedef enum gmlp_dtype_t { GMLP_BF16 = 0, GMLP_FP16 = 1 } gmlp_dtype_t;
+
+/* One gated-MLP problem (or one rank's shard of it).
+ * Dropout uses the Philox4x32-10 contract of oracle/philox.py: the keep bit of
+ * hidden element (row, col) depends only on (seed, offset) and on its GLOBAL
+ * index (row0_global + row) * N_global + (col0_global + col), so token-sharded
+ * and intermediate-sharded ranks reproduce the single-GPU mask. */
+typedef struct gmlp_problem_t {
+  int64_t M;            /* local token rows */
+  int64_t K;            /* hidden size */
+  int64_t N;            /* local intermediate columns */
+  int32_t dtype;        /* gmlp_dtype_t of every matrix and bias vector */
+  float dropout_p;      /* 0 disables dropout; must be in [0, 1) */
+  uint64_t seed;        /* Philox key */
+  uint64_t offset;      /* Philox counter words 2..3; advance once per module call */
+  int64_t row0_global;  /* global index of local row 0 (token sharding) */
+  int64_t col0_global;  /* global index of local intermediate column 0 (TP sharding) */
+  int64_t N_global;     /* un-sharded intermediate size; 0 means N */
+} gmlp_problem_t;
+
+/* H[M,N] = dropout(silu(x W_gate^T + b_gate) * (x W_up^T + b_up)).
+ * Replaces mlp_hidden_states_fwd (src/triton_gated_mlp/ops/fwd.py:198-279, kernel
+ * :65-166) with the bias and dropout that EagerGatedMLP applies
+ * (src/triton_gated_mlp/gated_mlp.py:96). b_gate / b_up may be NULL.
+ * g_save / u_save: both NULL, or both [M,N] buffers that receive the biased
+ * pre-activations for the backward pass. */
+int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, void* h,
+                    void* g_save, void* u_save, void* stream);
+
+/* y[M,K] = h W_down^T (+ b_down) (+ residual[M,K]).
+ * Replaces self.down_proj(hidden_states) (src/triton_gated_mlp/gated_mlp.py:236). */
+int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
+                  const void* b_down, const void* residual, void* y, void* stream);
+
+/* dH = dy W_down, then d_gate = dH' * u * silu'(g), d_up = dH' * silu(g) with
+ * dH' = dH * mask / (1-p), in one kernel. Replaces the dH half of down_proj's
+ * autograd (implicit at src/triton_gated_mlp/gated_mlp.py:236) fused with
+ * _compute_quantities_for_bwd (src/triton_gated_mlp/ops/bwd.py:82-211), reading
+ * the saved pre-activations instead of recomputing them. */
+int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down,
+                     const void* g, const void* u, void* d_gate, void* d_up, void* stream);
+
+/* The elementwise half of the above for a caller that already holds dH[M,N]
+ * (the op-level contract of mlp_hidden_states_bwd, ops/bwd.py:466-602). */
+int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const void* u,
+                  void* d_gate, void* d_up, void* stream);
+
+/* dx[M,K] = d_gate W_gate + d_up W_up. Replaces _compute_dx (ops/bwd.py:231-322). */
+int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                const void* w_gate, const void* w_up, void* dx, void* stream);
+
+/* dW_gate[N,K] = d_gate^T x, dW_up[N,K] = d_up^T x (full reduction over all M
+ * rows). Replaces _compute_dW_up_dW_gp (ops/bwd.py:379-463). */
+int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                        const void* x, void* dw_gate, void* dw_up, void* stream);
+
+/* dW_down[K,N] = dy^T h. Replaces the weight-gradient half of down_proj's
+ * autograd (implicit at src/triton_gated_mlp/gated_mlp.py:236). */
+int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                     void* stream);
+
+/* dst[cols] = sum over rows of src[rows, cols] (fp32 accumulation): the bias
+ * gradients db_gate, db_up (from d_gate, d_up) and db_down (from dy), which the
+ * reference leaves to autograd of nn.Linear / returns as None
+ * (src/triton_gated_mlp/gated_mlp.py:200). `scratch` holds
+ * gmlp_colsum_scratch_bytes(rows, cols) bytes of fp32 partial sums. */
+size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols);
+int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                void* scratch, size_t scratch_bytes, void* dst, void* stream);
+
+/* mask[M,N] (one byte per element, 1 = kept) for the problem's dropout settings:
+ * the device side of the bit-exact mask check. */
+int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream);
+
+/* C[M,N] = A B^T (+ bias[N]) with fp32 accumulation: the GEMM engine under every
+ * call above, exported for its own parity tests. a_mn = 0: A stored [M,K]
+ * (K-major); a_mn = 1: A stored [K,M]. b_mn = 0: B stored [N,K]; b_mn = 1: B
+ * stored [K,N]. lda / ldb / ldc are row pitches in elements. */
+int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,
+              const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+              const void* bias, void* stream);
+
+/* Reads and clears the current device's status word (synchronises the device).
+ * 0 = no kernel gave up a wait since the last read. */
+int gmlp_status_read(int* value);
+
+const char* gmlp_last_error(void);
+int gmlp_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GMLP_H */

@@ -1,0 +1,210 @@
+"""CPU restatement (torch fp32 on the host) of the reference's eager gated MLP.
+TEST INFRASTRUCTURE ONLY: imported by tests/, __graft_entry__.smoke() and
+bench.py's CPU baseline legs, never by the shipped package.
+
+What it restates (paths relative to the reference project):
+  forward    EagerGatedMLP.forward, src/triton_gated_mlp/gated_mlp.py:92-98:
+             y = down(dropout(silu(gate(x)) * up(x))), bias on all three linears.
+  backward   the closed form of eager_bwd (gated_mlp.py:131-156; the same block is
+             the known-answer recipe of tests/test_gated_mlp_bwd.py:108-123),
+             extended by the down projection's and the biases' gradients, which
+             the reference leaves to torch autograd.
+  silu'      _silu_op_bwd, gated_mlp.py:40-43.
+Dropout uses the counter-based mask of oracle/philox.py instead of nn.Dropout's
+generator (see that file for why).
+
+Pinned by tests/test_oracle_golden.py against outputs of the reference's own
+EagerGatedMLP / eager_fwd / eager_bwd, generated in the build container by
+tests/golden/make_golden.py (the reference publishes no golden vectors).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from . import philox
+
+# Tolerances of the parity contract for 16-bit kernels against this fp32 oracle.
+MAX_ABS_TOL = 2e-2
+MEAN_REL_TOL = 1e-2
+
+
+# ------------------------------------------------------------------ math ----
+def silu(b: Tensor) -> Tensor:
+    return b * torch.sigmoid(b)
+
+
+def silu_prime(b: Tensor) -> Tensor:
+    """sigma * (1 + b * (1 - sigma)), gated_mlp.py:41-42."""
+    sigma = 1 / (1 + torch.exp(-b))
+    return sigma * (1 + b * (1 - sigma))
+
+
+def hidden_forward(x, w_gate, b_gate, w_up, b_up, keep_scale: Optional[Tensor] = None):
+    """(H, G, U): hidden state after dropout and the biased pre-activations."""
+    g = x @ w_gate.T
+    if b_gate is not None:
+        g = g + b_gate
+    u = x @ w_up.T
+    if b_up is not None:
+        u = u + b_up
+    h = silu(g) * u
+    if keep_scale is not None:
+        h = h * keep_scale
+    return h, g, u
+
+
+def forward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, keep_scale: Optional[Tensor] = None) -> Tensor:
+    shapes = x.shape
+    x2 = x.reshape(-1, shapes[-1])
+    h, _, _ = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale)
+    y = h @ w_down.T
+    if b_down is not None:
+        y = y + b_down
+    return y.reshape(shapes[:-1] + (w_down.shape[0],))
+
+
+def hidden_backward(x, w_gate, w_up, g, u, dh):
+    """(dx, dW_up, dW_gate, d_gate, d_up) from dH; eager_bwd's closed form, gated_mlp.py:143-154."""
+    c = silu(g)
+    d_gate = (dh * u) * silu_prime(g)   # grad_output_a_act_prime
+    d_up = dh * c                       # grad_output_c
+    dx = d_up @ w_up + d_gate @ w_gate
+    return dx, d_up.T @ x, d_gate.T @ x, d_gate, d_up
+
+
+def backward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, dy, keep_scale: Optional[Tensor] = None
+             ) -> Dict[str, Tensor]:
+    """All gradients of forward() for upstream gradient dy. Keys follow nn.Module parameter names."""
+    x2 = x.reshape(-1, x.shape[-1])
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    h, g, u = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale)
+    dh = dy2 @ w_down
+    if keep_scale is not None:
+        dh = dh * keep_scale
+    dx, dw_up, dw_gate, d_gate, d_up = hidden_backward(x2, w_gate, w_up, g, u, dh)
+    out = {
+        "dx": dx.reshape(x.shape),
+        "dgate_proj.weight": dw_gate,
+        "dup_proj.weight": dw_up,
+        "ddown_proj.weight": dy2.T @ h,
+    }
+    if b_gate is not None:
+        out["dgate_proj.bias"] = d_gate.sum(0)
+    if b_up is not None:
+        out["dup_proj.bias"] = d_up.sum(0)
+    if b_down is not None:
+        out["ddown_proj.bias"] = dy2.sum(0)
+    return out
+
+
+def keep_scale_tensor(rows: int, cols: int, p: float, seed: int, offset: int, *, row0: int = 0,
+                      col0: int = 0, n_global: Optional[int] = None) -> Optional[Tensor]:
+    """mask * 1/(1-p) as fp32, or None when p == 0."""
+    if p <= 0.0:
+        return None
+    keep = philox.keep_mask(rows, cols, p, seed, offset, row0=row0, col0=col0, n_global=n_global)
+    return torch.from_numpy(keep.astype(np.float32) * philox.scale(p))
+
+
+# ----------------------------------------------------------------- cases ----
+@dataclass
+class Case:
+    """Seeded inputs of one configuration, already rounded to the engine's dtype.
+
+    The tensors are stored in the low-precision dtype; the oracle up-casts them to
+    fp32, so a comparison measures kernel error, not input quantisation.
+    """
+
+    x: Tensor
+    w_gate: Tensor
+    b_gate: Optional[Tensor]
+    w_up: Tensor
+    b_up: Optional[Tensor]
+    w_down: Tensor
+    b_down: Optional[Tensor]
+    dy: Tensor
+
+    def state_dict(self) -> Dict[str, Tensor]:
+        sd = {"gate_proj.weight": self.w_gate, "up_proj.weight": self.w_up, "down_proj.weight": self.w_down}
+        if self.b_gate is not None:
+            sd.update({"gate_proj.bias": self.b_gate, "up_proj.bias": self.b_up, "down_proj.bias": self.b_down})
+        return {k: v.float() for k, v in sd.items()}
+
+    def f32(self):
+        f = lambda t: None if t is None else t.float()
+        return (f(self.x), f(self.w_gate), f(self.b_gate), f(self.w_up), f(self.b_up), f(self.w_down),
+                f(self.b_down), f(self.dy))
+
+
+def _gen(seed: int) -> torch.Generator:
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    return g
+
+
+def make_case(M: int, K: int, N: int, bias: bool, dtype: torch.dtype, seed: int = 0, x_dist: str = "normal",
+              w_std: Optional[float] = 0.02, dy_std: float = 1.0, b_std: float = 0.02,
+              lead_shape: Optional[tuple] = None) -> Case:
+    """Synthetic inputs with the value distributions the benchmark configurations name.
+
+    One generator per tensor, seeded seed + tensor index, drawn in fp32 on the CPU and
+    then rounded to `dtype`. w_std=None draws nn.Linear's default init
+    (uniform(-1/sqrt(fan_in), 1/sqrt(fan_in))).
+    """
+    def normal(shape, std, idx):
+        return (torch.randn(shape, generator=_gen(seed + idx)) * std).to(dtype)
+
+    def linear_default(shape, idx):
+        bound = 1.0 / (shape[1] ** 0.5)
+        return ((torch.rand(shape, generator=_gen(seed + idx)) * 2 - 1) * bound).to(dtype)
+
+    xs = (M, K) if lead_shape is None else tuple(lead_shape) + (K,)
+    if x_dist == "uniform":
+        x = torch.rand(xs, generator=_gen(seed)).to(dtype)
+    else:
+        x = torch.randn(xs, generator=_gen(seed)).to(dtype)
+    if w_std is None:
+        w_gate, w_up, w_down = linear_default((N, K), 1), linear_default((N, K), 2), linear_default((K, N), 3)
+    else:
+        w_gate, w_up, w_down = normal((N, K), w_std, 1), normal((N, K), w_std, 2), normal((K, N), w_std, 3)
+    b_gate = normal((N,), b_std, 4) if bias else None
+    b_up = normal((N,), b_std, 5) if bias else None
+    b_down = normal((K,), b_std, 6) if bias else None
+    dy = (torch.randn(xs, generator=_gen(seed + 7)) * dy_std).to(dtype)
+    return Case(x, w_gate, b_gate, w_up, b_up, w_down, b_down, dy)
+
+
+def forward_backward(case: Case, dropout_p: float = 0.0, seed: int = 0, offset: int = 0, *, row0: int = 0,
+                     col0: int = 0, n_global: Optional[int] = None, grads: bool = True) -> Dict[str, Tensor]:
+    """fp32 oracle outputs for a case: {"y", "dx", "dgate_proj.weight", ...}."""
+    x, wg, bg, wu, bu, wd, bd, dy = case.f32()
+    rows = x.numel() // x.shape[-1]
+    ks = keep_scale_tensor(rows, wg.shape[0], dropout_p, seed, offset, row0=row0, col0=col0, n_global=n_global)
+    out = {"y": forward(x, wg, bg, wu, bu, wd, bd, ks)}
+    if grads:
+        out.update(backward(x, wg, bg, wu, bu, wd, bd, dy, ks))
+    return out
+
+
+# ---------------------------------------------------------------- parity ----
+def parity_errors(got: Tensor, want: Tensor):
+    """(max abs error, mean relative error = mean|got - want| / mean|want|)."""
+    got, want = got.double(), want.double()
+    diff = (got - want).abs()
+    denom = want.abs().mean().clamp_min(1e-30)
+    return diff.max().item(), (diff.mean() / denom).item()
+
+
+def assert_parity(got: Tensor, want: Tensor, name: str = "", max_abs: float = MAX_ABS_TOL,
+                  mean_rel: float = MEAN_REL_TOL) -> None:
+    assert got.shape == want.shape, f"{name}: shape {tuple(got.shape)} != {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{name}: non-finite values"
+    ma, mr = parity_errors(got, want)
+    assert ma <= max_abs and mr <= mean_rel, (
+        f"{name}: max abs err {ma:.3e} (tol {max_abs:.1e}), mean rel err {mr:.3e} (tol {mean_rel:.1e})"
+    )

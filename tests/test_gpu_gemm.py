@@ -1,0 +1,60 @@
+"""The tcgen05 GEMM engine against torch fp32 matmul, for every operand layout the
+forward and backward passes use, including ragged edges (M, N, K not multiples of
+the 128 x 256 x 64 tile)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    (128, 256, 64),      # one tile, one reduction block
+    (128, 256, 512),     # ring wraps (8 blocks through 4 stages)
+    (256, 512, 192),     # 2 x 2 tiles
+    (200, 328, 136),     # ragged everywhere (multiples of 8)
+    (1, 8, 8),           # smallest legal problem
+    (1536, 2304, 1024),  # more tiles than fit one wave of TMEM buffers per CTA
+    (148 * 128 * 3, 256, 128),  # three tiles per CTA on a 148-SM part: both accumulators reused
+]
+
+
+def _operands(M, N, K, a_mn, b_mn, dtype, dev):
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+    a = (torch.randn((M, K), generator=g) * 0.5).to(dtype)
+    b = (torch.randn((N, K), generator=g) * 0.5).to(dtype)
+    ref = a.float() @ b.float().T
+    a_dev = (a.T.contiguous() if a_mn else a).to(dev)
+    b_dev = (b.T.contiguous() if b_mn else b).to(dev)
+    return a_dev, b_dev, ref
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_gemm_layouts(pkg, cuda_dev, shape, a_mn, b_mn, dtype):
+    M, N, K = shape
+    if a_mn and M % 8:
+        pytest.skip("an M-contiguous A needs M % 8 == 0 (16-byte row pitch)")
+    if M > 4096 and dtype == torch.float16:
+        pytest.skip("large case once")
+    a, b, ref = _operands(M, N, K, a_mn, b_mn, dtype, cuda_dev)
+    c = pkg.ops.kernels.gemm(a, b, a_mn=a_mn, b_mn=b_mn).float().cpu()
+    # fp32 accumulation; the only rounding is the 16-bit store
+    tol = 2 ** -8 if dtype == torch.bfloat16 else 2 ** -10
+    err = (c - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= tol * max(scale, 1.0), f"max err {err:.3e} at scale {scale:.3e}"
+
+
+def test_gemm_bias(pkg, cuda_dev):
+    a, b, ref = _operands(300, 264, 320, False, False, torch.bfloat16, cuda_dev)
+    bias = torch.linspace(-1, 1, 264).to(torch.bfloat16)
+    c = pkg.ops.kernels.gemm(a, b, bias=bias.to(cuda_dev)).float().cpu()
+    ref = ref + bias.float()
+    assert (c - ref).abs().max().item() <= 2 ** -8 * max(ref.abs().max().item(), 1.0)
+
+
+def test_gemm_is_deterministic(pkg, cuda_dev):
+    a, b, _ = _operands(1024, 1024, 512, False, True, torch.bfloat16, cuda_dev)
+    c1 = pkg.ops.kernels.gemm(a, b, b_mn=True)
+    c2 = pkg.ops.kernels.gemm(a, b, b_mn=True)
+    assert torch.equal(c1, c2)

@@ -1,0 +1,15 @@
+"""B200-native gated MLP: the reference's FusedGatedMLP API on hand-written sm_100a kernels.
+
+The directory name carries a hyphen, so the package is registered under the
+importable name `triton_gated_mlp_b200` by `load_package()` in the repository's
+`__graft_entry__.py` (tests and bench.py call it); after that
+`from triton_gated_mlp_b200.gated_mlp import FusedGatedMLP` is the one-line swap
+for `from triton_gated_mlp.gated_mlp import FusedGatedMLP`.
+"""
+from . import _lib, build, parallel  # noqa: F401
+from .gated_mlp import FusedGatedMLP, FusedGatedMLPFunction, mlp_hidden_states_bwd, mlp_hidden_states_fwd  # noqa: F401
+
+__all__ = [
+    "FusedGatedMLP", "FusedGatedMLPFunction", "mlp_hidden_states_fwd", "mlp_hidden_states_bwd",
+    "parallel", "build",
+]

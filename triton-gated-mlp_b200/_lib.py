@@ -1,0 +1,124 @@
+"""ctypes binding of libgmlp.so (C ABI declared in include/gmlp.h).
+
+There is no fallback: if the library is missing or a call fails, the caller gets
+an exception that names the problem. Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIB_PATH = Path(__file__).resolve().parent / "libgmlp.so"
+
+GMLP_BF16, GMLP_FP16 = 0, 1
+
+# Every symbol include/gmlp.h declares; tests check that the library exports all of them.
+EXPORTS = (
+    "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
+    "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum",
+    "gmlp_dropout_mask", "gmlp_gemm",
+    "gmlp_status_read", "gmlp_last_error", "gmlp_version",
+)
+
+
+class GmlpError(RuntimeError):
+    pass
+
+
+class Problem(C.Structure):
+    """Mirror of gmlp_problem_t."""
+
+    _fields_ = [
+        ("M", C.c_int64), ("K", C.c_int64), ("N", C.c_int64),
+        ("dtype", C.c_int32), ("dropout_p", C.c_float),
+        ("seed", C.c_uint64), ("offset", C.c_uint64),
+        ("row0_global", C.c_int64), ("col0_global", C.c_int64), ("N_global", C.c_int64),
+    ]
+
+
+_lib = None
+
+
+def _declare(lib: C.CDLL) -> None:
+    vp, i32, i64, u8p = C.c_void_p, C.c_int32, C.c_int64, C.c_void_p
+    pp = C.POINTER(Problem)
+    lib.gmlp_hidden_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_down_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_bwd_dhidden.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_bwd_dact.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_bwd_dx.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_bwd_dw_gate_up.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_bwd_dw_down.argtypes = [pp, vp, vp, vp, vp]
+    lib.gmlp_colsum_scratch_bytes.argtypes = [i64, i64]
+    lib.gmlp_colsum_scratch_bytes.restype = C.c_size_t
+    lib.gmlp_colsum.argtypes = [i64, i64, i32, vp, i64, vp, C.c_size_t, vp, vp]
+    lib.gmlp_dropout_mask.argtypes = [pp, u8p, vp]
+    lib.gmlp_gemm.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp]
+    lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]
+    lib.gmlp_last_error.restype = C.c_char_p
+    lib.gmlp_version.restype = C.c_int
+    for name in EXPORTS:
+        getattr(lib, name)  # AttributeError here means the library and the header disagree
+
+
+def load() -> C.CDLL:
+    """Load libgmlp.so from the package directory (built in-tree by build.py)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise GmlpError(
+                f"{LIB_PATH} is missing: run `python __graft_entry__.py` (or the package's "
+                "build.build()) to compile the sm_100a kernels. There is no CPU or Triton fallback."
+            )
+        lib = C.CDLL(str(LIB_PATH))
+        _declare(lib)
+        _lib = lib
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise GmlpError(f"libgmlp error {rc}: {load().gmlp_last_error().decode()}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return GMLP_BF16
+    if dt == torch.float16:
+        return GMLP_FP16
+    raise NotImplementedError(
+        f"libgmlp computes in bfloat16 or float16 (fp32 accumulation); got {dt}. "
+        "Convert the module and its input with .to(torch.bfloat16) or .to(torch.float16)."
+    )
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*tensors: torch.Tensor | None) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise GmlpError("libgmlp has no CPU path: every tensor must live on a CUDA (sm_100a) device")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise GmlpError(f"tensors on different devices: {dev} and {t.device}")
+    return dev
+
+
+def status_read(device: torch.device | None = None) -> int:
+    """Synchronise `device` and return (and clear) its kernel status word."""
+    v = C.c_int(0)
+    with torch.cuda.device(device):
+        check(load().gmlp_status_read(C.byref(v)))
+    return v.value

@@ -1,0 +1,116 @@
+// HBM-bound helper kernels around the GEMMs: the SiLU/multiply derivative for a
+// caller-supplied dH, column sums for the bias gradients, and the dropout-mask
+// dump used by the bit-exact mask check.
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace gmlp {
+
+// d_gate = dH' * u * silu'(g), d_up = dH' * silu(g), dH' = dH * keep / (1-p).
+// One thread per 8 consecutive columns; grid-stride over the [M, N] matrix.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dact_kernel(const T* __restrict__ dh, const T* __restrict__ g, const T* __restrict__ u,
+            T* __restrict__ d_gate, T* __restrict__ d_up, long long M, long long N,
+            DropoutParams drop) {
+  const long long groups_per_row = N / 8;
+  const long long total = M * groups_per_row;
+  const bool drop_on = drop.thresh != 0u;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / groups_per_row;
+    const long long col = (i - row * groups_per_row) * 8;
+    const long long o = row * N + col;
+    float a[8], gv[8], uv[8], dg[8], du[8];
+    load8(dh + o, a);
+    load8(g + o, gv);
+    load8(u + o, uv);
+    if (drop_on) {
+      float f[8];
+      dropout_factors8(drop, drop.row0_global + row, drop.col0_global + col, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) a[k] *= f[k];
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = sigmoid_f(gv[k]);
+      du[k] = a[k] * gv[k] * s;
+      dg[k] = a[k] * uv[k] * s * (1.0f + gv[k] * (1.0f - s));
+    }
+    store8(d_gate + o, dg);
+    store8(d_up + o, du);
+  }
+}
+
+// keep-mask dump: one thread per 4 consecutive columns.
+__global__ void __launch_bounds__(256)
+dropout_mask_kernel(uint8_t* __restrict__ mask, long long M, long long N, DropoutParams drop) {
+  const long long quads_per_row = N / 4;
+  const long long total = M * quads_per_row;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / quads_per_row;
+    const long long col = (i - row * quads_per_row) * 4;
+    const unsigned long long e =
+        static_cast<unsigned long long>(drop.row0_global + row) *
+            static_cast<unsigned long long>(drop.ncols_global) +
+        static_cast<unsigned long long>(drop.col0_global + col);
+    const Philox4 r = dropout_words(drop, e >> 2);
+    uchar4 m;
+    m.x = r.x >= drop.thresh;
+    m.y = r.y >= drop.thresh;
+    m.z = r.z >= drop.thresh;
+    m.w = r.w >= drop.thresh;
+    *reinterpret_cast<uchar4*>(mask + row * N + col) = m;
+  }
+}
+
+// Column sums, pass 1: block (cb, rb) sums rows [rb*rows_per_block, ...) of the
+// 128 columns starting at cb*128 and writes them to partial[rb, :].
+constexpr int COLSUM_COLS = 128;
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* __restrict__ src, long long rows, long long cols, long long ld,
+                      long long rows_per_block, float* __restrict__ partial) {
+  __shared__ float red[16][COLSUM_COLS + 4];
+  const int tx = threadIdx.x & 15;  // 8-column group inside the 128-column slab
+  const int ty = threadIdx.x >> 4;  // row lane
+  const long long col = static_cast<long long>(blockIdx.x) * COLSUM_COLS + tx * 8;
+  const long long r0 = static_cast<long long>(blockIdx.y) * rows_per_block;
+  const long long r1 = min(rows, r0 + rows_per_block);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < cols) {
+    for (long long r = r0 + ty; r < r1; r += 16) {
+      float v[8];
+      load8(src + r * ld + col, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) red[ty][tx * 8 + k] = acc[k];
+  __syncthreads();
+  if (threadIdx.x < COLSUM_COLS) {
+    const long long c = static_cast<long long>(blockIdx.x) * COLSUM_COLS + threadIdx.x;
+    if (c < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) s += red[j][threadIdx.x];
+      partial[static_cast<long long>(blockIdx.y) * cols + c] = s;
+    }
+  }
+}
+
+// Column sums, pass 2: dst[c] = sum_rb partial[rb, c], rounded to T.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, long long cols, int row_blocks,
+                    T* __restrict__ dst) {
+  const long long c = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int rb = 0; rb < row_blocks; ++rb) s += partial[static_cast<long long>(rb) * cols + c];
+  dst[c] = static_cast<T>(s);
+}
+
+}  // namespace gmlp

@@ -1,0 +1,557 @@
+// C ABI of libgmlp.so (declared in include/gmlp.h): argument checks, TMA tensor
+// map encoding and kernel launches. No torch types, no allocation, no CPU path.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/gmlp.h"
+#include "elementwise.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace gmlp {
+
+// ------------------------------------------------------------------ errors --
+static thread_local char g_err[512] = "";
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// Per-device status word written by kernels that give up a bounded wait.
+__device__ int g_dev_status;
+
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int cc_major = 0;
+  int* status_ptr = nullptr;
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int device_info(const DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(GMLP_ERR_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess)
+      return fail(GMLP_ERR_LAUNCH, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    d.sm_count = prop.multiProcessorCount;
+    d.cc_major = prop.major;
+    if (d.cc_major != 10)
+      return fail(GMLP_ERR_ARCH, "libgmlp needs an sm_100a device, found compute capability %d.%d",
+                  prop.major, prop.minor);
+    void* sp = nullptr;
+    e = cudaGetSymbolAddress(&sp, g_dev_status);
+    if (e != cudaSuccess)
+      return fail(GMLP_ERR_LAUNCH, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    d.status_ptr = static_cast<int*>(sp);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || fn == nullptr || qres != cudaDriverEntryPointSuccess)
+        return fail(GMLP_ERR_LAUNCH, "cuTensorMapEncodeTiled entry point not available");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return GMLP_OK;
+}
+
+// ------------------------------------------------------------- tensor maps --
+// 2-D row-major matrix [outer, inner] of 16-bit elements, 128-byte swizzle,
+// out-of-bounds elements read as zero.
+static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
+                      int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt =
+      dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(GMLP_ERR_LAUNCH,
+                "cuTensorMapEncodeTiled failed (%d) for base=%p inner=%lld outer=%lld pitch=%lld",
+                static_cast<int>(r), base, static_cast<long long>(inner),
+                static_cast<long long>(outer), static_cast<long long>(pitch_elems));
+  return GMLP_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// One operand of C = A B^T as it lies in memory.
+struct Operand {
+  const void* ptr;
+  int64_t mn;     // extent along M (for A) or N (for B)
+  int64_t k;      // extent along the reduction
+  int64_t ld;     // row pitch in elements
+  bool mn_major;  // false: stored [mn, k]; true: stored [k, mn]
+};
+
+static int encode_operand(CUtensorMap* m, const Operand& o, uint32_t kmajor_box_rows, int dtype) {
+  if (!o.ptr) return fail(GMLP_ERR_ARG, "NULL matrix pointer");
+  if (!aligned16(o.ptr) || (o.ld % 8) != 0)
+    return fail(GMLP_ERR_ALIGN, "matrix base %p / pitch %lld not 16-byte aligned", o.ptr,
+                static_cast<long long>(o.ld));
+  if (o.mn_major) return encode_map(m, o.ptr, o.mn, o.k, o.ld, 64, BK, dtype);
+  return encode_map(m, o.ptr, o.k, o.mn, o.ld, BK, kmajor_box_rows, dtype);
+}
+
+// --------------------------------------------------------------- launching --
+struct Epilogue {
+  void* out0 = nullptr;
+  void* out1 = nullptr;
+  void* out2 = nullptr;
+  const void* in0 = nullptr;
+  const void* in1 = nullptr;
+  const void* bias0 = nullptr;
+  const void* bias1 = nullptr;
+  int64_t ld_out = 0;
+  int64_t ld_in = 0;
+  DropoutParams drop = {};
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
+static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
+                         const Operand& a0, const Operand* a1, const Operand& b0,
+                         const Operand* b1, int64_t k1, int batches, const Epilogue& ep,
+                         cudaStream_t stream) {
+  constexpr int STAGES = (BN > 128) ? 4 : 6;
+  constexpr uint32_t b_rows = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  CUtensorMap mA0, mA1, mB0, mB1;
+  int rc;
+  if ((rc = encode_operand(&mA0, a0, BM, dtype))) return rc;
+  if ((rc = encode_operand(&mB0, b0, b_rows, dtype))) return rc;
+  if (a1) {
+    if ((rc = encode_operand(&mA1, *a1, BM, dtype))) return rc;
+  } else {
+    mA1 = mA0;
+  }
+  if (b1) {
+    if ((rc = encode_operand(&mB1, *b1, b_rows, dtype))) return rc;
+  } else {
+    mB1 = mB0;
+  }
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.M = static_cast<int>(M);
+  args.N = static_cast<int>(N);
+  args.kb0 = static_cast<int>((a0.k + BK - 1) / BK);
+  args.kb1 = static_cast<int>((k1 + BK - 1) / BK);
+  args.batches = batches;
+  args.idesc = make_idesc_f16(BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
+  args.status = dev->status_ptr;
+  args.out0 = ep.out0;
+  args.out1 = ep.out1;
+  args.out2 = ep.out2;
+  args.in0 = ep.in0;
+  args.in1 = ep.in1;
+  args.bias0 = ep.bias0;
+  args.bias1 = ep.bias1;
+  args.ld_out = ep.ld_out;
+  args.ld_in = ep.ld_in;
+  args.drop = ep.drop;
+
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int64_t m_tiles = (M + BM - 1) / BM;
+  const int64_t n_tiles = (N + TILE_N - 1) / TILE_N;
+  const int64_t tiles = m_tiles * n_tiles * batches;
+  if (tiles <= 0 || tiles > 0x7fffffffLL) return fail(GMLP_ERR_SHAPE, "tile count out of range");
+  // Raster groups: about sqrt(#SMs) row tiles per group keeps the set of
+  // concurrently running tiles close to square, which minimises distinct A and
+  // B tiles that L2 has to serve at the same time.
+  args.group_m = 16;
+  const int grid = static_cast<int>(tiles < dev->sm_count ? tiles : dev->sm_count);
+  constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
+  auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, const Operand& a0,
+                       const Operand* a1, const Operand& b0, const Operand* b1, int64_t k1,
+                       int batches, const Epilogue& ep, cudaStream_t stream) {
+  if (dtype == GMLP_BF16)
+    return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1, k1,
+                                                             batches, ep, stream);
+  return launch_gemm_t<BN, A_MN, B_MN, EPI, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
+                                                    ep, stream);
+}
+
+static int check_problem(const gmlp_problem_t* p) {
+  if (!p) return fail(GMLP_ERR_ARG, "NULL problem descriptor");
+  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", p->dtype);
+  if (p->M <= 0 || p->K <= 0 || p->N <= 0)
+    return fail(GMLP_ERR_SHAPE, "M=%lld K=%lld N=%lld must be positive",
+                static_cast<long long>(p->M), static_cast<long long>(p->K),
+                static_cast<long long>(p->N));
+  if (p->M > 0x7fffffffLL || p->K > 0x7fffffffLL || p->N > 0x3fffffffLL)
+    return fail(GMLP_ERR_SHAPE, "dimension exceeds 32-bit tile coordinates");
+  if ((p->K % 8) != 0 || (p->N % 8) != 0)
+    return fail(GMLP_ERR_SHAPE, "K=%lld and N=%lld must be multiples of 8",
+                static_cast<long long>(p->K), static_cast<long long>(p->N));
+  if (!(p->dropout_p >= 0.0f && p->dropout_p < 1.0f))
+    return fail(GMLP_ERR_ARG, "dropout_p=%f outside [0, 1)", static_cast<double>(p->dropout_p));
+  const int64_t ng = p->N_global ? p->N_global : p->N;
+  if (p->dropout_p > 0.0f && ((ng % 4) != 0 || (p->col0_global % 4) != 0 || p->row0_global < 0 ||
+                              p->col0_global < 0 || p->col0_global + p->N > ng))
+    return fail(GMLP_ERR_SHAPE, "dropout needs N_global and col0_global multiples of 4 and the "
+                                "local columns inside [0, N_global)");
+  return GMLP_OK;
+}
+
+static DropoutParams make_dropout(const gmlp_problem_t* p) {
+  DropoutParams d;
+  memset(&d, 0, sizeof(d));
+  d.scale = 1.0f;
+  d.row0_global = p->row0_global;
+  d.col0_global = p->col0_global;
+  d.ncols_global = p->N_global ? p->N_global : p->N;
+  if (p->dropout_p > 0.0f) {
+    // floor(p * 2^32), evaluated in double so the CPU restatement agrees bit for bit.
+    double t = static_cast<double>(p->dropout_p) * 4294967296.0;
+    if (t > 4294967295.0) t = 4294967295.0;
+    d.thresh = static_cast<uint32_t>(t);
+    d.scale = 1.0f / (1.0f - p->dropout_p);
+    d.seed_lo = static_cast<uint32_t>(p->seed);
+    d.seed_hi = static_cast<uint32_t>(p->seed >> 32);
+    d.off_lo = static_cast<uint32_t>(p->offset);
+    d.off_hi = static_cast<uint32_t>(p->offset >> 32);
+  }
+  return d;
+}
+
+static int check_ptrs(std::initializer_list<const void*> ps) {
+  for (const void* q : ps) {
+    if (!q) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+    if (!aligned16(q)) return fail(GMLP_ERR_ALIGN, "pointer %p is not 16-byte aligned", q);
+  }
+  return GMLP_OK;
+}
+
+}  // namespace gmlp
+
+using namespace gmlp;
+
+extern "C" {
+
+int gmlp_version(void) { return 100; }
+
+const char* gmlp_last_error(void) { return g_err; }
+
+int gmlp_status_read(int* value) {
+  if (!value) return fail(GMLP_ERR_ARG, "NULL value pointer");
+  const DeviceInfo* dev;
+  int rc = device_info(&dev);
+  if (rc) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  int v = 0;
+  e = cudaMemcpy(&v, dev->status_ptr, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaMemcpy: %s", cudaGetErrorString(e));
+  if (v != 0) {
+    e = cudaMemset(dev->status_ptr, 0, sizeof(int));
+    if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaMemset: %s", cudaGetErrorString(e));
+  }
+  *value = v;
+  return GMLP_OK;
+}
+
+int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, void* h,
+                    void* g_save, void* u_save, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({x, w_gate, w_up, h}))) return rc;
+  if ((g_save == nullptr) != (u_save == nullptr))
+    return fail(GMLP_ERR_ARG, "g_save and u_save must both be given or both be NULL");
+  if ((b_gate && !aligned16(b_gate)) || (b_up && !aligned16(b_up)) ||
+      (g_save && (!aligned16(g_save) || !aligned16(u_save))))
+    return fail(GMLP_ERR_ALIGN, "bias / save buffers must be 16-byte aligned");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const Operand a{x, p->M, p->K, p->K, false};
+  const Operand bg{w_gate, p->N, p->K, p->K, false};
+  const Operand bu{w_up, p->N, p->K, p->K, false};
+  Epilogue ep;
+  ep.out0 = h;
+  ep.out1 = g_save;
+  ep.out2 = u_save;
+  ep.bias0 = b_gate;
+  ep.bias1 = b_up;
+  ep.ld_out = p->N;
+  ep.drop = make_dropout(p);
+  return launch_gemm<256, false, false, EPI_SWIGLU>(dev, p->dtype, p->M, p->N, a, nullptr, bg, &bu,
+                                                    0, 1, ep, static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
+                  const void* b_down, const void* residual, void* y, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({h, w_down, y}))) return rc;
+  if ((b_down && !aligned16(b_down)) || (residual && !aligned16(residual)))
+    return fail(GMLP_ERR_ALIGN, "bias / residual must be 16-byte aligned");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const Operand a{h, p->M, p->N, p->N, false};
+  const Operand b{w_down, p->K, p->N, p->N, false};
+  Epilogue ep;
+  ep.out0 = y;
+  ep.in0 = residual;
+  ep.bias0 = b_down;
+  ep.ld_out = p->K;
+  ep.ld_in = p->K;
+  return launch_gemm<256, false, false, EPI_STORE>(dev, p->dtype, p->M, p->K, a, nullptr, b,
+                                                   nullptr, 0, 1, ep,
+                                                   static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down,
+                     const void* g, const void* u, void* d_gate, void* d_up, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({dy, w_down, g, u, d_gate, d_up}))) return rc;
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  // dH[M,N] = dy[M,K] . W_down[K,N]: the reduction runs over W_down's rows.
+  const Operand a{dy, p->M, p->K, p->K, false};
+  const Operand b{w_down, p->N, p->K, p->N, true};
+  Epilogue ep;
+  ep.out0 = d_gate;
+  ep.out1 = d_up;
+  ep.in0 = g;
+  ep.in1 = u;
+  ep.ld_out = p->N;
+  ep.ld_in = p->N;
+  ep.drop = make_dropout(p);
+  return launch_gemm<256, false, true, EPI_DHIDDEN>(dev, p->dtype, p->M, p->N, a, nullptr, b,
+                                                    nullptr, 0, 1, ep,
+                                                    static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                const void* w_gate, const void* w_up, void* dx, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({d_gate, d_up, w_gate, w_up, dx}))) return rc;
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  // dx[M,K] = d_gate[M,N] . W_gate[N,K] + d_up[M,N] . W_up[N,K]: one accumulator,
+  // two reduction segments of length N.
+  const Operand a0{d_gate, p->M, p->N, p->N, false};
+  const Operand a1{d_up, p->M, p->N, p->N, false};
+  const Operand b0{w_gate, p->K, p->N, p->K, true};
+  const Operand b1{w_up, p->K, p->N, p->K, true};
+  Epilogue ep;
+  ep.out0 = dx;
+  ep.ld_out = p->K;
+  return launch_gemm<256, false, true, EPI_STORE>(dev, p->dtype, p->M, p->K, a0, &a1, b0, &b1,
+                                                  p->N, 1, ep, static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                        const void* x, void* dw_gate, void* dw_up, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({d_gate, d_up, x, dw_gate, dw_up}))) return rc;
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  // dW[N,K] = d^T[N,M] . x[M,K]: both operands lie token-major, the reduction
+  // runs over their rows. Two problems share x.
+  const Operand a0{d_gate, p->N, p->M, p->N, true};
+  const Operand a1{d_up, p->N, p->M, p->N, true};
+  const Operand b{x, p->K, p->M, p->K, true};
+  Epilogue ep;
+  ep.out0 = dw_gate;
+  ep.out1 = dw_up;
+  ep.ld_out = p->K;
+  return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr, 0,
+                                                 2, ep, static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                     void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({dy, h, dw_down}))) return rc;
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  // dW_down[K,N] = dy^T[K,M] . h[M,N]
+  const Operand a{dy, p->K, p->M, p->K, true};
+  const Operand b{h, p->N, p->M, p->N, true};
+  Epilogue ep;
+  ep.out0 = dw_down;
+  ep.ld_out = p->N;
+  return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->K, p->N, a, nullptr, b, nullptr,
+                                                 0, 1, ep, static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const void* u,
+                  void* d_gate, void* d_up, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({dh, g, u, d_gate, d_up}))) return rc;
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const DropoutParams d = make_dropout(p);
+  const long long groups = p->M * (p->N / 8);
+  long long blocks = (groups + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->dtype == GMLP_BF16)
+    dact_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dh), static_cast<const __nv_bfloat16*>(g),
+        static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(d_gate),
+        static_cast<__nv_bfloat16*>(d_up), p->M, p->N, d);
+  else
+    dact_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const __half*>(dh), static_cast<const __half*>(g),
+        static_cast<const __half*>(u), static_cast<__half*>(d_gate), static_cast<__half*>(d_up),
+        p->M, p->N, d);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if (!mask) return fail(GMLP_ERR_ARG, "NULL mask pointer");
+  if ((reinterpret_cast<uintptr_t>(mask) & 3u) != 0)
+    return fail(GMLP_ERR_ALIGN, "mask must be 4-byte aligned");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const DropoutParams d = make_dropout(p);
+  const long long quads = p->M * (p->N / 4);
+  long long blocks = (quads + 255) / 256;
+  const long long cap = static_cast<long long>(dev->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  dropout_mask_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      mask, p->M, p->N, d);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+static int colsum_row_blocks(int64_t rows, int64_t cols) {
+  const int64_t col_blocks = (cols + COLSUM_COLS - 1) / COLSUM_COLS;
+  int64_t rb = (148 * 4 + col_blocks - 1) / col_blocks;  // about four blocks per SM
+  const int64_t max_rb = (rows + 63) / 64;               // at least 64 rows per block
+  if (rb > max_rb) rb = max_rb;
+  if (rb < 1) rb = 1;
+  return static_cast<int>(rb);
+}
+
+size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>(colsum_row_blocks(rows, cols)) * static_cast<size_t>(cols) *
+         sizeof(float);
+}
+
+int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                void* scratch, size_t scratch_bytes, void* dst, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (rows <= 0 || cols <= 0 || (cols % 8) != 0 || (ld % 8) != 0 || ld < cols)
+    return fail(GMLP_ERR_SHAPE, "colsum needs rows > 0, cols and ld multiples of 8, ld >= cols");
+  if (!src || !dst || !scratch) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(src) || !aligned16(scratch))
+    return fail(GMLP_ERR_ALIGN, "src / scratch must be 16-byte aligned");
+  if (scratch_bytes < gmlp_colsum_scratch_bytes(rows, cols))
+    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes,
+                gmlp_colsum_scratch_bytes(rows, cols));
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  const int rb = colsum_row_blocks(rows, cols);
+  const long long rows_per_block = (rows + rb - 1) / rb;
+  const dim3 grid(static_cast<unsigned>((cols + COLSUM_COLS - 1) / COLSUM_COLS),
+                  static_cast<unsigned>(rb));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* part = static_cast<float*>(scratch);
+  const unsigned fin_blocks = static_cast<unsigned>((cols + 255) / 256);
+  if (dtype == GMLP_BF16) {
+    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows_per_block, part);
+    colsum_final_kernel<__nv_bfloat16><<<fin_blocks, 256, 0, st>>>(
+        part, cols, rb, static_cast<__nv_bfloat16*>(dst));
+  } else {
+    colsum_partial_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), rows,
+                                                        cols, ld, rows_per_block, part);
+    colsum_final_kernel<__half><<<fin_blocks, 256, 0, st>>>(part, cols, rb,
+                                                            static_cast<__half*>(dst));
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,
+              const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+              const void* bias, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (M <= 0 || N <= 0 || K <= 0 || (N % 8) != 0 || (ldc % 8) != 0 || M > 0x7fffffffLL ||
+      N > 0x7fffffffLL || K > 0x7fffffffLL)
+    return fail(GMLP_ERR_SHAPE, "gemm needs positive M, N, K; N and ldc multiples of 8");
+  if (!C || !aligned16(C) || (bias && !aligned16(bias)))
+    return fail(GMLP_ERR_ALIGN, "C / bias must be non-NULL and 16-byte aligned");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  const Operand a{A, M, K, lda, a_mn != 0};
+  const Operand b{B, N, K, ldb, b_mn != 0};
+  Epilogue ep;
+  ep.out0 = C;
+  ep.bias0 = bias;
+  ep.ld_out = ldc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!a_mn && !b_mn)
+    return launch_gemm<256, false, false, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0,
+                                                     1, ep, st);
+  if (!a_mn && b_mn)
+    return launch_gemm<256, false, true, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
+                                                    ep, st);
+  if (a_mn && b_mn)
+    return launch_gemm<256, true, true, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
+                                                   ep, st);
+  return launch_gemm<256, true, false, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
+                                                  ep, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,166 @@
+"""FusedGatedMLP: the reference's module API on sm_100a kernels.
+
+Drop-in for the reference's FusedGatedMLP (src/triton_gated_mlp/gated_mlp.py:203-237):
+same constructor keywords, parameter names (gate_proj / up_proj / down_proj, so
+state_dicts and copy_weights keep working), attributes (hidden_size,
+intermediate_size, act_fn, dropout) and forward(x) contract for any number of
+leading dimensions. Semantics are those of EagerGatedMLP (:73-98): bias on all
+three projections and dropout on the hidden state, which the reference's fused
+path silently drops (:172-180, :200).
+
+One autograd.Function spans all three projections. Forward: one tcgen05 kernel
+for gate/up + bias + SiLU*up + dropout, one for the down projection. Backward:
+dH fused with the activation derivative, then dX, dW_gate/dW_up, dW_down, and
+column sums for the bias gradients; the gate / up pre-activations are saved, not
+recomputed.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor, nn
+from torch.autograd.function import Function
+
+from .ops import kernels
+from .ops.fwd import SUPPORTED_ACTS, mlp_hidden_states_fwd  # noqa: F401  (re-exported like the reference)
+from .ops.bwd import mlp_hidden_states_bwd  # noqa: F401
+from .ops.kernels import Dropout, Shard
+from . import parallel
+
+
+class FusedGatedMLPFunction(Function):
+    """y = down(dropout(silu(gate(x)) * up(x))) with hand-written forward and backward.
+
+    Replaces the reference's FusedGatedMLPFunction (gated_mlp.py:159-200), which
+    covers only the gate/up half and returns no bias gradients.
+    """
+
+    @staticmethod
+    def forward(ctx, x: Tensor, W_gate: Tensor, b_gate: Optional[Tensor], W_up: Tensor,
+                b_up: Optional[Tensor], W_down: Tensor, b_down: Optional[Tensor],
+                drop: Dropout, shard: Shard, tp_group) -> Tensor:
+        need_bwd = any(ctx.needs_input_grad)
+        if need_bwd:
+            h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True)
+        else:
+            h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False)
+            g = u = None
+        # With the intermediate dimension sharded, every rank holds a partial sum
+        # of y; the output bias is added once, by the rank that owns column 0.
+        add_bias = b_down if (tp_group is None or shard.col0 == 0) else None
+        y = kernels.down_fwd(h, W_down, add_bias)
+        if tp_group is not None:
+            parallel.all_reduce_sum(y, tp_group)
+        if need_bwd:
+            ctx.save_for_backward(x, W_gate, W_up, W_down, g, u, h)
+            ctx.drop, ctx.shard, ctx.tp_group = drop, shard, tp_group
+            ctx.has_bias = (b_gate is not None, b_up is not None, b_down is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x, W_gate, W_up, W_down, g, u, h = ctx.saved_tensors
+        need = ctx.needs_input_grad
+        dy = dy.contiguous()
+        dx = dW_gate = db_gate = dW_up = db_up = dW_down = db_down = None
+        need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
+        if need_hidden:
+            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard)
+            if need[0]:
+                dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
+                if ctx.tp_group is not None:
+                    parallel.all_reduce_sum(dx, ctx.tp_group)
+            if need[1] or need[3]:
+                dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
+            if need[2] and ctx.has_bias[0]:
+                db_gate = kernels.colsum(d_gate)
+            if need[4] and ctx.has_bias[1]:
+                db_up = kernels.colsum(d_up)
+        if need[5]:
+            dW_down = kernels.bwd_dw_down(dy, h)
+        if need[6] and ctx.has_bias[2]:
+            db_down = kernels.colsum(dy)
+        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None
+
+
+class FusedGatedMLP(nn.Module):
+    """Gated MLP block; see the module docstring.
+
+    Extra keyword-only arguments (all default to the single-GPU reference behaviour):
+      parallel_mode  "none" | "token" | "tp". "token": this rank holds a slice of
+                     the token rows and full weights; no communication, only the
+                     dropout mask is offset by `token_row0`. "tp": this rank's
+                     parameters are the rank-th slice of the intermediate
+                     dimension (intermediate_size is the LOCAL size) and the
+                     down-projection partial sums are all-reduced over
+                     `process_group`.
+      process_group  torch.distributed group for "tp".
+      philox_seed    dropout seed; `philox_offset` advances by one per training
+                     forward call.
+    """
+
+    def __init__(
+        self,
+        hidden_size: int = 256,
+        intermediate_size: int = 512,
+        bias: bool = True,
+        hidden_act: str = "silu",
+        dropout_p: float = 0.0,
+        *,
+        parallel_mode: str = "none",
+        process_group=None,
+        tp_rank: Optional[int] = None,
+        tp_size: Optional[int] = None,
+        philox_seed: int = 0,
+    ):
+        super().__init__()
+        if hidden_act not in SUPPORTED_ACTS:
+            raise NotImplementedError(f"gate activation {hidden_act!r}: only SiLU is implemented")
+        if parallel_mode not in ("none", "token", "tp"):
+            raise ValueError(f"parallel_mode {parallel_mode!r} not in ('none', 'token', 'tp')")
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=bias)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=bias)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=bias)
+        self.act = nn.SiLU()
+        self.act_fn = hidden_act
+        self.dropout = nn.Dropout(dropout_p)
+        self.parallel_mode = parallel_mode
+        self.process_group = process_group
+        if parallel_mode == "tp":
+            self.tp_rank, self.tp_size = parallel.resolve_rank_size(process_group, tp_rank, tp_size)
+        else:
+            self.tp_rank, self.tp_size = 0, 1
+        self.token_row0 = 0
+        self.philox_seed = int(philox_seed)
+        self.philox_offset = 0
+
+    def set_philox(self, seed: int, offset: int = 0) -> None:
+        self.philox_seed, self.philox_offset = int(seed), int(offset)
+
+    def _shard(self) -> Shard:
+        if self.parallel_mode == "tp":
+            return Shard(row0=0, col0=self.tp_rank * self.intermediate_size,
+                         n_global=self.tp_size * self.intermediate_size)
+        if self.parallel_mode == "token":
+            return Shard(row0=int(self.token_row0), col0=0, n_global=self.intermediate_size)
+        return Shard()
+
+    def forward(self, x: Tensor) -> Tensor:
+        shapes = x.shape
+        if len(shapes) > 2:
+            x = x.reshape(-1, shapes[-1])
+        p = float(self.dropout.p) if self.training else 0.0
+        drop = Dropout(p, self.philox_seed, self.philox_offset)
+        if p > 0.0:
+            self.philox_offset += 1
+        tp_group = self.process_group if self.parallel_mode == "tp" else None
+        if self.parallel_mode == "tp" and tp_group is None:
+            tp_group = parallel.default_group()
+        y = FusedGatedMLPFunction.apply(
+            x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
+            self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group,
+        )
+        return y.view(shapes) if len(shapes) > 2 else y

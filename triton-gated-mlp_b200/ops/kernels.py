@@ -1,0 +1,227 @@
+"""One Python function per libgmlp entry point: tensors in, tensors out.
+
+These wrappers allocate outputs with torch (caller-owned device memory), check
+what the C ABI cannot see (contiguity, dtype agreement, device), and enqueue the
+kernel on torch's current stream. They never compute anything themselves.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+from .._lib import Problem, check, dtype_code, load, ptr, require_cuda, stream_of
+
+
+@dataclass(frozen=True)
+class Dropout:
+    """Dropout settings of one call: probability plus the Philox (seed, offset)."""
+
+    p: float = 0.0
+    seed: int = 0
+    offset: int = 0
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Where this rank's rows / intermediate columns sit in the un-sharded problem."""
+
+    row0: int = 0        # global index of local token row 0
+    col0: int = 0        # global index of local intermediate column 0
+    n_global: int = 0    # un-sharded intermediate size (0: same as local N)
+
+
+NO_DROPOUT = Dropout()
+NO_SHARD = Shard()
+
+
+def _problem(M: int, K: int, N: int, dt: torch.dtype, drop: Dropout, shard: Shard) -> Problem:
+    return Problem(
+        M=M, K=K, N=N, dtype=dtype_code(dt), dropout_p=float(drop.p),
+        seed=int(drop.seed) & 0xFFFFFFFFFFFFFFFF, offset=int(drop.offset) & 0xFFFFFFFFFFFFFFFF,
+        row0_global=shard.row0, col0_global=shard.col0, N_global=shard.n_global,
+    )
+
+
+def _c(t: Tensor | None) -> Tensor | None:
+    """Contiguous view of t (copies only if t is strided)."""
+    return None if t is None else (t if t.is_contiguous() else t.contiguous())
+
+
+def _same_dtype(*ts: Tensor | None) -> torch.dtype:
+    dt = None
+    for t in ts:
+        if t is None:
+            continue
+        if dt is None:
+            dt = t.dtype
+        elif t.dtype != dt:
+            raise TypeError(f"mixed dtypes: {dt} and {t.dtype}")
+    return dt
+
+
+def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
+               drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False):
+    """H = dropout(silu(x W_gate^T + b_gate) * (x W_up^T + b_up)); with save=True also
+    returns the biased pre-activations (G, U)."""
+    dev = require_cuda(x, w_gate, b_gate, w_up, b_up)
+    dt = _same_dtype(x, w_gate, b_gate, w_up, b_up)
+    x, w_gate, w_up, b_gate, b_up = _c(x), _c(w_gate), _c(w_up), _c(b_gate), _c(b_up)
+    M, K = x.shape
+    N = w_gate.shape[0]
+    h = torch.empty((M, N), dtype=dt, device=dev)
+    g = torch.empty((M, N), dtype=dt, device=dev) if save else None
+    u = torch.empty((M, N), dtype=dt, device=dev) if save else None
+    if M > 0:
+        prob = _problem(M, K, N, dt, drop, shard)
+        with torch.cuda.device(dev):
+            check(load().gmlp_hidden_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up),
+                                         ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
+    return (h, g, u) if save else h
+
+
+def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor | None = None) -> Tensor:
+    """y = h W_down^T (+ b_down) (+ residual)."""
+    dev = require_cuda(h, w_down, b_down, residual)
+    dt = _same_dtype(h, w_down, b_down, residual)
+    h, w_down, b_down, residual = _c(h), _c(w_down), _c(b_down), _c(residual)
+    M, N = h.shape
+    K = w_down.shape[0]
+    y = torch.empty((M, K), dtype=dt, device=dev)
+    if M > 0:
+        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+        with torch.cuda.device(dev):
+            check(load().gmlp_down_fwd(C.byref(prob), ptr(h), ptr(w_down), ptr(b_down), ptr(residual),
+                                       ptr(y), stream_of(h)))
+    return y
+
+
+def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT,
+                shard: Shard = NO_SHARD):
+    """(d_gate, d_up) from dy through W_down and the SiLU/multiply derivative."""
+    dev = require_cuda(dy, w_down, g, u)
+    dt = _same_dtype(dy, w_down, g, u)
+    dy, w_down, g, u = _c(dy), _c(w_down), _c(g), _c(u)
+    M, K = dy.shape
+    N = w_down.shape[1]
+    d_gate = torch.empty((M, N), dtype=dt, device=dev)
+    d_up = torch.empty((M, N), dtype=dt, device=dev)
+    if M > 0:
+        prob = _problem(M, K, N, dt, drop, shard)
+        with torch.cuda.device(dev):
+            check(load().gmlp_bwd_dhidden(C.byref(prob), ptr(dy), ptr(w_down), ptr(g), ptr(u),
+                                          ptr(d_gate), ptr(d_up), stream_of(dy)))
+    return d_gate, d_up
+
+
+def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD):
+    """(d_gate, d_up) from a caller-supplied dH."""
+    dev = require_cuda(dh, g, u)
+    dt = _same_dtype(dh, g, u)
+    dh, g, u = _c(dh), _c(g), _c(u)
+    M, N = dh.shape
+    d_gate = torch.empty((M, N), dtype=dt, device=dev)
+    d_up = torch.empty((M, N), dtype=dt, device=dev)
+    if M > 0:
+        prob = _problem(M, 8, N, dt, drop, shard)
+        with torch.cuda.device(dev):
+            check(load().gmlp_bwd_dact(C.byref(prob), ptr(dh), ptr(g), ptr(u), ptr(d_gate), ptr(d_up),
+                                       stream_of(dh)))
+    return d_gate, d_up
+
+
+def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor) -> Tensor:
+    """dx = d_gate W_gate + d_up W_up."""
+    dev = require_cuda(d_gate, d_up, w_gate, w_up)
+    dt = _same_dtype(d_gate, d_up, w_gate, w_up)
+    d_gate, d_up, w_gate, w_up = _c(d_gate), _c(d_up), _c(w_gate), _c(w_up)
+    M, N = d_gate.shape
+    K = w_gate.shape[1]
+    dx = torch.empty((M, K), dtype=dt, device=dev)
+    if M > 0:
+        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+        with torch.cuda.device(dev):
+            check(load().gmlp_bwd_dx(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(w_gate), ptr(w_up),
+                                     ptr(dx), stream_of(d_gate)))
+    return dx
+
+
+def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor):
+    """(dW_gate, dW_up) = (d_gate^T x, d_up^T x)."""
+    dev = require_cuda(d_gate, d_up, x)
+    dt = _same_dtype(d_gate, d_up, x)
+    d_gate, d_up, x = _c(d_gate), _c(d_up), _c(x)
+    M, N = d_gate.shape
+    K = x.shape[1]
+    if M == 0:
+        return (torch.zeros((N, K), dtype=dt, device=dev), torch.zeros((N, K), dtype=dt, device=dev))
+    dw_gate = torch.empty((N, K), dtype=dt, device=dev)
+    dw_up = torch.empty((N, K), dtype=dt, device=dev)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    with torch.cuda.device(dev):
+        check(load().gmlp_bwd_dw_gate_up(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(x), ptr(dw_gate),
+                                         ptr(dw_up), stream_of(x)))
+    return dw_gate, dw_up
+
+
+def bwd_dw_down(dy: Tensor, h: Tensor) -> Tensor:
+    """dW_down = dy^T h."""
+    dev = require_cuda(dy, h)
+    dt = _same_dtype(dy, h)
+    dy, h = _c(dy), _c(h)
+    M, K = dy.shape
+    N = h.shape[1]
+    if M == 0:
+        return torch.zeros((K, N), dtype=dt, device=dev)
+    dw = torch.empty((K, N), dtype=dt, device=dev)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    with torch.cuda.device(dev):
+        check(load().gmlp_bwd_dw_down(C.byref(prob), ptr(dy), ptr(h), ptr(dw), stream_of(dy)))
+    return dw
+
+
+def colsum(src: Tensor) -> Tensor:
+    """Column sums of a [rows, cols] matrix (fp32 accumulation), in src's dtype."""
+    dev = require_cuda(src)
+    src = _c(src)
+    rows, cols = src.shape
+    if rows == 0:
+        return torch.zeros((cols,), dtype=src.dtype, device=dev)
+    lib = load()
+    nbytes = lib.gmlp_colsum_scratch_bytes(rows, cols)
+    scratch = torch.empty((nbytes // 4,), dtype=torch.float32, device=dev)
+    dst = torch.empty((cols,), dtype=src.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.gmlp_colsum(rows, cols, dtype_code(src.dtype), ptr(src), src.stride(0), ptr(scratch),
+                              nbytes, ptr(dst), stream_of(src)))
+    return dst
+
+
+def dropout_mask(M: int, N: int, drop: Dropout, shard: Shard = NO_SHARD,
+                 device: torch.device | str = "cuda") -> Tensor:
+    """uint8 keep-mask [M, N] of the Philox dropout contract, generated on the GPU."""
+    device = torch.device(device)
+    mask = torch.empty((M, N), dtype=torch.uint8, device=device)
+    prob = _problem(M, 8, N, torch.bfloat16, drop, shard)
+    with torch.cuda.device(device):
+        check(load().gmlp_dropout_mask(C.byref(prob), ptr(mask), torch.cuda.current_stream(device).cuda_stream))
+    return mask
+
+
+def gemm(a: Tensor, b: Tensor, a_mn: bool = False, b_mn: bool = False, bias: Tensor | None = None) -> Tensor:
+    """C = A B^T on the tcgen05 engine. a_mn: `a` is stored [K, M]; b_mn: `b` is stored [K, N]."""
+    dev = require_cuda(a, b, bias)
+    dt = _same_dtype(a, b, bias)
+    a, b, bias = _c(a), _c(b), _c(bias)
+    K, M = (a.shape if a_mn else a.shape[::-1])
+    Kb, N = (b.shape if b_mn else b.shape[::-1])
+    if K != Kb:
+        raise ValueError(f"reduction extents differ: {K} vs {Kb}")
+    c = torch.empty((M, N), dtype=dt, device=dev)
+    with torch.cuda.device(dev):
+        check(load().gmlp_gemm(dtype_code(dt), int(a_mn), int(b_mn), M, N, K, ptr(a), a.stride(0), ptr(b),
+                               b.stride(0), ptr(c), c.stride(0), ptr(bias), stream_of(a)))
+    return c
