@@ -34,7 +34,8 @@ CASES = [
 
 @pytest.mark.parametrize("M,K,N,bias,dtype,p", CASES)
 def test_forward_backward_parity(pkg, cuda_dev, M, K, N, bias, dtype, p):
-    case = orc.make_case(M, K, N, bias, dtype, seed=M + N, w_std=0.05, dy_std=0.5)
+    # weights ~ N(0, 1/(4K)) keep activations and outputs O(1), where the absolute tolerance is meaningful
+    case = orc.make_case(M, K, N, bias, dtype, seed=M + N, w_std=0.5 * K ** -0.5, dy_std=0.05)
     got, _ = _run(pkg, cuda_dev, case, dtype, p=p, seed=0x5EED, offset=2)
     want = orc.forward_backward(case, dropout_p=p, seed=0x5EED, offset=2)
     assert set(got) == set(want)

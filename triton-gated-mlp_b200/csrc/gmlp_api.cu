@@ -47,6 +47,11 @@ static int device_info(const DeviceInfo** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= 64) return fail(GMLP_ERR_ARG, "device index %d out of range", dev);
+  // Binds the device's primary context to the calling thread. Threads that never
+  // made a runtime call that needs a context (autograd's backward threads) have the
+  // right device selected but no driver context, which tensor-map encoding needs.
+  e = cudaSetDevice(dev);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaSetDevice: %s", cudaGetErrorString(e));
   std::lock_guard<std::mutex> lk(g_mu);
   DeviceInfo& d = g_dev[dev];
   if (!d.ready) {
