@@ -124,6 +124,12 @@ int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, i
               const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
               const void* bias, void* stream);
 
+/* Tuning / test hook with no counterpart in the reference: which GEMM kernel the
+ * calls above launch. 0 (default) = per problem, 1 = always the single-CTA kernel
+ * (128-row tiles), 2 = always the CTA-pair kernel (256-row tiles on two SMs,
+ * tcgen05 cta_group::2). Returns the previous mode; other values only query. */
+int gmlp_set_cta_pair_mode(int mode);
+
 /* Reads and clears the current device's status word (synchronises the device).
  * 0 = no kernel gave up a wait since the last read. */
 int gmlp_status_read(int* value);

@@ -155,6 +155,144 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
   return c;
 }
 
+// Epilogue of one 128-row accumulator tile, executed by one warp for its 32 TMEM
+// lanes: lane i owns output row `row` and walks the tile's columns in chunks of 32.
+// `taddr` addresses (lane quarter, first accumulator column of the tile).
+template <int BN, int EPI, typename T>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row,
+                                              int batch, int n0, T* out0, T* out1, T* out2,
+                                              const T* in0, const T* in1, const T* bias0,
+                                              const T* bias1, bool drop_on) {
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const bool row_ok = row < args.M;
+        if (EPI == EPI_STORE) {
+          T* const out = (batch ? out1 : out0) + static_cast<long long>(row) * args.ld_out;
+          const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
+  #pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= args.N) break;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            if (row_ok) {
+  #pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int gc = col + j * 8;
+                if (gc < args.N) {
+                  float v[8];
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j * 8 + i]);
+                  if (bias0) {
+                    float b[8];
+                    load8(bias0 + gc, b);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += b[i];
+                  }
+                  if (res) {
+                    float b[8];
+                    load8(res + gc, b);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += b[i];
+                  }
+                  store8(out + gc, v);
+                }
+              }
+            }
+          }
+        } else if (EPI == EPI_SWIGLU) {
+          const long long ro = static_cast<long long>(row) * args.ld_out;
+          const long long grow = args.drop.row0_global + row;
+  #pragma unroll 1
+          for (int c = 0; c < TILE_N / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= args.N) break;
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32(taddr + c * 32, rg);
+            tmem_ld_32x32(taddr + TILE_N + c * 32, ru);
+            tmem_ld_wait();
+            if (row_ok) {
+  #pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int gc = col + j * 8;
+                if (gc < args.N) {
+                  float g[8], u[8], h[8];
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    g[i] = __uint_as_float(rg[j * 8 + i]);
+                    u[i] = __uint_as_float(ru[j * 8 + i]);
+                  }
+                  if (bias0) {
+                    float b[8];
+                    load8(bias0 + gc, b);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) g[i] += b[i];
+                  }
+                  if (bias1) {
+                    float b[8];
+                    load8(bias1 + gc, b);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) u[i] += b[i];
+                  }
+                  if (out1) {  // keep the pre-activations for the backward pass
+                    store8(out1 + ro + gc, g);
+                    store8(out2 + ro + gc, u);
+                  }
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) h[i] = g[i] * sigmoid_f(g[i]) * u[i];
+                  if (drop_on) {
+                    float f[8];
+                    dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) h[i] *= f[i];
+                  }
+                  store8(out0 + ro + gc, h);
+                }
+              }
+            }
+          }
+        } else {  // EPI_DHIDDEN
+          const long long ro = static_cast<long long>(row) * args.ld_out;
+          const long long ri = static_cast<long long>(row) * args.ld_in;
+          const long long grow = args.drop.row0_global + row;
+  #pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            const int col = n0 + c * 32;
+            if (col >= args.N) break;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            if (row_ok) {
+  #pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int gc = col + j * 8;
+                if (gc < args.N) {
+                  float dh[8], g[8], u[8], dg[8], du[8];
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(r[j * 8 + i]);
+                  load8(in0 + ri + gc, g);
+                  load8(in1 + ri + gc, u);
+                  if (drop_on) {
+                    float f[8];
+                    dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+  #pragma unroll
+                    for (int i = 0; i < 8; ++i) dh[i] *= f[i];
+                  }
+  #pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float s = sigmoid_f(g[i]);
+                    du[i] = dh[i] * g[i] * s;
+                    dg[i] = dh[i] * u[i] * s * (1.0f + g[i] * (1.0f - s));
+                  }
+                  store8(out0 + ro + gc, dg);
+                  store8(out1 + ro + gc, du);
+                }
+              }
+            }
+          }
+        }
+}
+
 // ------------------------------------------------------------------ kernel --
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -340,135 +478,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + lane_addr;
       const int row = tc.m_tile * BM + row_in_tile;
-      const bool row_ok = row < args.M;
       const int n0 = tc.n_tile * TILE_N;
 
-      if (EPI == EPI_STORE) {
-        T* const out = (tc.batch ? out1 : out0) + static_cast<long long>(row) * args.ld_out;
-        const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= args.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int gc = col + j * 8;
-              if (gc < args.N) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j * 8 + i]);
-                if (bias0) {
-                  float b[8];
-                  load8(bias0 + gc, b);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] += b[i];
-                }
-                if (res) {
-                  float b[8];
-                  load8(res + gc, b);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] += b[i];
-                }
-                store8(out + gc, v);
-              }
-            }
-          }
-        }
-      } else if (EPI == EPI_SWIGLU) {
-        const long long ro = static_cast<long long>(row) * args.ld_out;
-        const long long grow = args.drop.row0_global + row;
-#pragma unroll 1
-        for (int c = 0; c < TILE_N / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= args.N) break;
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32(taddr + c * 32, rg);
-          tmem_ld_32x32(taddr + TILE_N + c * 32, ru);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int gc = col + j * 8;
-              if (gc < args.N) {
-                float g[8], u[8], h[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  g[i] = __uint_as_float(rg[j * 8 + i]);
-                  u[i] = __uint_as_float(ru[j * 8 + i]);
-                }
-                if (bias0) {
-                  float b[8];
-                  load8(bias0 + gc, b);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) g[i] += b[i];
-                }
-                if (bias1) {
-                  float b[8];
-                  load8(bias1 + gc, b);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) u[i] += b[i];
-                }
-                if (out1) {  // keep the pre-activations for the backward pass
-                  store8(out1 + ro + gc, g);
-                  store8(out2 + ro + gc, u);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) h[i] = g[i] * sigmoid_f(g[i]) * u[i];
-                if (drop_on) {
-                  float f[8];
-                  dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) h[i] *= f[i];
-                }
-                store8(out0 + ro + gc, h);
-              }
-            }
-          }
-        }
-      } else {  // EPI_DHIDDEN
-        const long long ro = static_cast<long long>(row) * args.ld_out;
-        const long long ri = static_cast<long long>(row) * args.ld_in;
-        const long long grow = args.drop.row0_global + row;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = n0 + c * 32;
-          if (col >= args.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (row_ok) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int gc = col + j * 8;
-              if (gc < args.N) {
-                float dh[8], g[8], u[8], dg[8], du[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(r[j * 8 + i]);
-                load8(in0 + ri + gc, g);
-                load8(in1 + ri + gc, u);
-                if (drop_on) {
-                  float f[8];
-                  dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) dh[i] *= f[i];
-                }
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float s = sigmoid_f(g[i]);
-                  du[i] = dh[i] * g[i] * s;
-                  dg[i] = dh[i] * u[i] * s * (1.0f + g[i] * (1.0f - s));
-                }
-                store8(out0 + ro + gc, dg);
-                store8(out1 + ro + gc, du);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<BN, EPI, T>(args, taddr, row, tc.batch, n0, out0, out1, out2, in0, in1, bias0, bias1,
+                                drop_on);
       // The accumulator has been read: hand it back to the MMA issuer.
       tc_fence_before_sync();
       __syncwarp();
@@ -486,6 +499,240 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+
+// ------------------------------------------------------- CTA-pair kernel ----
+// Same roles and pipeline as above, but two CTAs on neighbouring SMs (a cluster
+// of 2) work on one 256-row tile with tcgen05.mma.cta_group::2: each CTA stages
+// its own 128 rows of A and its own half of B's columns, so a CTA fetches
+// 128 x 64 of A plus (BN/2) x 64 of B per reduction block instead of 128 x 64 plus
+// BN x 64. That cuts the L2 -> shared-memory traffic per MMA by a third at BN = 256,
+// which is what bounds the single-CTA kernel. No TMA multicast is involved: every
+// byte of shared memory is written by the CTA that owns it.
+//
+// Protocol differences to the single-CTA kernel:
+//   full[s]    lives in the leader (cluster rank 0); both CTAs' loads count their
+//              bytes on it; the leader's producer arms it for 2 x the per-CTA bytes.
+//   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
+//              both copies at once.
+//   tempty[a]  lives in the leader, 8 arrivals: 4 epilogue warps of each CTA.
+template <int BN, int STAGES>
+constexpr size_t gemm_pair_smem_bytes() {
+  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + 1024;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
+                         const __grid_constant__ CUtensorMap tmA1,
+                         const __grid_constant__ CUtensorMap tmB0,
+                         const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tcgen05 N range for M = 256");
+  static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
+  static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
+  constexpr int HALF_N = BN / 2;  // B columns staged by each CTA
+  constexpr uint32_t A_BYTES = BM * 128;
+  constexpr uint32_t B_BYTES = HALF_N * 128;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = tmem_cols_for(BN);
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr int PAIR_M = 2 * BM;
+  constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, B_LBO = B_MN ? BK * 128 : 16;
+  constexpr uint32_t A_KSTEP = (A_MN ? 2048 : 32) >> 4, B_KSTEP = (B_MN ? 2048 : 32) >> 4;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int m_tiles = (args.M + PAIR_M - 1) / PAIR_M;
+  const int n_tiles = (args.N + TILE_N - 1) / TILE_N;
+  const int total_tiles = args.batches * m_tiles * n_tiles;
+  const int kb_total = args.kb0 + args.kb1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // 4 epilogue warps in each CTA of the pair
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA0);
+    tma_prefetch_desc(&tmB0);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_base_holder), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer --
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+        const int m0 = tc.m_tile * PAIR_M + static_cast<int>(rank) * BM;
+        const int n0 = tc.n_tile * TILE_N;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) {
+            ok = false;
+            break;
+          }
+          const int seg = kb >= args.kb0 ? 1 : 0;
+          const int k0 = (seg ? kb - args.kb0 : kb) * BK;
+          const CUtensorMap* ma = (seg | tc.batch) ? &tmA1 : &tmA0;
+          const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t fb = mapa_shared(full_bar(stage), 0);  // the leader's barrier
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          if (A_MN) {
+            tma_load_2d_pair(sa, ma, fb, m0, k0);
+            tma_load_2d_pair(sa + BK * 128, ma, fb, m0 + 64, k0);
+          } else {
+            tma_load_2d_pair(sa, ma, fb, k0, m0);
+          }
+          if (EPI == EPI_SWIGLU) {
+            // leader stages the gate rows, the peer the up rows of the same hidden columns
+            tma_load_2d_pair(sb, rank == 0 ? &tmB0 : &tmB1, fb, k0, n0);
+          } else if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < HALF_N / 64; ++j)
+              tma_load_2d_pair(sb + j * (BK * 128), mb, fb,
+                               n0 + static_cast<int>(rank) * HALF_N + 64 * j, k0);
+          } else {
+            tma_load_2d_pair(sb, mb, fb, k0, n0 + static_cast<int>(rank) * HALF_N);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_PRODUCER);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------- MMA issuer (leader only) --
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abortp)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
+          const uint64_t bdesc = make_smem_desc(sa + A_BYTES, B_LBO, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_f16_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                          bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
+                          (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(tfull_bar(acc));
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_MMA);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    T* const out0 = static_cast<T*>(args.out0);
+    T* const out1 = static_cast<T*>(args.out1);
+    T* const out2 = static_cast<T*>(args.out2);
+    const T* const in0 = static_cast<const T*>(args.in0);
+    const T* const in1 = static_cast<const T*>(args.in1);
+    const T* const bias0 = static_cast<const T*>(args.bias0);
+    const T* const bias1 = static_cast<const T*>(args.bias1);
+    const bool drop_on = args.drop.thresh != 0u;
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles; tile += num_pairs, ++local) {
+      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait(tfull_bar(acc), acc_phase, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + lane_addr;
+      const int row = tc.m_tile * PAIR_M + static_cast<int>(rank) * BM + row_in_tile;
+      const int n0 = tc.n_tile * TILE_N;
+      epilogue_tile<BN, EPI, T>(args, taddr, row, tc.batch, n0, out0, out1, out2, in0, in1, bias0,
+                                bias1, drop_on);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
+    }
+    if (!ok && lane == 0) {
+      abort_flag = 1;
+      atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+    }
+  }
+
+  // Neither CTA may exit (or free TMEM) while its peer can still read its shared
+  // memory, write its TMEM or arrive on its barriers.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 

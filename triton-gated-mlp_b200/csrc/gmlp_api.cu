@@ -140,13 +140,20 @@ struct Epilogue {
   DropoutParams drop = {};
 };
 
+// 0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA-pair kernel.
+static int g_pair_mode = 0;
+
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
 static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
                          const Operand& a0, const Operand* a1, const Operand& b0,
                          const Operand* b1, int64_t k1, int batches, const Epilogue& ep,
                          cudaStream_t stream) {
-  constexpr int STAGES = (BN > 128) ? 4 : 6;
-  constexpr uint32_t b_rows = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  // The CTA-pair kernel works on 256-row tiles; with a single row tile there is
+  // nothing for the second CTA to do.
+  const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && M > BM);
+  constexpr int STAGES = 4;
+  constexpr int PAIR_STAGES = 6;
+  const uint32_t b_rows = pair ? BN / 2 : ((EPI == EPI_SWIGLU) ? BN / 2 : BN);
   CUtensorMap mA0, mA1, mB0, mB1;
   int rc;
   if ((rc = encode_operand(&mA0, a0, BM, dtype))) return rc;
@@ -168,7 +175,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.kb0 = static_cast<int>((a0.k + BK - 1) / BK);
   args.kb1 = static_cast<int>((k1 + BK - 1) / BK);
   args.batches = batches;
-  args.idesc = make_idesc_f16(BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
+  args.idesc = make_idesc_f16(pair ? 2 * BM : BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
   args.status = dev->status_ptr;
   args.out0 = ep.out0;
   args.out1 = ep.out1;
@@ -182,22 +189,36 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.drop = ep.drop;
 
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-  const int64_t m_tiles = (M + BM - 1) / BM;
+  const int64_t tile_m = pair ? 2 * BM : BM;
+  const int64_t m_tiles = (M + tile_m - 1) / tile_m;
   const int64_t n_tiles = (N + TILE_N - 1) / TILE_N;
   const int64_t tiles = m_tiles * n_tiles * batches;
   if (tiles <= 0 || tiles > 0x7fffffffLL) return fail(GMLP_ERR_SHAPE, "tile count out of range");
-  // Raster groups: about sqrt(#SMs) row tiles per group keeps the set of
-  // concurrently running tiles close to square, which minimises distinct A and
-  // B tiles that L2 has to serve at the same time.
-  args.group_m = 16;
-  const int grid = static_cast<int>(tiles < dev->sm_count ? tiles : dev->sm_count);
-  constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
-  auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess)
-    return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+  // Raster groups: a group of row tiles sweeps all column tiles, so the tiles in
+  // flight at any time (one per SM or SM pair) share a small set of A and B tiles
+  // in L2. 2048 rows per group either way.
+  args.group_m = pair ? 8 : 16;
+  cudaError_t e;
+  if (pair) {
+    const int64_t max_pairs = dev->sm_count / 2;
+    const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    constexpr size_t smem = gemm_pair_smem_bytes<BN, PAIR_STAGES>();
+    auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES>;
+    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess)
+      return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+  } else {
+    const int grid = static_cast<int>(tiles < dev->sm_count ? tiles : dev->sm_count);
+    constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
+    auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
+    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    if (e != cudaSuccess)
+      return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
@@ -272,7 +293,13 @@ using namespace gmlp;
 
 extern "C" {
 
-int gmlp_version(void) { return 100; }
+int gmlp_version(void) { return 101; }
+
+int gmlp_set_cta_pair_mode(int mode) {
+  const int prev = g_pair_mode;
+  if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+  return prev;
+}
 
 const char* gmlp_last_error(void) { return g_err; }
 
