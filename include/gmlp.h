@@ -112,6 +112,23 @@ size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols);
 int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
                 void* scratch, size_t scratch_bytes, void* dst, void* stream);
 
+/* Skinny-M (decode) forward for M <= 64 tokens, K and N multiples of 64:
+ * h[M,N] = silu(x W_gate^T + b_gate) * (x W_up^T + b_up), then y[M,K] = h W_down^T +
+ * b_down, as two weight-streaming kernels (HBM-bound; every weight byte is read
+ * once). Covers the same reference interfaces as gmlp_hidden_fwd + gmlp_down_fwd
+ * (src/triton_gated_mlp/ops/fwd.py:198-279 and gated_mlp.py:236) for the token
+ * counts at which the reference's smallest tile (BLOCK_SIZE_M = 16, ops/fwd.py:49)
+ * already wastes the tensor pipe. dropout_p must be 0.
+ * `scratch`: gmlp_decode_scratch_bytes(p) bytes, 16-byte aligned. Its leading
+ * counter area (the first 64 KiB is more than enough) must be ZERO before the first
+ * call; every call leaves it zero again, so one memset at allocation suffices.
+ * Calls that share a scratch buffer must not overlap on the GPU. */
+size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p);
+int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
+                    const void* b_down, void* h, void* y, void* scratch, size_t scratch_bytes,
+                    void* stream);
+
 /* mask[M,N] (one byte per element, 1 = kept) for the problem's dropout settings:
  * the device side of the bit-exact mask check. */
 int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream);
@@ -129,6 +146,12 @@ int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, i
  * (128-row tiles), 2 = always the CTA-pair kernel (256-row tiles on two SMs,
  * tcgen05 cta_group::2). Returns the previous mode; other values only query. */
 int gmlp_set_cta_pair_mode(int mode);
+
+/* Tuning hook with no counterpart in the reference (the reference autotunes its
+ * GROUP_SIZE_M, src/triton_gated_mlp/ops/fwd.py:48-62): row tiles per raster
+ * group of the persistent tile order; 0 restores the built-in default. Returns
+ * the previous value; values outside [0, 4096] only query. */
+int gmlp_set_raster_group(int row_tiles);
 
 /* Reads and clears the current device's status word (synchronises the device).
  * 0 = no kernel gave up a wait since the last read. */

@@ -1,0 +1,60 @@
+"""Skinny-M (decode) forward: the weight-streaming kernels against the CPU oracle,
+including shapes whose row tiles are split across CTAs in every possible way."""
+import pytest
+import torch
+
+from oracle import gated_mlp_oracle as orc
+from _util import build_module
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("M", [1, 8, 32, 64])
+@pytest.mark.parametrize("K,N,bias", [
+    (512, 1024, False),     # fewer work units than SMs in the down projection
+    (1024, 3584, True),     # the 8-way tensor-parallel shard width of a 28672 intermediate
+    (2048, 7168, False),    # many split tiles in both kernels
+])
+def test_decode_matches_oracle(pkg, cuda_dev, M, K, N, bias):
+    case = orc.make_case(M, K, N, bias, torch.bfloat16, seed=M + K, w_std=0.5 * K ** -0.5)
+    m = build_module(pkg, case, torch.bfloat16, cuda_dev).eval()
+    with torch.no_grad():
+        y = m(case.x.to(cuda_dev))
+    assert m._decode_scratch is not None, "the decode path was not taken"
+    orc.assert_parity(y.float().cpu(), orc.forward_backward(case, grads=False)["y"], "y")
+
+
+def test_decode_equals_gemm_path_and_is_repeatable(pkg, cuda_dev):
+    """Same inputs through the tile-GEMM kernels (M padded into a 128-row tile) and the
+    streaming kernels; the streaming result must not depend on CTA arrival order."""
+    K_ = pkg.ops.kernels
+    case = orc.make_case(48, 1024, 4096, True, torch.bfloat16, seed=3, w_std=0.02)
+    t = [v.to(cuda_dev) if v is not None else None
+         for v in (case.x, case.w_gate, case.b_gate, case.w_up, case.b_up, case.w_down, case.b_down)]
+    y_gemm = K_.down_fwd(K_.hidden_fwd(t[0], t[1], t[2], t[3], t[4]), t[5], t[6])
+    scratch = K_.decode_scratch(48, 1024, 4096, torch.bfloat16, cuda_dev)
+    ys = [K_.decode_fwd(*t, scratch=scratch) for _ in range(5)]
+    assert all(torch.equal(ys[0], y) for y in ys[1:])
+    # counter area: one int per 128-row weight tile of each kernel, each block padded to 256 bytes
+    n_counters = (256 + 256) // 4
+    assert int(scratch[:n_counters].abs().sum()) == 0, "counters must be left at zero"
+    orc.assert_parity(ys[0].float().cpu(), y_gemm.float().cpu(), "decode vs gemm", max_abs=2e-2, mean_rel=1e-2)
+
+
+def test_decode_fp16_and_3d_input(pkg, cuda_dev):
+    case = orc.make_case(0, 256, 512, True, torch.float16, seed=9, lead_shape=(2, 5), w_std=0.03)
+    m = build_module(pkg, case, torch.float16, cuda_dev).eval()
+    with torch.no_grad():
+        y = m(case.x.to(cuda_dev))
+    assert y.shape == (2, 5, 256)
+    orc.assert_parity(y.float().cpu(), orc.forward_backward(case, grads=False)["y"], "y")
+
+
+def test_decode_rejects_what_it_cannot_do(pkg, cuda_dev):
+    K_ = pkg.ops.kernels
+    z = lambda *s: torch.zeros(s, dtype=torch.bfloat16, device=cuda_dev)
+    with pytest.raises(ValueError):
+        K_.decode_fwd(z(65, 128), z(256, 128), None, z(256, 128), None, z(128, 256), None)
+    with pytest.raises(pkg._lib.GmlpError, match="scratch"):
+        K_.decode_fwd(z(4, 128), z(256, 128), None, z(256, 128), None, z(128, 256), None,
+                      scratch=torch.zeros(64, dtype=torch.int32, device=cuda_dev))

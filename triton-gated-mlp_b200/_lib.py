@@ -18,7 +18,7 @@ GMLP_BF16, GMLP_FP16 = 0, 1
 EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum",
-    "gmlp_dropout_mask", "gmlp_gemm", "gmlp_set_cta_pair_mode",
+    "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group",
     "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
 
@@ -56,7 +56,11 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_colsum.argtypes = [i64, i64, i32, vp, i64, vp, C.c_size_t, vp, vp]
     lib.gmlp_dropout_mask.argtypes = [pp, u8p, vp]
     lib.gmlp_gemm.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp]
+    lib.gmlp_decode_scratch_bytes.argtypes = [pp]
+    lib.gmlp_decode_scratch_bytes.restype = C.c_size_t
+    lib.gmlp_decode_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_set_cta_pair_mode.argtypes = [i32]
+    lib.gmlp_set_raster_group.argtypes = [i32]
     lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]
     lib.gmlp_last_error.restype = C.c_char_p
     lib.gmlp_version.restype = C.c_int
@@ -128,3 +132,8 @@ def status_read(device: torch.device | None = None) -> int:
 def set_cta_pair_mode(mode: int) -> int:
     """0 = per problem, 1 = single-CTA kernel only, 2 = CTA-pair kernel only; returns the previous mode."""
     return load().gmlp_set_cta_pair_mode(int(mode))
+
+
+def set_raster_group(row_tiles: int) -> int:
+    """Row tiles per raster group of the persistent tile order (0 = default); returns the previous value."""
+    return load().gmlp_set_raster_group(int(row_tiles))

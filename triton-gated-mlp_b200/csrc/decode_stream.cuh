@@ -1,0 +1,341 @@
+// Skinny-M (decode) forward: M <= 64 tokens, so the cost is one pass over the
+// weights and the kernels are judged on HBM bandwidth, not tensor throughput.
+//
+// Layout of the work ("swap-AB"): the 128 TMEM lanes / MMA rows are 128 WEIGHT rows
+// and the (padded) token count MPAD in {16, 32, 64} is the MMA N dimension, so a
+// 16 KB weight tile [128 x 64] is used once by one small tcgen05.mma group and
+// the tensor pipe stays far below its limit while TMA streams the weights.
+//
+// Balance ("stream-K"): the work is the list of (weight row tile, 64-wide
+// reduction block) units in row-tile-major order. CTA c of G takes the
+// contiguous unit range [c*U/G, (c+1)*U/G): every CTA streams the same number of
+// weight bytes (to within one unit) whatever the tile count is. A row tile whose
+// reduction is split across CTAs is finished by whichever contributor arrives
+// last: each contributor stores its fp32 partial tile to its own scratch slot,
+// bumps the tile's counter, and the one that completes the count sums all slots in
+// CTA order (so the result does not depend on arrival order), applies the
+// epilogue, and resets the counter. There is no spin-wait anywhere in this
+// scheme.
+//
+//   DUAL = true   H^T[n, m]  = silu(Wg[n,:].x[m,:] + bg[n]) * (Wu[n,:].x[m,:] + bu[n])
+//                 two accumulators (gate, up) per tile, written as H[m, n]
+//   DUAL = false  Y^T[k, m]  = Wd[k,:].h[m,:] + bd[k], written as Y[m, k]
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace gmlp {
+
+struct DecodeArgs {
+  int M;          // tokens (<= MPAD)
+  int rows;       // weight rows: N for DUAL, K (hidden) otherwise
+  int kbt;        // 64-wide reduction blocks per row tile
+  uint32_t idesc;
+  int* status;
+  const void* bias0;  // per weight row (gate bias, or down bias)
+  const void* bias1;  // up bias (DUAL)
+  void* out;          // H[M, rows] or Y[M, rows]
+  long long ld_out;
+  float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
+  int* counters;      // [row tiles], zero on entry and on exit
+};
+
+constexpr int DECODE_THREADS = 192;
+
+template <int MPAD, bool DUAL>
+__host__ __device__ constexpr int decode_stages() {
+  return DUAL ? 5 : 8;
+}
+template <int MPAD, bool DUAL>
+constexpr size_t decode_smem_bytes() {
+  return static_cast<size_t>(decode_stages<MPAD, DUAL>()) * ((DUAL ? 2 : 1) * 16384 + MPAD * 128) +
+         1024;
+}
+
+__device__ __forceinline__ long long unit_start(long long c, long long total, long long g) {
+  return (c * total) / g;
+}
+
+template <int MPAD, bool DUAL, typename T>
+__global__ void __launch_bounds__(DECODE_THREADS, 1)
+decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
+                     const __grid_constant__ CUtensorMap tmW1,
+                     const __grid_constant__ CUtensorMap tmAct, const DecodeArgs args) {
+  static_assert(MPAD == 16 || MPAD == 32 || MPAD == 64, "token padding");
+  constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int STAGES = decode_stages<MPAD, DUAL>();
+  constexpr uint32_t W_BYTES = 128 * 128;  // one [128 x 64] 16-bit weight tile
+  constexpr uint32_t ACT_BYTES = MPAD * 128;
+  constexpr uint32_t STAGE_BYTES = NACC * W_BYTES + ACT_BYTES;
+  constexpr uint32_t ACC_COLS = NACC * MPAD;  // TMEM columns per accumulator buffer
+  constexpr uint32_t TMEM_COLS = (2 * ACC_COLS <= 32) ? 32 : (2 * ACC_COLS <= 64) ? 64
+                                 : (2 * ACC_COLS <= 128) ? 128 : 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+  __shared__ int last_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long row_tiles = (args.rows + 127) / 128;
+  const long long total = row_tiles * args.kbt;
+  const long long u_begin = unit_start(blockIdx.x, total, gridDim.x);
+  const long long u_end = unit_start(blockIdx.x + 1, total, gridDim.x);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmW0);
+    tma_prefetch_desc(&tmAct);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------- TMA producer --
+    if (lane == 0) {
+      // Weights are read exactly once: mark them evict-first so they do not push
+      // the (re-used) activations out of L2.
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_a = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end; ++u) {
+        const int tile = static_cast<int>(u / args.kbt);
+        const int kb = static_cast<int>(u - static_cast<long long>(tile) * args.kbt);
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sw = smem_base + stage * STAGE_BYTES;
+        const uint32_t fb = full_bar(stage);
+        mbar_expect_tx(fb, STAGE_BYTES);
+        tma_load_2d_hint(sw, &tmW0, fb, kb * BK, tile * 128, pol_w);
+        if (DUAL) tma_load_2d_hint(sw + W_BYTES, &tmW1, fb, kb * BK, tile * 128, pol_w);
+        tma_load_2d_hint(sw + NACC * W_BYTES, &tmAct, fb, kb * BK, 0, pol_a);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_PRODUCER);
+      }
+    }
+  } else if (warp == 1) {
+    // --------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int seg = 0;
+      bool ok = true;
+      long long u = u_begin;
+      while (u < u_end && ok) {
+        const long long tile = u / args.kbt;
+        const long long tile_end = (tile + 1) * args.kbt;
+        const long long seg_end = tile_end < u_end ? tile_end : u_end;
+        const int acc = seg & 1;
+        const uint32_t acc_phase = (seg >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abortp)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        bool first = true;
+        for (; u < seg_end; ++u) {
+          if (!mbar_wait(full_bar(stage), phase, abortp)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sw = smem_base + stage * STAGE_BYTES;
+          const uint64_t w0desc = make_smem_desc(sw, 16, 1024);
+          const uint64_t w1desc = make_smem_desc(sw + W_BYTES, 16, 1024);
+          const uint64_t xdesc = make_smem_desc(sw + NACC * W_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t accum = (first && k == 0) ? 0u : 1u;
+            umma_f16(d_tmem, w0desc + static_cast<uint64_t>(2 * k),
+                     xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+            if (DUAL)
+              umma_f16(d_tmem + MPAD, w1desc + static_cast<uint64_t>(2 * k),
+                       xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+          }
+          first = false;
+          umma_commit(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(tfull_bar(acc));
+        ++seg;
+      }
+      if (!ok) {
+        abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_MMA);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;
+    const int r_in_tile = quarter * 32 + lane;  // weight row inside the tile = TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int ep_tid = threadIdx.x - 64;  // 0..127 among the epilogue warps
+    T* const out = static_cast<T*>(args.out);
+    const T* const bias0 = static_cast<const T*>(args.bias0);
+    const T* const bias1 = static_cast<const T*>(args.bias1);
+    constexpr long long SLOT_FLOATS = static_cast<long long>(NACC) * 128 * MPAD;
+    int seg = 0;
+    bool ok = true;
+    long long u = u_begin;
+    while (u < u_end) {
+      const long long tile = u / args.kbt;
+      const long long tile_begin = tile * args.kbt;
+      const long long tile_end = tile_begin + args.kbt;
+      const long long seg_end = tile_end < u_end ? tile_end : u_end;
+      const bool complete = (u == tile_begin) && (seg_end == tile_end);
+      const int acc = seg & 1;
+      const uint32_t acc_phase = (seg >> 1) & 1;
+      ok = mbar_wait(tfull_bar(acc), acc_phase, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && lane == 0) {
+        abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+      }
+      // The four epilogue warps meet at named barriers further down; they must all
+      // take the same way out, so they agree on the outcome of the wait first. Every
+      // warp reaches this barrier because its wait above is bounded.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abortp != 0) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + lane_addr;
+      float v[NACC][MPAD];
+#pragma unroll
+      for (int a = 0; a < NACC; ++a) {
+#pragma unroll
+        for (int c = 0; c < MPAD / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld_32x16(taddr + a * MPAD + c * 16, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[a][c * 16 + i] = __uint_as_float(r[i]);
+        }
+      }
+      // TMEM has been read into registers: the MMA issuer may reuse the buffer.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+
+      bool finish = complete;
+      if (!complete) {
+        // Store this CTA's partial tile to its own slot, then count it.
+        const int which = (u == u_begin) ? 0 : 1;
+        float* slot = args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS;
+#pragma unroll
+        for (int a = 0; a < NACC; ++a) {
+          float4* dst = reinterpret_cast<float4*>(slot + (static_cast<long long>(a) * 128 + r_in_tile) * MPAD);
+#pragma unroll
+          for (int i = 0; i < MPAD / 4; ++i)
+            dst[i] = make_float4(v[a][4 * i], v[a][4 * i + 1], v[a][4 * i + 2], v[a][4 * i + 3]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+        if (ep_tid == 0) {
+          const int nkb = static_cast<int>(seg_end - u);
+          const int old = atomicAdd(args.counters + tile, nkb);
+          last_flag = (old + nkb == args.kbt) ? 1 : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finish = last_flag != 0;
+        if (finish) {
+          __threadfence();
+          // Sum every contributor's slot in CTA order (deterministic).
+          const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
+          const long long c_last = (tile_end * gridDim.x - 1) / total;
+#pragma unroll
+          for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int i = 0; i < MPAD; ++i) v[a][i] = 0.f;
+          for (long long c = c_first; c <= c_last; ++c) {
+            const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
+            const float* src = args.slots + (2LL * c + w) * SLOT_FLOATS;
+#pragma unroll
+            for (int a = 0; a < NACC; ++a) {
+              const float4* s4 = reinterpret_cast<const float4*>(
+                  src + (static_cast<long long>(a) * 128 + r_in_tile) * MPAD);
+#pragma unroll
+              for (int i = 0; i < MPAD / 4; ++i) {
+                const float4 q = __ldcg(s4 + i);
+                v[a][4 * i] += q.x;
+                v[a][4 * i + 1] += q.y;
+                v[a][4 * i + 2] += q.z;
+                v[a][4 * i + 3] += q.w;
+              }
+            }
+          }
+          if (ep_tid == 0) args.counters[tile] = 0;  // leave the scratch ready for the next call
+        }
+      }
+      if (finish) {
+        const long long wrow = tile * 128 + r_in_tile;
+        if (wrow < args.rows) {
+          const float b0 = bias0 ? static_cast<float>(bias0[wrow]) : 0.f;
+          const float b1 = (DUAL && bias1) ? static_cast<float>(bias1[wrow]) : 0.f;
+#pragma unroll
+          for (int m = 0; m < MPAD; ++m) {
+            if (m < args.M) {
+              float o;
+              if (DUAL) {
+                const float g = v[0][m] + b0;
+                o = g * sigmoid_f(g) * (v[NACC - 1][m] + b1);
+              } else {
+                o = v[0][m] + b0;
+              }
+              out[static_cast<long long>(m) * args.ld_out + wrow] = static_cast<T>(o);
+            }
+          }
+        }
+      }
+      u = seg_end;
+      ++seg;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gmlp

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/gmlp.h"
+#include "decode_stream.cuh"
 #include "elementwise.cuh"
 #include "gemm_tcgen05.cuh"
 
@@ -142,6 +143,8 @@ struct Epilogue {
 
 // 0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA-pair kernel.
 static int g_pair_mode = 0;
+// Row tiles per raster group; 0 = the built-in default.
+static int g_group_m = 0;
 
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
 static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
@@ -197,7 +200,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // Raster groups: a group of row tiles sweeps all column tiles, so the tiles in
   // flight at any time (one per SM or SM pair) share a small set of A and B tiles
   // in L2. 2048 rows per group either way.
-  args.group_m = pair ? 8 : 16;
+  args.group_m = g_group_m > 0 ? g_group_m : (pair ? 8 : 16);
   cudaError_t e;
   if (pair) {
     const int64_t max_pairs = dev->sm_count / 2;
@@ -298,6 +301,12 @@ int gmlp_version(void) { return 101; }
 int gmlp_set_cta_pair_mode(int mode) {
   const int prev = g_pair_mode;
   if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+  return prev;
+}
+
+int gmlp_set_raster_group(int row_tiles) {
+  const int prev = g_group_m;
+  if (row_tiles >= 0 && row_tiles <= 4096) g_group_m = row_tiles;
   return prev;
 }
 
@@ -551,6 +560,120 @@ int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int6
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ decode --
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct DecodeLayout {
+  int mpad;
+  size_t counters1_off, counters2_off, slots_off, total;
+};
+static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
+  DecodeLayout l;
+  l.mpad = p->M <= 16 ? 16 : (p->M <= 32 ? 32 : 64);
+  const size_t t1 = static_cast<size_t>((p->N + 127) / 128), t2 = static_cast<size_t>((p->K + 127) / 128);
+  l.counters1_off = 0;
+  l.counters2_off = align_up(t1 * sizeof(int), 256);
+  l.slots_off = l.counters2_off + align_up(t2 * sizeof(int), 256);
+  l.total = l.slots_off + 2ull * ctas * 2ull * 128ull * l.mpad * sizeof(float);
+  return l;
+}
+
+template <int MPAD, bool DUAL, typename T>
+static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
+                           const void* w0, const void* w1, const void* act, int64_t act_ld,
+                           const void* bias0, const void* bias1, void* out, int64_t ld_out,
+                           float* slots, int* counters, cudaStream_t stream) {
+  CUtensorMap mW0, mW1, mAct;
+  int rc;
+  if ((rc = encode_map(&mW0, w0, red, rows, red, BK, 128, dtype))) return rc;
+  if (DUAL) {
+    if ((rc = encode_map(&mW1, w1, red, rows, red, BK, 128, dtype))) return rc;
+  } else {
+    mW1 = mW0;
+  }
+  if ((rc = encode_map(&mAct, act, red, M, act_ld, BK, MPAD, dtype))) return rc;
+  DecodeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M;
+  a.rows = static_cast<int>(rows);
+  a.kbt = static_cast<int>((red + BK - 1) / BK);
+  a.idesc = make_idesc_f16(128, MPAD, dtype == GMLP_BF16 ? 1 : 0, false, false);
+  a.status = dev->status_ptr;
+  a.bias0 = bias0;
+  a.bias1 = bias1;
+  a.out = out;
+  a.ld_out = ld_out;
+  a.slots = slots;
+  a.counters = counters;
+  const long long total = ((rows + 127) / 128) * static_cast<long long>(a.kbt);
+  const int grid = static_cast<int>(total < dev->sm_count ? total : dev->sm_count);
+  constexpr size_t smem = decode_smem_bytes<MPAD, DUAL>();
+  auto kfn = decode_stream_kernel<MPAD, DUAL, T>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  kfn<<<grid, DECODE_THREADS, smem, stream>>>(mW0, mW1, mAct, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+template <bool DUAL, typename... Args>
+static int launch_decode(int mpad, int dtype, Args... args) {
+  const bool bf = dtype == GMLP_BF16;
+  if (mpad == 16)
+    return bf ? launch_decode_t<16, DUAL, __nv_bfloat16>(args...) : launch_decode_t<16, DUAL, __half>(args...);
+  if (mpad == 32)
+    return bf ? launch_decode_t<32, DUAL, __nv_bfloat16>(args...) : launch_decode_t<32, DUAL, __half>(args...);
+  return bf ? launch_decode_t<64, DUAL, __nv_bfloat16>(args...) : launch_decode_t<64, DUAL, __half>(args...);
+}
+
+extern "C" {
+
+size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p) {
+  if (!p || p->M <= 0 || p->M > 64 || p->K <= 0 || p->N <= 0) return 0;
+  const DeviceInfo* dev;
+  int ctas = 256;  // without a device: an upper bound on the SM count
+  if (device_info(&dev) == GMLP_OK) ctas = dev->sm_count;
+  return decode_layout(p, ctas).total;
+}
+
+int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
+                    const void* b_down, void* h, void* y, void* scratch, size_t scratch_bytes,
+                    void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if (p->M > 64) return fail(GMLP_ERR_SHAPE, "decode path takes at most 64 tokens, got %lld",
+                             static_cast<long long>(p->M));
+  if (p->dropout_p != 0.0f) return fail(GMLP_ERR_ARG, "decode path is inference only: dropout_p must be 0");
+  if ((rc = check_ptrs({x, w_gate, w_up, w_down, h, y, scratch}))) return rc;
+  if ((p->K % 64) != 0 || (p->N % 64) != 0)
+    return fail(GMLP_ERR_SHAPE, "decode path needs K and N multiples of 64");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const DecodeLayout l = decode_layout(p, dev->sm_count);
+  if (scratch_bytes < l.total)
+    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes, l.total);
+  char* sc = static_cast<char*>(scratch);
+  float* slots = reinterpret_cast<float*>(sc + l.slots_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = static_cast<int>(p->M);
+  // H[M,N] = silu(x Wg^T + bg) * (x Wu^T + bu): weight rows = N, reduction = K
+  rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
+                           b_gate, b_up, h, p->N, slots,
+                           reinterpret_cast<int*>(sc + l.counters1_off), st);
+  if (rc) return rc;
+  // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
+  return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
+                              static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
+                              static_cast<const void*>(nullptr), y, p->K, slots,
+                              reinterpret_cast<int*>(sc + l.counters2_off), st);
 }
 
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,

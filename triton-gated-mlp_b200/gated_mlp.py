@@ -136,6 +136,7 @@ class FusedGatedMLP(nn.Module):
         self.token_row0 = 0
         self.philox_seed = int(philox_seed)
         self.philox_offset = 0
+        self._decode_scratch = None
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -148,6 +149,20 @@ class FusedGatedMLP(nn.Module):
             return Shard(row0=int(self.token_row0), col0=0, n_global=self.intermediate_size)
         return Shard()
 
+    def _decode_forward(self, x: Tensor, tp_group) -> Tensor:
+        """Inference with at most 64 tokens: the weight-streaming kernels (HBM-bound)."""
+        key = (x.device, x.dtype)
+        if self._decode_scratch is None or self._decode_scratch[0] != key:
+            self._decode_scratch = (key, kernels.decode_scratch(
+                x.shape[0], self.hidden_size, self.intermediate_size, x.dtype, x.device))
+        own_bias = tp_group is None or self.tp_rank == 0
+        y = kernels.decode_fwd(x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight,
+                               self.up_proj.bias, self.down_proj.weight,
+                               self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1])
+        if tp_group is not None:
+            parallel.all_reduce_sum(y, tp_group)
+        return y
+
     def forward(self, x: Tensor) -> Tensor:
         shapes = x.shape
         if len(shapes) > 2:
@@ -159,6 +174,12 @@ class FusedGatedMLP(nn.Module):
         tp_group = self.process_group if self.parallel_mode == "tp" else None
         if self.parallel_mode == "tp" and tp_group is None:
             tp_group = parallel.default_group()
+        needs_grad = torch.is_grad_enabled() and (
+            x.requires_grad or any(q.requires_grad for q in self.parameters()))
+        if (not needs_grad and p == 0.0 and x.is_cuda
+                and kernels.decode_supported(x.shape[0], self.hidden_size, self.intermediate_size)):
+            y = self._decode_forward(x, tp_group)
+            return y.view(shapes) if len(shapes) > 2 else y
         y = FusedGatedMLPFunction.apply(
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
             self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group,

@@ -183,6 +183,49 @@ def bwd_dw_down(dy: Tensor, h: Tensor) -> Tensor:
     return dw
 
 
+DECODE_MAX_TOKENS = 64
+
+
+def decode_supported(M: int, K: int, N: int) -> bool:
+    """Shapes the weight-streaming decode kernels accept."""
+    return 0 < M <= DECODE_MAX_TOKENS and K % 64 == 0 and N % 64 == 0
+
+
+def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device) -> Tensor:
+    """Zero-initialised scratch for decode_fwd (partial-tile slots + per-tile counters).
+
+    Sized for up to 64 tokens, so one buffer serves every decode call of a module.
+    The kernels leave the counters zero, so the buffer is reusable without clearing.
+    """
+    prob = _problem(DECODE_MAX_TOKENS, K, N, dt, NO_DROPOUT, NO_SHARD)
+    with torch.cuda.device(device):
+        nbytes = load().gmlp_decode_scratch_bytes(C.byref(prob))
+    return torch.zeros(((nbytes + 3) // 4,), dtype=torch.int32, device=device)
+
+
+def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
+               w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None) -> Tensor:
+    """y = (silu(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down for M <= 64 tokens."""
+    dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down)
+    dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down)
+    x, w_gate, w_up, w_down = _c(x), _c(w_gate), _c(w_up), _c(w_down)
+    b_gate, b_up, b_down = _c(b_gate), _c(b_up), _c(b_down)
+    M, K = x.shape
+    N = w_gate.shape[0]
+    if not decode_supported(M, K, N):
+        raise ValueError(f"decode path needs 1 <= M <= 64 and K, N multiples of 64; got M={M} K={K} N={N}")
+    if scratch is None:
+        scratch = decode_scratch(M, K, N, dt, dev)
+    h = torch.empty((M, N), dtype=dt, device=dev)
+    y = torch.empty((M, K), dtype=dt, device=dev)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    with torch.cuda.device(dev):
+        check(load().gmlp_decode_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),
+                                     ptr(w_down), ptr(b_down), ptr(h), ptr(y), ptr(scratch),
+                                     scratch.numel() * scratch.element_size(), stream_of(x)))
+    return y
+
+
 def colsum(src: Tensor) -> Tensor:
     """Column sums of a [rows, cols] matrix (fp32 accumulation), in src's dtype."""
     dev = require_cuda(src)
