@@ -40,8 +40,8 @@ WORKLOADS = {
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes (read + write) of one launch of the gate/up kernel at the default workload,
-# from the ncu capture summarised in profiles/ (None until a capture exists).
-K1_DRAM_TRAFFIC_BYTES = None
+# from the ncu capture summarised in profiles/gateup_pair_kernel_llama8b_fwd.md.
+K1_DRAM_TRAFFIC_BYTES = 1.272e9
 
 
 def flops_per_step(w) -> float:
@@ -319,9 +319,10 @@ def run_gpu(args, w, name):
             k1_flops = 4.0 * M * K * N
             ach = k1_flops / (k1_ms * 1e-3) / 1e12
             line["roofline"] = {
-                "kernel": "gemm_tcgen05_kernel<EPI_SWIGLU> (gate/up GEMM + SiLU*up epilogue)", "bound": "tensor",
+                "kernel": "gemm_tcgen05_pair_kernel<256, K-major, K-major, EPI_SWIGLU> (gate/up GEMM + SiLU*up epilogue)", "bound": "tensor",
                 "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": peak_src,
-                "frac_of_nominal": ach / NOMINAL_BF16_TFLOPS, "traffic": K1_DRAM_TRAFFIC_BYTES,
+                "frac_of_nominal": ach / NOMINAL_BF16_TFLOPS,
+                "traffic": K1_DRAM_TRAFFIC_BYTES if name == "llama3-8b-mlp-fwd-bf16" else None,
                 "ms_per_launch": k1_ms, "algorithmic_flops_per_launch": k1_flops,
             }
         else:

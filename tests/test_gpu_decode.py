@@ -21,7 +21,7 @@ def test_decode_matches_oracle(pkg, cuda_dev, M, K, N, bias):
     with torch.no_grad():
         y = m(case.x.to(cuda_dev))
     assert m._decode_scratch is not None, "the decode path was not taken"
-    orc.assert_parity(y.float().cpu(), orc.forward_backward(case, grads=False)["y"], "y")
+    orc.assert_parity(y.cpu(), orc.forward_backward(case, grads=False)["y"], "y")
 
 
 def test_decode_equals_gemm_path_and_is_repeatable(pkg, cuda_dev):
@@ -38,7 +38,7 @@ def test_decode_equals_gemm_path_and_is_repeatable(pkg, cuda_dev):
     # counter area: one int per 128-row weight tile of each kernel, each block padded to 256 bytes
     n_counters = (256 + 256) // 4
     assert int(scratch[:n_counters].abs().sum()) == 0, "counters must be left at zero"
-    orc.assert_parity(ys[0].float().cpu(), y_gemm.float().cpu(), "decode vs gemm", max_abs=2e-2, mean_rel=1e-2)
+    orc.assert_parity(ys[0].cpu(), y_gemm.float().cpu(), "decode vs gemm", max_abs=2e-2, mean_rel=1e-2)
 
 
 def test_decode_fp16_and_3d_input(pkg, cuda_dev):
@@ -47,7 +47,7 @@ def test_decode_fp16_and_3d_input(pkg, cuda_dev):
     with torch.no_grad():
         y = m(case.x.to(cuda_dev))
     assert y.shape == (2, 5, 256)
-    orc.assert_parity(y.float().cpu(), orc.forward_backward(case, grads=False)["y"], "y")
+    orc.assert_parity(y.cpu(), orc.forward_backward(case, grads=False)["y"], "y")
 
 
 def test_decode_rejects_what_it_cannot_do(pkg, cuda_dev):

@@ -22,10 +22,10 @@ def test_module_matches_reference_outputs(pkg, cuda_dev, name):
     y = m(x)
     y.backward(t["dy"].to(cuda_dev))
     assert y.shape == t["y"].shape and y.dtype == dt
-    orc.assert_parity(y.float().cpu(), t["y"], "y")
-    orc.assert_parity(x.grad.float().cpu(), t["dx"], "dx")
+    orc.assert_parity(y.cpu(), t["y"], "y")
+    orc.assert_parity(x.grad.cpu(), t["dx"], "dx")
     for pname, prm in m.named_parameters():
-        orc.assert_parity(prm.grad.float().cpu(), t["d" + pname], "d" + pname)
+        orc.assert_parity(prm.grad.cpu(), t["d" + pname], "d" + pname)
 
 
 def test_ops_match_reference_closed_form(pkg, cuda_dev):

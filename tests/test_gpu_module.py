@@ -18,7 +18,7 @@ def _run(pkg, dev, case, dtype, p=0.0, seed=0, offset=0, train=True):
     y.backward(case.dy.to(dev))
     got = {"y": y, "dx": x.grad}
     got.update({"d" + n: q.grad for n, q in m.named_parameters()})
-    return {k: v.float().cpu() for k, v in got.items()}, m
+    return {k: v.cpu() for k, v in got.items()}, m
 
 
 CASES = [
@@ -56,7 +56,7 @@ def test_three_dimensional_input_and_no_grad(pkg, cuda_dev):
     with torch.no_grad():
         y = m(case.x.to(cuda_dev))
     assert y.shape == (16, 32, 256)
-    orc.assert_parity(y.float().cpu(), orc.forward_backward(case, grads=False)["y"], "y")
+    orc.assert_parity(y.cpu(), orc.forward_backward(case, grads=False)["y"], "y")
 
 
 def test_autograd_grad_subset_like_reference_test(pkg, cuda_dev):
@@ -68,9 +68,9 @@ def test_autograd_grad_subset_like_reference_test(pkg, cuda_dev):
     gx, gu, gg = torch.autograd.grad(out, (x, m.up_proj.weight, m.gate_proj.weight),
                                      grad_outputs=case.dy.to(cuda_dev))
     want = orc.forward_backward(case)
-    orc.assert_parity(gx.float().cpu(), want["dx"], "dx")
-    orc.assert_parity(gu.float().cpu(), want["dup_proj.weight"], "dW_up")
-    orc.assert_parity(gg.float().cpu(), want["dgate_proj.weight"], "dW_gate")
+    orc.assert_parity(gx.cpu(), want["dx"], "dx")
+    orc.assert_parity(gu.cpu(), want["dup_proj.weight"], "dW_up")
+    orc.assert_parity(gg.cpu(), want["dgate_proj.weight"], "dW_gate")
     assert m.down_proj.weight.grad is None
 
 

@@ -52,3 +52,9 @@ def test_parity_metric():
     assert orc.parity_errors(want + 0.01, want) == pytest.approx((0.01, 0.01), rel=1e-4)
     with pytest.raises(AssertionError):
         orc.assert_parity(want + 0.05, want, "t")
+    # outputs with rms > 1: output rounding is not counted, the rest is measured in units of the rms
+    big = torch.full((4,), 16.0)
+    assert orc.parity_errors(big + 0.32, big) == pytest.approx((0.02, 0.02), rel=1e-4)
+    orc.assert_parity((big + 0.125).to(torch.bfloat16), big, "next bf16 above 16")
+    with pytest.raises(AssertionError):
+        orc.assert_parity(big + 0.5, big, "too far")
