@@ -112,6 +112,27 @@ size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols);
 int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
                 void* scratch, size_t scratch_bytes, void* dst, void* stream);
 
+/* gmlp_colsum for callers that cannot hand over scratch memory. It has no counterpart
+ * in the reference. Same result as gmlp_colsum, but the fp32 partial sums go to a 1 MiB
+ * array inside the library image (every GPU that loads the library holds that 1 MiB
+ * until the process exits), and the call makes no cudaMalloc / cudaFree or any other
+ * allocating call. It is meant for hosts that bind this ABI from a runtime which gave
+ * all device memory to its own pool at start-up (so there is nothing left to allocate
+ * from and no torch allocator to ask), or which must not trigger the device-wide
+ * synchronisation an allocation implies in the middle of a latency-critical loop.
+ *   - Limit: gmlp_colsum_scratch_bytes(rows, cols) <= 1 MiB, which holds for every
+ *     cols <= 262144 at any row count. Wider matrices are refused with
+ *     GMLP_ERR_SCRATCH and a message; use gmlp_colsum for them.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) with that device current; make that first call before
+ *     starting any stream capture.
+ *   - All calls on a device share the one array. It keeps whatever the last call left
+ *     there, which is harmless (the first pass overwrites every value the second pass
+ *     reads), but two calls that overlap on the GPU (different streams) race on it:
+ *     serialise them. */
+int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                       void* dst, void* stream);
+
 /* Skinny-M (decode) forward for M <= 64 tokens, K and N multiples of 64:
  * h[M,N] = silu(x W_gate^T + b_gate) * (x W_up^T + b_up), then y[M,K] = h W_down^T +
  * b_down, as two weight-streaming kernels (HBM-bound; every weight byte is read

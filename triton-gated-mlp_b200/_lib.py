@@ -17,7 +17,7 @@ GMLP_BF16, GMLP_FP16 = 0, 1
 # Every symbol include/gmlp.h declares; tests check that the library exports all of them.
 EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
-    "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum",
+    "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group",
     "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
@@ -54,6 +54,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_colsum_scratch_bytes.argtypes = [i64, i64]
     lib.gmlp_colsum_scratch_bytes.restype = C.c_size_t
     lib.gmlp_colsum.argtypes = [i64, i64, i32, vp, i64, vp, C.c_size_t, vp, vp]
+    lib.gmlp_colsum_static.argtypes = [i64, i64, i32, vp, i64, vp, vp]
     lib.gmlp_dropout_mask.argtypes = [pp, u8p, vp]
     lib.gmlp_gemm.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp]
     lib.gmlp_decode_scratch_bytes.argtypes = [pp]

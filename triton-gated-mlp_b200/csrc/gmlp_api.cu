@@ -710,3 +710,75 @@ int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, i
 }
 
 }  // extern "C"
+
+// ------------------------------------- column sums without caller scratch ----
+// Scratch for gmlp_colsum_static lives in the library image. The array's name is a
+// host-side handle in host code, not a device address: the address kernels can use
+// is looked up once per device with cudaGetSymbolAddress (below) and cached.
+namespace gmlp {
+constexpr size_t COLSUM_STATIC_BYTES = 1u << 20;  // 1 MiB per GPU that loads the library
+static __device__ __align__(256) float g_colsum_static_scratch[COLSUM_STATIC_BYTES / sizeof(float)];
+static float* g_colsum_static_ptr[64] = {};
+static std::mutex g_colsum_static_mu;
+}  // namespace gmlp
+
+extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* src,
+                                  int64_t ld, void* dst, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (rows <= 0 || cols <= 0 || (cols % 8) != 0 || (ld % 8) != 0 || ld < cols)
+    return fail(GMLP_ERR_SHAPE, "colsum needs rows > 0, cols and ld multiples of 8, ld >= cols");
+  if (!src || !dst) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(src)) return fail(GMLP_ERR_ALIGN, "src must be 16-byte aligned");
+  const size_t need = gmlp_colsum_scratch_bytes(rows, cols);
+  if (need > COLSUM_STATIC_BYTES)
+    return fail(GMLP_ERR_SCRATCH,
+                "rows=%lld cols=%lld needs %zu bytes of partial sums but the built-in scratch of "
+                "gmlp_colsum_static holds %zu; use gmlp_colsum with caller-provided scratch",
+                static_cast<long long>(rows), static_cast<long long>(cols), need,
+                static_cast<size_t>(COLSUM_STATIC_BYTES));
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  int ordinal = 0;
+  cudaError_t e = cudaGetDevice(&ordinal);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  float* part = nullptr;
+  {
+    // First call on this device: resolve the array's device address, with this
+    // device current. Later calls reuse it.
+    std::lock_guard<std::mutex> lk(g_colsum_static_mu);
+    if (!g_colsum_static_ptr[ordinal]) {
+      float* p = nullptr;
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_colsum_static_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(GMLP_ERR_LAUNCH, "cudaGetSymbolAddress(colsum scratch): %s",
+                    cudaGetErrorString(e));
+      g_colsum_static_ptr[ordinal] = p;
+    }
+    part = g_colsum_static_ptr[ordinal];
+  }
+  // Pass 1 writes every partial sum that pass 2 reads, so nothing left in the array
+  // by an earlier call is ever read and nothing has to be cleared.
+  const int rb = colsum_row_blocks(rows, cols);
+  const long long rows_per_block = (rows + rb - 1) / rb;
+  const dim3 grid(static_cast<unsigned>((cols + COLSUM_COLS - 1) / COLSUM_COLS),
+                  static_cast<unsigned>(rb));
+  const unsigned fin_blocks = static_cast<unsigned>((cols + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == GMLP_BF16) {
+    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows_per_block, part);
+    colsum_final_kernel<__nv_bfloat16><<<fin_blocks, 256, 0, st>>>(
+        part, cols, rb, static_cast<__nv_bfloat16*>(dst));
+  } else {
+    colsum_partial_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), rows,
+                                                        cols, ld, rows_per_block, part);
+    colsum_final_kernel<__half><<<fin_blocks, 256, 0, st>>>(part, cols, rb,
+                                                            static_cast<__half*>(dst));
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
