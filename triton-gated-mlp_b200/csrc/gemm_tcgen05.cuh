@@ -2,7 +2,7 @@
 // epilogues. One CTA per SM walks a grouped tile order; per CTA:
 //   warp 0 (one lane)  TMA producer: fills a STAGES-deep shared-memory ring
 //   warp 1 (one lane)  MMA issuer: tcgen05.mma into one of two TMEM accumulators
-//   warps 2..5         epilogue: tcgen05.ld the finished accumulator, apply the
+//   warps 2..17        epilogue: tcgen05.ld the finished accumulator, apply the
 //                      fused elementwise work, store to global memory
 // The two TMEM accumulators let the epilogue of tile i overlap the main loop of
 // tile i+1. No cluster launch and no TMA multicast is used.
@@ -24,6 +24,7 @@ enum : int {
   EPI_STORE = 0,    // C (+ bias[n]) (+ residual[m, n])            -> out0 / out1 (per batch)
   EPI_SWIGLU = 1,   // accumulator = [gate | up] per tile; H = dropout(silu(g) * u)
   EPI_DHIDDEN = 2,  // accumulator = dH; reads G, U; writes dGate, dUp
+  EPI_STORE_TMA = 3,  // EPI_STORE through staged TMA stores (short reductions, see below)
 };
 
 enum : int {
@@ -56,16 +57,24 @@ struct GemmArgs {
 constexpr int BM = 128;        // rows per tile = TMEM lanes
 constexpr int BK = 64;         // reduction elements per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 16;     // reduction elements per tcgen05.mma (16-bit inputs)
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 576;  // producer warp, MMA warp, 16 epilogue warps
 
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
   return (2 * bn <= 32) ? 32u : (2 * bn <= 64) ? 64u : (2 * bn <= 128) ? 128u
          : (2 * bn <= 256) ? 256u : 512u;
 }
 
-template <int BN, int STAGES>
+// Epilogue warps and their store-staging buffers (see epilogue_tile below).
+constexpr int EPI_WARPS = 16;
+constexpr int EPI_PARTS = EPI_WARPS / 4;
+constexpr int STAGE_BUF_BYTES = 32 * 32;                  // 32 rows x 16 sixteen-bit values
+constexpr int STAGE_RING = 4;
+constexpr int STAGING_BYTES = EPI_WARPS * STAGE_RING * STAGE_BUF_BYTES;  // 64 KB
+
+// Operand ring + (for the staged epilogues) the store staging area + alignment slack.
+template <int BN, int STAGES, int EPI>
 constexpr size_t gemm_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + 1024;
+  return static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + (EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? 96 * 1024 : STAGING_BYTES)) + 1024;
 }
 
 // ------------------------------------------------------------ small helpers --
@@ -110,9 +119,13 @@ __device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = q;
 }
 
-// sigma(x) = 1 / (1 + e^-x); the clamp keeps e^-x finite in fp32.
+// sigma(x) = 1 / (1 + e^-x) = 0.5 * tanh(x / 2) + 0.5: one MUFU op and two FMAs. The
+// hardware tanh approximation has a maximum relative error of about 2^-11, far below
+// the resolution of the 16-bit outputs.
 __device__ __forceinline__ float sigmoid_f(float x) {
-  return __fdividef(1.0f, 1.0f + __expf(-fmaxf(x, -80.0f)));
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(t, 0.5f, 0.5f);
 }
 
 // keep/scale factors for the 8 consecutive columns starting at (grow, gcol),
@@ -155,142 +168,404 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
   return c;
 }
 
+// Epilogue warps: EPI_WARPS = 16, four per TMEM lane quarter. Warp e (0..15) reads
+// lanes 32 * (e & 3) and column part (e >> 2) of the tile.
+//
+// Output path. A thread owns one output ROW, so writing its values straight to global
+// memory makes every store instruction touch 32 different cache lines with 16 bytes
+// each; measured on the training shape, each extra output matrix written that way cost
+// as much as a third of the whole GEMM. Instead each warp stages a [32 rows x 16
+// columns] block (1 KB, 32-byte rows) in shared memory and one lane hands it to the TMA
+// store engine, which writes full 32-byte sectors, clips rows >= M and columns >= N by
+// itself and runs asynchronously. Each warp owns a ring of four 1 KB staging buffers.
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
+  float2 a = Pack2<T>::unpack(q.x), b = Pack2<T>::unpack(q.y), c = Pack2<T>::unpack(q.z),
+         d = Pack2<T>::unpack(q.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  uint4 q;
+  q.x = Pack2<T>::pack(v[0], v[1]);
+  q.y = Pack2<T>::pack(v[2], v[3]);
+  q.z = Pack2<T>::pack(v[4], v[5]);
+  q.w = Pack2<T>::pack(v[6], v[7]);
+  return q;
+}
+
+// One warp's ring of staging buffers and the bookkeeping for its TMA stores.
+struct StoreRing {
+  uint32_t base;  // shared::cta address of this warp's STAGE_RING buffers
+  int next;       // buffer the next block goes to
+  int lane;
+
+  // Make the next buffer writable: all but the STAGE_RING - 1 most recent stores of
+  // this warp must have finished reading shared memory.
+  __device__ __forceinline__ uint32_t acquire() {
+    if (lane == 0) tma_store_wait_read<STAGE_RING - 1>();
+    __syncwarp();
+    return base + next * STAGE_BUF_BYTES;
+  }
+  // This lane's 16 values (two 16-byte halves) of its row.
+  __device__ __forceinline__ void write(uint32_t buf, const uint4& lo, const uint4& hi) {
+    st_shared_v4(buf + lane * 32, lo);
+    st_shared_v4(buf + lane * 32 + 16, hi);
+  }
+  // Hand the filled buffer to the TMA engine: block origin (col, row0) in the output.
+  __device__ __forceinline__ void flush(uint32_t buf, const CUtensorMap* map, int col, int row0) {
+    fence_proxy_async_smem();  // generic-proxy writes above -> visible to the async proxy
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map, buf, col, row0);
+      tma_store_commit();
+    }
+    next = (next + 1) % STAGE_RING;
+  }
+  __device__ __forceinline__ void drain() {
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
+  }
+};
+
 // Epilogue of one 128-row accumulator tile, executed by one warp for its 32 TMEM
-// lanes: lane i owns output row `row` and walks the tile's columns in chunks of 32.
-// `taddr` addresses (lane quarter, first accumulator column of the tile).
+// lanes and its part of the tile's columns: lane i owns output row `row` (`row0` is
+// lane 0's row) and walks the columns in units of 16. `taddr` addresses (lane quarter,
+// first accumulator column of the tile).
 template <int BN, int EPI, typename T>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row,
-                                              int batch, int n0, T* out0, T* out1, T* out2,
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row0,
+                                              int lane, int batch, int n0, int part,
+                                              StoreRing& ring, const CUtensorMap* mo0,
+                                              const CUtensorMap* mo1, const CUtensorMap* mo2,
                                               const T* in0, const T* in1, const T* bias0,
                                               const T* bias1, bool drop_on) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
+  static_assert(NU >= 1, "tile too narrow for the column parts");
+  const int row = row0 + lane;
   const bool row_ok = row < args.M;
-        if (EPI == EPI_STORE) {
-          T* const out = (batch ? out1 : out0) + static_cast<long long>(row) * args.ld_out;
-          const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
-  #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= args.N) break;
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
-            if (row_ok) {
-  #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int gc = col + j * 8;
-                if (gc < args.N) {
-                  float v[8];
-  #pragma unroll
-                  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j * 8 + i]);
-                  if (bias0) {
-                    float b[8];
-                    load8(bias0 + gc, b);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += b[i];
-                  }
-                  if (res) {
-                    float b[8];
-                    load8(res + gc, b);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += b[i];
-                  }
-                  store8(out + gc, v);
-                }
-              }
+  const int u0 = part * NU;
+
+  if (EPI == EPI_STORE) {
+    // One output matrix behind a long main loop: direct 16-byte stores keep up (the
+    // tensor pipe stays above 95 % busy), so this path spends no shared memory on
+    // staging and keeps a deeper operand ring instead.
+    T* const out = static_cast<T*>(batch ? args.out1 : args.out0) + static_cast<long long>(row) * args.ld_out;
+    const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
+#pragma unroll
+    for (int ui = 0; ui < NU; ++ui) {
+      const int col = n0 + (u0 + ui) * 16;
+      uint32_t acc[16];
+      tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
+      tmem_ld_wait();
+      if (row_ok && col < args.N) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int gc = col + j * 8;
+          if (gc < args.N) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
+            if (bias0) {
+              float b[8];
+              load8(bias0 + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += b[i];
             }
-          }
-        } else if (EPI == EPI_SWIGLU) {
-          const long long ro = static_cast<long long>(row) * args.ld_out;
-          const long long grow = args.drop.row0_global + row;
-  #pragma unroll 1
-          for (int c = 0; c < TILE_N / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= args.N) break;
-            uint32_t rg[32], ru[32];
-            tmem_ld_32x32(taddr + c * 32, rg);
-            tmem_ld_32x32(taddr + TILE_N + c * 32, ru);
-            tmem_ld_wait();
-            if (row_ok) {
-  #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int gc = col + j * 8;
-                if (gc < args.N) {
-                  float g[8], u[8], h[8];
-  #pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    g[i] = __uint_as_float(rg[j * 8 + i]);
-                    u[i] = __uint_as_float(ru[j * 8 + i]);
-                  }
-                  if (bias0) {
-                    float b[8];
-                    load8(bias0 + gc, b);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) g[i] += b[i];
-                  }
-                  if (bias1) {
-                    float b[8];
-                    load8(bias1 + gc, b);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) u[i] += b[i];
-                  }
-                  if (out1) {  // keep the pre-activations for the backward pass
-                    store8(out1 + ro + gc, g);
-                    store8(out2 + ro + gc, u);
-                  }
-  #pragma unroll
-                  for (int i = 0; i < 8; ++i) h[i] = g[i] * sigmoid_f(g[i]) * u[i];
-                  if (drop_on) {
-                    float f[8];
-                    dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) h[i] *= f[i];
-                  }
-                  store8(out0 + ro + gc, h);
-                }
-              }
+            if (res) {
+              float b[8];
+              load8(res + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += b[i];
             }
-          }
-        } else {  // EPI_DHIDDEN
-          const long long ro = static_cast<long long>(row) * args.ld_out;
-          const long long ri = static_cast<long long>(row) * args.ld_in;
-          const long long grow = args.drop.row0_global + row;
-  #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col = n0 + c * 32;
-            if (col >= args.N) break;
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + c * 32, r);
-            tmem_ld_wait();
-            if (row_ok) {
-  #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int gc = col + j * 8;
-                if (gc < args.N) {
-                  float dh[8], g[8], u[8], dg[8], du[8];
-  #pragma unroll
-                  for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(r[j * 8 + i]);
-                  load8(in0 + ri + gc, g);
-                  load8(in1 + ri + gc, u);
-                  if (drop_on) {
-                    float f[8];
-                    dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
-  #pragma unroll
-                    for (int i = 0; i < 8; ++i) dh[i] *= f[i];
-                  }
-  #pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const float s = sigmoid_f(g[i]);
-                    du[i] = dh[i] * g[i] * s;
-                    dg[i] = dh[i] * u[i] * s * (1.0f + g[i] * (1.0f - s));
-                  }
-                  store8(out0 + ro + gc, dg);
-                  store8(out1 + ro + gc, du);
-                }
-              }
-            }
+            store8(out + gc, v);
           }
         }
+      }
+    }
+  } else if (EPI == EPI_STORE_TMA) {
+    // Same result as EPI_STORE. When the reduction is short the main loop of a tile is
+    // too brief to hide row-wise global stores, so the block goes out through the
+    // staging ring and the TMA store engine instead (at the price of one ring stage).
+    const CUtensorMap* mo = batch ? mo1 : mo0;
+    const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
+#pragma unroll
+    for (int ui = 0; ui < NU; ++ui) {
+      const int col = n0 + (u0 + ui) * 16;
+      uint32_t acc[16];
+      tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
+      tmem_ld_wait();
+      if (col < args.N && row0 < args.M) {  // warp-uniform
+        uint4 q[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int gc = col + j * 8;
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
+          if (gc < args.N) {
+            if (bias0) {
+              float b[8];
+              load8(bias0 + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += b[i];
+            }
+            if (res && row_ok) {
+              float b[8];
+              load8(res + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] += b[i];
+            }
+          }
+          q[j] = pack8<T>(v);
+        }
+        const uint32_t buf = ring.acquire();
+        ring.write(buf, q[0], q[1]);
+        ring.flush(buf, mo, col, row0);
+      }
+    }
+  } else if (EPI == EPI_SWIGLU) {
+    const long long grow = args.drop.row0_global + row;
+#pragma unroll
+    for (int ui = 0; ui < NU; ++ui) {
+      const int col = n0 + (u0 + ui) * 16;
+      uint32_t rg[16], ru[16];
+      tmem_ld_32x16(taddr + (u0 + ui) * 16, rg);
+      tmem_ld_32x16(taddr + TILE_N + (u0 + ui) * 16, ru);
+      tmem_ld_wait();
+      if (col < args.N && row0 < args.M) {  // warp-uniform
+        uint4 qh[2], qg[2], qu[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int gc = col + j * 8;
+          float g[8], u[8], h[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            g[i] = __uint_as_float(rg[j * 8 + i]);
+            u[i] = __uint_as_float(ru[j * 8 + i]);
+          }
+          if (gc < args.N) {
+            if (bias0) {
+              float b[8];
+              load8(bias0 + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) g[i] += b[i];
+            }
+            if (bias1) {
+              float b[8];
+              load8(bias1 + gc, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) u[i] += b[i];
+            }
+          }
+          if (mo1) {  // keep the pre-activations for the backward pass
+            qg[j] = pack8<T>(g);
+            qu[j] = pack8<T>(u);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[i] = g[i] * sigmoid_f(g[i]) * u[i];
+          if (drop_on) {
+            float f[8];
+            dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[i] *= f[i];
+          }
+          qh[j] = pack8<T>(h);
+        }
+        uint32_t buf = ring.acquire();
+        ring.write(buf, qh[0], qh[1]);
+        ring.flush(buf, mo0, col, row0);
+        if (mo1) {
+          buf = ring.acquire();
+          ring.write(buf, qg[0], qg[1]);
+          ring.flush(buf, mo1, col, row0);
+          buf = ring.acquire();
+          ring.write(buf, qu[0], qu[1]);
+          ring.flush(buf, mo2, col, row0);
+        }
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------- dH epilogue (B1) ----
+// The dH epilogue needs G and U at the accumulator's positions. Reading them row by
+// row from global memory has the same problem as writing row by row, so each warp
+// brings them in with TMA as [32 x 16] blocks, one 2 KB (G, U) buffer pair per
+// 16-column unit, computes dGate / dUp in place (each lane overwrites exactly the 32
+// bytes of G and of U it has just read) and hands the same buffers to the TMA store
+// engine. Three pairs per warp: the loads of unit k+1 are in flight while unit k is
+// computed and while the stores of unit k-1 drain. The prefetch runs across tile
+// boundaries, since G and U do not depend on the GEMM.
+constexpr int DH_PAIRS = 3;
+constexpr int DH_PAIR_BYTES = 2 * STAGE_BUF_BYTES;
+constexpr int DH_STAGING_BYTES = EPI_WARPS * DH_PAIRS * DH_PAIR_BYTES;  // 96 KB
+static_assert(DH_STAGING_BYTES == 96 * 1024, "keep gemm_smem_bytes in step");
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 q;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+               : "r"(addr)
+               : "memory");
+  return q;
+}
+
+// Shared-memory footprint of a kernel's epilogue.
+template <int EPI>
+__host__ __device__ constexpr int epilogue_smem_bytes() {
+  return EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? DH_STAGING_BYTES : STAGING_BYTES);
+}
+
+// The epilogue role of one warp for all tiles of its CTA (or CTA pair).
+//   TILE_M     rows per tile: 128, or 256 for a CTA pair (row_off = cluster rank * 128)
+//   tfull0 / tempty0   shared::cta addresses of tfull[0] / tempty[0] ([1] is 8 bytes on)
+//   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
+//   epi_smem   this CTA's epilogue staging area; lbar0: 3 load barriers per warp
+template <int BN, int EPI, typename T, int TILE_M, bool REMOTE>
+__device__ __forceinline__ void epilogue_role(
+    const GemmArgs& args, int warp, int lane, int first_tile, int tile_stride, int total_tiles,
+    int m_tiles, int n_tiles, int row_off, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
+    uint32_t epi_smem, uint32_t lbar0, const CUtensorMap* mo0, const CUtensorMap* mo1_in,
+    const CUtensorMap* mo2, const CUtensorMap* mi0, const CUtensorMap* mi1, int* abort_flag) {
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  volatile int* abortp = abort_flag;
+  const int ew = warp - 2;          // epilogue warp index 0..15
+  const int quarter = warp & 3;     // TMEM lanes this warp may read
+  const int col_part = ew >> 2;
+  const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+  const T* const in0 = static_cast<const T*>(args.in0);
+  const T* const in1 = static_cast<const T*>(args.in1);
+  const T* const bias0 = static_cast<const T*>(args.bias0);
+  const T* const bias1 = static_cast<const T*>(args.bias1);
+  const CUtensorMap* const mo1 = (EPI == EPI_STORE_TMA || args.out1) ? mo1_in : nullptr;
+  const bool drop_on = args.drop.thresh != 0u;
+  auto release_tmem = [&](int acc) {
+    // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
+    // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
+    // semantics; no fence is placed here on purpose, since a fence would also wait for
+    // this warp's outstanding global stores.
+    __syncwarp();
+    if (lane == 0) {
+      if (REMOTE) mbar_arrive_cluster(mapa_shared(tempty0 + 8u * acc, 0));
+      else mbar_arrive(tempty0 + 8u * acc);
+    }
+  };
+  bool ok = true;
+  int local = 0;
+
+  if (EPI != EPI_DHIDDEN) {
+    StoreRing ring{epi_smem + ew * (STAGE_RING * STAGE_BUF_BYTES), 0, lane};
+    for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
+      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+      const int acc = local & 1;
+      ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + lane_addr;
+      const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
+      epilogue_tile<BN, EPI, T>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, ring,
+                                mo0, mo1, mo2, in0, in1, bias0, bias1, drop_on);
+      release_tmem(acc);
+    }
+    if (EPI != EPI_STORE) ring.drain();  // shared memory must stay valid until TMA has read it
+  } else {
+    constexpr int NU = BN / 16 / EPI_PARTS;  // 16-column units per warp and tile
+    const uint32_t my_smem = epi_smem + ew * (DH_PAIRS * DH_PAIR_BYTES);
+    const uint32_t my_bar = lbar0 + 8u * (ew * DH_PAIRS);
+    // (row0, col) of unit ui of `tile`
+    auto unit_origin = [&](int tile, int ui, int& row0, int& col) {
+      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+      row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
+      col = tc.n_tile * TILE_N + (col_part * NU + ui) * 16;
+    };
+    // Issue the G / U loads of unit number k (lane 0 only).
+    auto issue_load = [&](int k, int tile, int ui) {
+      int row0, col;
+      unit_origin(tile, ui, row0, col);
+      const int p = k % DH_PAIRS;
+      // This runs before the stores of unit k-1 are issued. The pair was last read by the
+      // two stores of unit k-3; the only groups committed since are the two of unit k-2.
+      tma_store_wait_read<2>();
+      const uint32_t buf = my_smem + p * DH_PAIR_BYTES;
+      const uint32_t bar = my_bar + 8u * p;
+      mbar_expect_tx(bar, DH_PAIR_BYTES);
+      tma_load_2d(buf, mi0, bar, col, row0);
+      tma_load_2d(buf + STAGE_BUF_BYTES, mi1, bar, col, row0);
+    };
+    int k = 0;
+    if (first_tile < total_tiles && lane == 0) issue_load(0, first_tile, 0);
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++local) {
+      const int acc = local & 1;
+      ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + lane_addr + col_part * NU * 16;
+#pragma unroll 1
+      for (int ui = 0; ui < NU; ++ui, ++k) {
+        // prefetch the next unit's G and U (possibly the first unit of the next tile)
+        if (lane == 0) {
+          if (ui + 1 < NU) issue_load(k + 1, tile, ui + 1);
+          else if (tile + tile_stride < total_tiles) issue_load(k + 1, tile + tile_stride, 0);
+        }
+        int row0, col;
+        unit_origin(tile, ui, row0, col);
+        uint32_t acc_r[16];
+        tmem_ld_32x16(taddr + ui * 16, acc_r);
+        const int p = k % DH_PAIRS;
+        ok = mbar_wait(my_bar + 8u * p, (k / DH_PAIRS) & 1, abortp);
+        ok = __all_sync(0xffffffffu, ok);
+        tmem_ld_wait();
+        if (!ok) break;
+        const uint32_t gbuf = my_smem + p * DH_PAIR_BYTES + lane * 32;
+        const uint32_t ubuf = gbuf + STAGE_BUF_BYTES;
+        const long long grow = args.drop.row0_global + row0 + lane;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float dh[8], g[8], u[8], dg[8], du[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(acc_r[j * 8 + i]);
+          unpack8<T>(ld_shared_v4(gbuf + j * 16), g);
+          unpack8<T>(ld_shared_v4(ubuf + j * 16), u);
+          if (drop_on) {
+            float f[8];
+            dropout_factors8(args.drop, grow, args.drop.col0_global + col + j * 8, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dh[i] *= f[i];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float sg = sigmoid_f(g[i]);
+            du[i] = dh[i] * g[i] * sg;
+            dg[i] = dh[i] * u[i] * sg * (1.0f + g[i] * (1.0f - sg));
+          }
+          st_shared_v4(gbuf + j * 16, pack8<T>(dg));
+          st_shared_v4(ubuf + j * 16, pack8<T>(du));
+        }
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
+        __syncwarp();
+        if (lane == 0) {
+          // Blocks entirely outside the matrix are clipped by the hardware.
+          tma_store_2d(mo0, my_smem + p * DH_PAIR_BYTES, col, row0);
+          tma_store_commit();
+          tma_store_2d(mo1_in, my_smem + p * DH_PAIR_BYTES + STAGE_BUF_BYTES, col, row0);
+          tma_store_commit();
+        }
+      }
+      if (!ok) break;
+      release_tmem(acc);
+    }
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
+  }
+  if (!ok && lane == 0) {
+    *abort_flag = 1;
+    atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+  }
 }
 
 // ------------------------------------------------------------------ kernel --
@@ -299,7 +574,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
                     const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0,
-                    const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmB1,
+                    const __grid_constant__ CUtensorMap tmO0,
+                    const __grid_constant__ CUtensorMap tmO1,
+                    const __grid_constant__ CUtensorMap tmO2,
+                    const __grid_constant__ CUtensorMap tmI0,
+                    const __grid_constant__ CUtensorMap tmI1, const GemmArgs args) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N range for M = 128");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 64 == 0, "MN-major B arrives in 64-column boxes");
@@ -318,6 +598,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  // dH epilogue only: one barrier per (epilogue warp, G/U buffer pair)
+  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_WARPS * DH_PAIRS : 1];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -342,8 +624,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tempty_bar(a), EPI_WARPS);  // one arrival per epilogue warp
     }
+    if (EPI == EPI_DHIDDEN)
+      for (int i = 0; i < EPI_WARPS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -455,42 +739,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
   } else {
     // ------------------------------------------------------------ epilogue --
-    const int quarter = warp & 3;  // TMEM lanes this warp may read
-    const int row_in_tile = quarter * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    T* const out0 = static_cast<T*>(args.out0);
-    T* const out1 = static_cast<T*>(args.out1);
-    T* const out2 = static_cast<T*>(args.out2);
-    const T* const in0 = static_cast<const T*>(args.in0);
-    const T* const in1 = static_cast<const T*>(args.in1);
-    const T* const bias0 = static_cast<const T*>(args.bias0);
-    const T* const bias1 = static_cast<const T*>(args.bias1);
-    const bool drop_on = args.drop.thresh != 0u;
-    int local = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
-      ok = mbar_wait(tfull_bar(acc), acc_phase, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + lane_addr;
-      const int row = tc.m_tile * BM + row_in_tile;
-      const int n0 = tc.n_tile * TILE_N;
-
-      epilogue_tile<BN, EPI, T>(args, taddr, row, tc.batch, n0, out0, out1, out2, in0, in1, bias0, bias1,
-                                drop_on);
-      // The accumulator has been read: hand it back to the MMA issuer.
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
-    }
-    if (!ok && lane == 0) {
-      abort_flag = 1;
-      atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
-    }
+    epilogue_role<BN, EPI, T, BM, false>(args, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
+                                         n_tiles, 0, tmem_base, tfull_bar(0), tempty_bar(0),
+                                         smem_base + STAGES * STAGE_BYTES, smem_u32(lbars), &tmO0, &tmO1,
+                                         &tmO2, &tmI0, &tmI1, &abort_flag);
   }
 
   tc_fence_before_sync();
@@ -517,10 +769,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 //              bytes on it; the leader's producer arms it for 2 x the per-CTA bytes.
 //   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
 //              both copies at once.
-//   tempty[a]  lives in the leader, 8 arrivals: 4 epilogue warps of each CTA.
-template <int BN, int STAGES>
+//   tempty[a]  lives in the leader, 32 arrivals: the 16 epilogue warps of each CTA.
+template <int BN, int STAGES, int EPI>
 constexpr size_t gemm_pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + 1024;
+  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + (EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? 96 * 1024 : STAGING_BYTES)) + 1024;
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
@@ -528,7 +780,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
                          const __grid_constant__ CUtensorMap tmA1,
                          const __grid_constant__ CUtensorMap tmB0,
-                         const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
+                         const __grid_constant__ CUtensorMap tmB1,
+                         const __grid_constant__ CUtensorMap tmO0,
+                         const __grid_constant__ CUtensorMap tmO1,
+                         const __grid_constant__ CUtensorMap tmO2,
+                    const __grid_constant__ CUtensorMap tmI0,
+                    const __grid_constant__ CUtensorMap tmI1, const GemmArgs args) {
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tcgen05 N range for M = 256");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
@@ -546,6 +803,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  // dH epilogue only: one barrier per (epilogue warp, G/U buffer pair)
+  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_WARPS * DH_PAIRS : 1];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -573,8 +832,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);  // 4 epilogue warps in each CTA of the pair
+      mbar_init(tempty_bar(a), 2 * EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
+    if (EPI == EPI_DHIDDEN)
+      for (int i = 0; i < EPI_WARPS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -688,40 +949,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
     }
   } else {
     // ------------------------------------------------------------ epilogue --
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    T* const out0 = static_cast<T*>(args.out0);
-    T* const out1 = static_cast<T*>(args.out1);
-    T* const out2 = static_cast<T*>(args.out2);
-    const T* const in0 = static_cast<const T*>(args.in0);
-    const T* const in1 = static_cast<const T*>(args.in1);
-    const T* const bias0 = static_cast<const T*>(args.bias0);
-    const T* const bias1 = static_cast<const T*>(args.bias1);
-    const bool drop_on = args.drop.thresh != 0u;
-    int local = 0;
-    bool ok = true;
-    for (int tile = pair; tile < total_tiles; tile += num_pairs, ++local) {
-      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
-      ok = mbar_wait(tfull_bar(acc), acc_phase, abortp);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + lane_addr;
-      const int row = tc.m_tile * PAIR_M + static_cast<int>(rank) * BM + row_in_tile;
-      const int n0 = tc.n_tile * TILE_N;
-      epilogue_tile<BN, EPI, T>(args, taddr, row, tc.batch, n0, out0, out1, out2, in0, in1, bias0,
-                                bias1, drop_on);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_shared(tempty_bar(acc), 0));
-    }
-    if (!ok && lane == 0) {
-      abort_flag = 1;
-      atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
-    }
+    epilogue_role<BN, EPI, T, PAIR_M, true>(args, warp, lane, pair, num_pairs, total_tiles, m_tiles,
+                                            n_tiles, static_cast<int>(rank) * BM, tmem_base, tfull_bar(0),
+                                            tempty_bar(0), smem_base + STAGES * STAGE_BYTES,
+                                            smem_u32(lbars), &tmO0, &tmO1, &tmO2, &tmI0, &tmI1,
+                                            &abort_flag);
   }
 
   // Neither CTA may exit (or free TMEM) while its peer can still read its shared

@@ -18,14 +18,6 @@ struct Philox4 {
   uint32_t x, y, z, w;
 };
 
-__host__ __device__ __forceinline__ uint32_t philox_mulhi(uint32_t a, uint32_t b) {
-#ifdef __CUDA_ARCH__
-  return __umulhi(a, b);
-#else
-  return static_cast<uint32_t>((static_cast<uint64_t>(a) * b) >> 32);
-#endif
-}
-
 __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2,
                                                           uint32_t c3, uint32_t k0,
                                                           uint32_t k1) {
@@ -33,8 +25,10 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t 
   constexpr uint32_t W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    const uint32_t hi0 = philox_mulhi(M0, c0), lo0 = M0 * c0;
-    const uint32_t hi1 = philox_mulhi(M1, c2), lo1 = M1 * c2;
+    // one 32 x 32 -> 64-bit multiply per product (a single IMAD.WIDE on the GPU)
+    const uint64_t p0 = static_cast<uint64_t>(M0) * c0, p1 = static_cast<uint64_t>(M1) * c2;
+    const uint32_t hi0 = static_cast<uint32_t>(p0 >> 32), lo0 = static_cast<uint32_t>(p0);
+    const uint32_t hi1 = static_cast<uint32_t>(p1 >> 32), lo1 = static_cast<uint32_t>(p1);
     const uint32_t n0 = hi1 ^ c1 ^ k0;
     const uint32_t n2 = hi0 ^ c3 ^ k1;
     c0 = n0;
