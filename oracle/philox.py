@@ -12,10 +12,13 @@ paper's known-answer vectors in tests/test_oracle_philox.py.
 
 Contract, for hidden element (row, col) of the un-sharded H[M, N_global]:
     e        = row * N_global + col
-    r[0:4]   = philox4x32_10(counter = (lo32(e >> 2), hi32(e >> 2), lo32(offset), hi32(offset)),
+    r[0:4]   = philox4x32_10(counter = (lo32(e >> 3), hi32(e >> 3), lo32(offset), hi32(offset)),
                              key     = (lo32(seed), hi32(seed)))
-    keep     = r[e & 3] >= floor(p * 2**32)
+    u16      = 16-bit half number (e & 1) (0 = low half) of word r[(e & 7) >> 1]
+    keep     = u16 >= floor(p * 2**16)
     scale    = float32(1) / (float32(1) - float32(p))
+One generator call serves 8 consecutive elements, sixteen random bits each, so the
+drop probability is honoured to within 2**-16.
 """
 from __future__ import annotations
 
@@ -50,9 +53,9 @@ def philox4x32_10(c0, c1, c2, c3, k0: int, k1: int):
 
 
 def threshold(p: float) -> int:
-    """floor(p * 2**32) with p first rounded to float32 (the C ABI carries p as a float)."""
-    t = float(np.float32(p)) * 4294967296.0
-    return int(min(t, 4294967295.0))
+    """floor(p * 2**16) with p first rounded to float32 (the C ABI carries p as a float)."""
+    t = float(np.float32(p)) * 65536.0
+    return int(min(t, 65535.0))
 
 
 def scale(p: float) -> np.float32:
@@ -65,11 +68,12 @@ def keep_mask(rows: int, cols: int, p: float, seed: int, offset: int, *, row0: i
     n_global = cols if n_global is None or n_global == 0 else n_global
     if p <= 0.0:
         return np.ones((rows, cols), dtype=bool)
-    assert n_global % 4 == 0 and col0 % 4 == 0 and cols % 4 == 0
+    assert n_global % 8 == 0 and col0 % 8 == 0 and cols % 8 == 0
     r = (np.arange(rows, dtype=np.uint64) + np.uint64(row0))[:, None]
-    q = (np.arange(cols // 4, dtype=np.uint64) * np.uint64(4) + np.uint64(col0))[None, :]
-    e4 = (r * np.uint64(n_global) + q) >> np.uint64(2)
-    w = philox4x32_10(e4 & MASK32, e4 >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
+    q = (np.arange(cols // 8, dtype=np.uint64) * np.uint64(8) + np.uint64(col0))[None, :]
+    e8 = (r * np.uint64(n_global) + q) >> np.uint64(3)
+    w = philox4x32_10(e8 & MASK32, e8 >> np.uint64(32), np.uint64(offset & 0xFFFFFFFF),
                       np.uint64((offset >> 32) & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
-    words = np.stack(w, axis=-1).reshape(rows, cols)  # lane e & 3 is the last axis
-    return words >= np.uint32(threshold(p))
+    words = np.stack(w, axis=-1)                                   # [rows, cols/8, 4]
+    halves = np.stack([words & np.uint32(0xFFFF), words >> np.uint32(16)], axis=-1)  # [..., 4, 2]: low half first
+    return halves.reshape(rows, cols) >= np.uint32(threshold(p))

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
     (128, 256, 0.1, 0x5EED, 0, 0, 0, 0),
     (200, 136, 0.5, 123456789012345, 77, 0, 0, 0),
     (64, 128, 0.25, 3, 9, 4096, 128, 512),            # a token- and column-shifted shard
-    (8, 1024, 0.9, 2 ** 63 + 5, 2 ** 40 + 1, 2 ** 24, 0, 1024),  # 64-bit seed/offset, index > 2**32
+    (8, 1024, 0.9, 2 ** 63 + 5, 2 ** 40 + 1, 2 ** 26, 0, 1024),  # 64-bit seed/offset, index >> 3 beyond 2**32
 ])
 def test_mask_bit_exact(pkg, cuda_dev, M, N, p, seed, offset, row0, col0, ng):
     K = pkg.ops.kernels

@@ -22,7 +22,7 @@ def _randn(shape, std, dev, seed):
     return (torch.randn(shape, device=dev, generator=g) * std).to(torch.bfloat16)
 
 
-def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=128, n_quads=16, seed=0):
+def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=128, n_quads=8, seed=0):
     seed_p, offset = 0x5EED, 1
     x = _randn((M, K), 1.0, dev, seed)
     m = pkg.FusedGatedMLP(K, N, bias=bias, dropout_p=p).to(dev).to(torch.bfloat16)
@@ -67,8 +67,8 @@ def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=12
     orc.assert_parity(f(xr.grad[ridx]), dx_want, "dx rows")
 
     # ---- intermediate units: weight / bias gradients over all M rows
-    quads = np.sort(rng.choice(N // 4, size=n_quads, replace=False))
-    cols = (quads[:, None] * 4 + np.arange(4)[None, :]).reshape(-1)
+    quads = np.sort(rng.choice(N // 8, size=n_quads, replace=False))   # groups of 8 consecutive units
+    cols = (quads[:, None] * 8 + np.arange(8)[None, :]).reshape(-1)
     cidx = torch.from_numpy(cols).to(dev)
     xf, dyf = f(x), f(dy)
     gs = xf @ wg[cols].T + (bg[cols] if bg is not None else 0)
@@ -76,7 +76,7 @@ def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=12
     dhs = dyf @ wd[:, cols]
     hs = orc.silu(gs) * us
     if p > 0:
-        keep = np.concatenate([philox.keep_mask(M, 4, p, seed_p, offset, col0=int(q) * 4, n_global=N) for q in quads],
+        keep = np.concatenate([philox.keep_mask(M, 8, p, seed_p, offset, col0=int(q) * 8, n_global=N) for q in quads],
                               axis=1)
         kcs = torch.from_numpy(keep.astype(np.float32) * philox.scale(p))
         dhs, hs = dhs * kcs, hs * kcs
@@ -103,7 +103,7 @@ def test_training_shape_all_gradients_full_size(pkg, cuda_dev):
 
 def test_large_prefill_forward_backward_full_size(pkg, cuda_dev):
     """M=65536, K=8192, N=28672, W ~ N(0,0.01), dY ~ N(0,1e-2); about 26 GB on the device."""
-    _sliced_check(pkg, cuda_dev, 65536, 8192, 28672, False, 0.0, 0.01, 1e-2, backward=True, n_rows=48, n_quads=6)
+    _sliced_check(pkg, cuda_dev, 65536, 8192, 28672, False, 0.0, 0.01, 1e-2, backward=True, n_rows=48, n_quads=3)
     torch.cuda.empty_cache()
 
 

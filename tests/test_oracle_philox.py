@@ -19,8 +19,9 @@ def test_philox4x32_10_known_answers():
 
 def test_threshold_and_scale():
     assert philox.threshold(0.0) == 0
-    assert philox.threshold(0.5) == 2 ** 31
-    assert philox.threshold(0.1) == int(float(np.float32(0.1)) * 2 ** 32)
+    assert philox.threshold(0.5) == 2 ** 15
+    assert philox.threshold(0.1) == int(float(np.float32(0.1)) * 2 ** 16) == 6553
+    assert philox.threshold(0.99999) == 65535
     assert philox.scale(0.5) == np.float32(2.0)
 
 
@@ -43,8 +44,20 @@ def test_mask_is_invariant_to_sharding():
     assert (tp == full[:, 128:]).all()
 
 
+def test_lane_order_within_one_generator_call():
+    """Element e uses 16-bit half (e & 1) of word (e & 7) >> 1 of the call with counter e >> 3."""
+    seed, offset, n = 0x1234_5678_9ABC, 3, 64
+    m = philox.keep_mask(1, n, 0.5, seed, offset)
+    for e in (0, 1, 6, 7, 8, 13, 63):
+        w = philox.philox4x32_10(np.uint32(e >> 3), np.uint32(0), np.uint32(offset), np.uint32(0),
+                                 seed & 0xFFFFFFFF, seed >> 32)
+        word = int(w[(e & 7) >> 1])
+        u16 = (word >> 16) if (e & 1) else (word & 0xFFFF)
+        assert m[0, e] == (u16 >= 2 ** 15)
+
+
 def test_mask_index_beyond_32_bits():
-    # element index e = row * N crosses 2**34 here: the counter's second word must be used
-    a = philox.keep_mask(2, 1024, 0.5, seed=1, offset=0, row0=(1 << 24), n_global=1024)
-    b = philox.keep_mask(2, 1024, 0.5, seed=1, offset=0, row0=(1 << 24) + (1 << 22), n_global=1024)
+    # element index e = row * N crosses 2**35 here: the counter's second word must be used
+    a = philox.keep_mask(2, 1024, 0.5, seed=1, offset=0, row0=(1 << 25), n_global=1024)
+    b = philox.keep_mask(2, 1024, 0.5, seed=1, offset=0, row0=(1 << 25) + (1 << 23), n_global=1024)
     assert (a != b).any()

@@ -42,26 +42,21 @@ dact_kernel(const T* __restrict__ dh, const T* __restrict__ g, const T* __restri
   }
 }
 
-// keep-mask dump: one thread per 4 consecutive columns.
+// keep-mask dump: one thread per 8 consecutive columns.
 __global__ void __launch_bounds__(256)
 dropout_mask_kernel(uint8_t* __restrict__ mask, long long M, long long N, DropoutParams drop) {
-  const long long quads_per_row = N / 4;
-  const long long total = M * quads_per_row;
+  const long long groups_per_row = N / 8;
+  const long long total = M * groups_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = i / quads_per_row;
-    const long long col = (i - row * quads_per_row) * 4;
-    const unsigned long long e =
-        static_cast<unsigned long long>(drop.row0_global + row) *
-            static_cast<unsigned long long>(drop.ncols_global) +
-        static_cast<unsigned long long>(drop.col0_global + col);
-    const Philox4 r = dropout_words(drop, e >> 2);
-    uchar4 m;
-    m.x = r.x >= drop.thresh;
-    m.y = r.y >= drop.thresh;
-    m.z = r.z >= drop.thresh;
-    m.w = r.w >= drop.thresh;
-    *reinterpret_cast<uchar4*>(mask + row * N + col) = m;
+    const long long row = i / groups_per_row;
+    const long long col = (i - row * groups_per_row) * 8;
+    float f[8];
+    dropout_factors8(drop, drop.row0_global + row, drop.col0_global + col, f);
+    uint2 m;
+    m.x = (f[0] != 0.f) | ((f[1] != 0.f) << 8) | ((f[2] != 0.f) << 16) | ((f[3] != 0.f) << 24);
+    m.y = (f[4] != 0.f) | ((f[5] != 0.f) << 8) | ((f[6] != 0.f) << 16) | ((f[7] != 0.f) << 24);
+    *reinterpret_cast<uint2*>(mask + row * N + col) = m;
   }
 }
 

@@ -64,12 +64,15 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
          : (2 * bn <= 256) ? 256u : 512u;
 }
 
-// Epilogue warps and their store-staging buffers (see epilogue_tile below).
+// Epilogue warps and their staging buffers (see epilogue_tile below). The four warps
+// that share a column part (one per TMEM lane quarter) form a GROUP: together they
+// own all 128 rows of a 16-column unit, stage it as one [128 x 16] block (4 KB) and
+// one of them issues one TMA operation for it.
 constexpr int EPI_WARPS = 16;
-constexpr int EPI_PARTS = EPI_WARPS / 4;
-constexpr int STAGE_BUF_BYTES = 32 * 32;                  // 32 rows x 16 sixteen-bit values
-constexpr int STAGE_RING = 4;
-constexpr int STAGING_BYTES = EPI_WARPS * STAGE_RING * STAGE_BUF_BYTES;  // 64 KB
+constexpr int EPI_PARTS = EPI_WARPS / 4;                  // groups
+constexpr int STAGE_BUF_BYTES = 128 * 32;                 // 128 rows x 16 sixteen-bit values
+constexpr int STAGE_RING = 4;                             // buffers per group
+constexpr int STAGING_BYTES = EPI_PARTS * STAGE_RING * STAGE_BUF_BYTES;  // 64 KB
 
 // Operand ring + (for the staged epilogues) the store staging area + alignment slack.
 template <int BN, int STAGES, int EPI>
@@ -128,23 +131,22 @@ __device__ __forceinline__ float sigmoid_f(float x) {
   return fmaf(t, 0.5f, 0.5f);
 }
 
-// keep/scale factors for the 8 consecutive columns starting at (grow, gcol),
-// gcol a multiple of 4 in the global index space.
+// keep/scale factors for the 8 consecutive columns starting at (grow, gcol), gcol a
+// multiple of 8 in the global index space: one Philox call, sixteen bits per element.
 __device__ __forceinline__ void dropout_factors8(const DropoutParams& d, long long grow,
                                                  long long gcol, float (&f)[8]) {
   const unsigned long long e =
       static_cast<unsigned long long>(grow) * static_cast<unsigned long long>(d.ncols_global) +
       static_cast<unsigned long long>(gcol);
-  const Philox4 r0 = dropout_words(d, e >> 2);
-  const Philox4 r1 = dropout_words(d, (e >> 2) + 1);
-  f[0] = r0.x >= d.thresh ? d.scale : 0.0f;
-  f[1] = r0.y >= d.thresh ? d.scale : 0.0f;
-  f[2] = r0.z >= d.thresh ? d.scale : 0.0f;
-  f[3] = r0.w >= d.thresh ? d.scale : 0.0f;
-  f[4] = r1.x >= d.thresh ? d.scale : 0.0f;
-  f[5] = r1.y >= d.thresh ? d.scale : 0.0f;
-  f[6] = r1.z >= d.thresh ? d.scale : 0.0f;
-  f[7] = r1.w >= d.thresh ? d.scale : 0.0f;
+  const Philox4 r = dropout_words(d, e >> 3);
+  f[0] = (r.x & 0xFFFFu) >= d.thresh ? d.scale : 0.0f;
+  f[1] = (r.x >> 16) >= d.thresh ? d.scale : 0.0f;
+  f[2] = (r.y & 0xFFFFu) >= d.thresh ? d.scale : 0.0f;
+  f[3] = (r.y >> 16) >= d.thresh ? d.scale : 0.0f;
+  f[4] = (r.z & 0xFFFFu) >= d.thresh ? d.scale : 0.0f;
+  f[5] = (r.z >> 16) >= d.thresh ? d.scale : 0.0f;
+  f[6] = (r.w & 0xFFFFu) >= d.thresh ? d.scale : 0.0f;
+  f[7] = (r.w >> 16) >= d.thresh ? d.scale : 0.0f;
 }
 
 struct TileCoord {
@@ -174,11 +176,13 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
 // Output path. A thread owns one output ROW, so writing its values straight to global
 // memory makes every store instruction touch 32 different cache lines with 16 bytes
 // each; measured on the training shape, each extra output matrix written that way cost
-// as much as a third of the whole GEMM. Instead each warp stages a [32 rows x 16
-// columns] block (1 KB, 32-byte rows) in shared memory and one lane hands it to the TMA
-// store engine, which writes full 32-byte sectors, clips rows >= M and columns >= N by
-// itself and runs asynchronously. Each warp owns a ring of four 1 KB staging buffers.
-
+// as much as a third of the whole GEMM. Instead the four warps of a group stage a
+// [128 rows x 16 columns] block (4 KB, 32-byte rows, 32-byte swizzle) in shared memory
+// and one thread hands it to the TMA store engine, which writes full 32-byte sectors,
+// clips rows >= M and columns >= N by itself and runs asynchronously. Blocks are this
+// large because the TMA engine of an SM retires roughly one operation per 90 cycles:
+// with one [32 x 16] block per warp the dH epilogue alone needed 256 operations per
+// tile and ran at exactly that rate.
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
   float2 a = Pack2<T>::unpack(q.x), b = Pack2<T>::unpack(q.y), c = Pack2<T>::unpack(q.z),
@@ -196,47 +200,56 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return q;
 }
 
-// One warp's ring of staging buffers and the bookkeeping for its TMA stores.
-struct StoreRing {
-  uint32_t base;  // shared::cta address of this warp's STAGE_RING buffers
-  int next;       // buffer the next block goes to
-  int lane;
+__device__ __forceinline__ void group_sync(int gid) {
+  asm volatile("bar.sync %0, 128;" ::"r"(gid) : "memory");  // the four warps of one group
+}
 
-  // Make the next buffer writable: all but the STAGE_RING - 1 most recent stores of
-  // this warp must have finished reading shared memory.
-  __device__ __forceinline__ uint32_t acquire() {
-    if (lane == 0) tma_store_wait_read<STAGE_RING - 1>();
-    __syncwarp();
-    return base + next * STAGE_BUF_BYTES;
-  }
-  // This lane's 16 values (two 16-byte halves) of its row.
-  __device__ __forceinline__ void write(uint32_t buf, const uint4& lo, const uint4& hi) {
-    st_shared_v4(buf + lane * 32, lo);
-    st_shared_v4(buf + lane * 32 + 16, hi);
+// A group's ring of staging buffers and the bookkeeping for its TMA stores. Every
+// member of the group holds a copy and calls the same sequence of methods.
+struct StoreRing {
+  uint32_t base;     // shared::cta address of this group's STAGE_RING buffers
+  uint32_t row_off;  // byte offset of this thread's row inside a block
+  uint32_t sw;       // 32-byte swizzle of that row: 16 when its two halves swap places
+  int next;          // buffer the next block goes to
+  int gid;           // named barrier of the group
+  bool issuer;       // the one thread of the group that talks to the TMA engine
+
+  __device__ __forceinline__ uint32_t current() const { return base + next * STAGE_BUF_BYTES; }
+  // This thread's 16 values (two 16-byte halves) of its row. In the swizzled layout the
+  // halves swap places in rows 4..7 of every group of 8, which spreads a warp's 16-byte
+  // accesses over all banks.
+  __device__ __forceinline__ void write(uint32_t buf, const uint4& lo, const uint4& hi) const {
+    st_shared_v4(buf + row_off + sw, lo);
+    st_shared_v4(buf + row_off + (16u ^ sw), hi);
   }
   // Hand the filled buffer to the TMA engine: block origin (col, row0) in the output.
+  // Before the group barrier the issuer makes sure the buffer that comes NEXT is no
+  // longer being read (it was used STAGE_RING - 1 flushes ago), so after the barrier
+  // every member may start filling it.
   __device__ __forceinline__ void flush(uint32_t buf, const CUtensorMap* map, int col, int row0) {
     fence_proxy_async_smem();  // generic-proxy writes above -> visible to the async proxy
-    __syncwarp();
-    if (lane == 0) {
+    if (issuer) tma_store_wait_read<STAGE_RING - 2>();
+    group_sync(gid);
+    if (issuer) {
       tma_store_2d(map, buf, col, row0);
       tma_store_commit();
     }
     next = (next + 1) % STAGE_RING;
   }
-  __device__ __forceinline__ void drain() {
-    if (lane == 0) tma_store_wait_all();
-    __syncwarp();
+  __device__ __forceinline__ void drain() const {
+    if (issuer) tma_store_wait_all();
   }
 };
 
 // Epilogue of one 128-row accumulator tile, executed by one warp for its 32 TMEM
-// lanes and its part of the tile's columns: lane i owns output row `row` (`row0` is
-// lane 0's row) and walks the columns in units of 16. `taddr` addresses (lane quarter,
-// first accumulator column of the tile).
+// lanes and its part of the tile's columns: lane i owns output row
+// tile_row0 + 32 * quarter + i and walks the columns in units of 16. `taddr` addresses
+// (lane quarter, first accumulator column of the tile). All four warps of a group
+// execute the same sequence of ring flushes (the conditions around them depend on
+// columns only, never on the warp's rows).
 template <int BN, int EPI, typename T>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row0,
-                                              int lane, int batch, int n0, int part,
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int tile_row0,
+                                              int quarter, int lane, int batch, int n0, int part,
                                               StoreRing& ring, const CUtensorMap* mo0,
                                               const CUtensorMap* mo1, const CUtensorMap* mo2,
                                               const T* in0, const T* in1, const T* bias0,
@@ -244,7 +257,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
   static_assert(NU >= 1, "tile too narrow for the column parts");
-  const int row = row0 + lane;
+  const int row = tile_row0 + quarter * 32 + lane;
   const bool row_ok = row < args.M;
   const int u0 = part * NU;
 
@@ -297,7 +310,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
       uint32_t acc[16];
       tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
       tmem_ld_wait();
-      if (col < args.N && row0 < args.M) {  // warp-uniform
+      if (col < args.N) {  // uniform over the group
         uint4 q[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -321,9 +334,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
           }
           q[j] = pack8<T>(v);
         }
-        const uint32_t buf = ring.acquire();
+        const uint32_t buf = ring.current();
         ring.write(buf, q[0], q[1]);
-        ring.flush(buf, mo, col, row0);
+        ring.flush(buf, mo, col, tile_row0);
       }
     }
   } else if (EPI == EPI_SWIGLU) {
@@ -335,7 +348,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
       tmem_ld_32x16(taddr + (u0 + ui) * 16, rg);
       tmem_ld_32x16(taddr + TILE_N + (u0 + ui) * 16, ru);
       tmem_ld_wait();
-      if (col < args.N && row0 < args.M) {  // warp-uniform
+      if (col < args.N) {  // uniform over the group
         uint4 qh[2], qg[2], qu[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -374,16 +387,16 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
           }
           qh[j] = pack8<T>(h);
         }
-        uint32_t buf = ring.acquire();
+        uint32_t buf = ring.current();
         ring.write(buf, qh[0], qh[1]);
-        ring.flush(buf, mo0, col, row0);
+        ring.flush(buf, mo0, col, tile_row0);
         if (mo1) {
-          buf = ring.acquire();
+          buf = ring.current();
           ring.write(buf, qg[0], qg[1]);
-          ring.flush(buf, mo1, col, row0);
-          buf = ring.acquire();
+          ring.flush(buf, mo1, col, tile_row0);
+          buf = ring.current();
           ring.write(buf, qu[0], qu[1]);
-          ring.flush(buf, mo2, col, row0);
+          ring.flush(buf, mo2, col, tile_row0);
         }
       }
     }
@@ -392,16 +405,16 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
 
 // --------------------------------------------------------- dH epilogue (B1) ----
 // The dH epilogue needs G and U at the accumulator's positions. Reading them row by
-// row from global memory has the same problem as writing row by row, so each warp
-// brings them in with TMA as [32 x 16] blocks, one 2 KB (G, U) buffer pair per
-// 16-column unit, computes dGate / dUp in place (each lane overwrites exactly the 32
+// row from global memory has the same problem as writing row by row, so each group
+// brings them in with TMA as [128 x 16] blocks, one 8 KB (G, U) buffer pair per
+// 16-column unit, computes dGate / dUp in place (each thread overwrites exactly the 32
 // bytes of G and of U it has just read) and hands the same buffers to the TMA store
-// engine. Three pairs per warp: the loads of unit k+1 are in flight while unit k is
+// engine. Three pairs per group: the loads of unit k+1 are in flight while unit k is
 // computed and while the stores of unit k-1 drain. The prefetch runs across tile
 // boundaries, since G and U do not depend on the GEMM.
 constexpr int DH_PAIRS = 3;
 constexpr int DH_PAIR_BYTES = 2 * STAGE_BUF_BYTES;
-constexpr int DH_STAGING_BYTES = EPI_WARPS * DH_PAIRS * DH_PAIR_BYTES;  // 96 KB
+constexpr int DH_STAGING_BYTES = EPI_PARTS * DH_PAIRS * DH_PAIR_BYTES;  // 96 KB
 static_assert(DH_STAGING_BYTES == 96 * 1024, "keep gemm_smem_bytes in step");
 
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
@@ -413,35 +426,47 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   return q;
 }
 
-// Shared-memory footprint of a kernel's epilogue.
-template <int EPI>
-__host__ __device__ constexpr int epilogue_smem_bytes() {
-  return EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? DH_STAGING_BYTES : STAGING_BYTES);
-}
-
 // The epilogue role of one warp for all tiles of its CTA (or CTA pair).
 //   TILE_M     rows per tile: 128, or 256 for a CTA pair (row_off = cluster rank * 128)
 //   tfull0 / tempty0   shared::cta addresses of tfull[0] / tempty[0] ([1] is 8 bytes on)
 //   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
-//   epi_smem   this CTA's epilogue staging area; lbar0: 3 load barriers per warp
+//   epi_smem   this CTA's epilogue staging area; lbar0: DH_PAIRS load barriers per group
+//   grp_abort  one word per group, written by the group's issuer warp only
+//
+// Staged epilogues synchronise the four warps of a group with named barriers, which
+// have no time limit. To keep every wait in the kernel bounded, only the group's issuer
+// warp (lane quarter 0) waits on mbarriers; it publishes the outcome in grp_abort before
+// the next group barrier and all four warps act on that one word, so they always take
+// the same way out.
 template <int BN, int EPI, typename T, int TILE_M, bool REMOTE>
 __device__ __forceinline__ void epilogue_role(
     const GemmArgs& args, int warp, int lane, int first_tile, int tile_stride, int total_tiles,
     int m_tiles, int n_tiles, int row_off, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
-    uint32_t epi_smem, uint32_t lbar0, const CUtensorMap* mo0, const CUtensorMap* mo1_in,
-    const CUtensorMap* mo2, const CUtensorMap* mi0, const CUtensorMap* mi1, int* abort_flag) {
+    uint32_t epi_smem, uint32_t lbar0, int* grp_abort_all, const CUtensorMap* mo0,
+    const CUtensorMap* mo1_in, const CUtensorMap* mo2, const CUtensorMap* mi0,
+    const CUtensorMap* mi1, int* abort_flag) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr bool GROUPED = (EPI != EPI_STORE);
   volatile int* abortp = abort_flag;
   const int ew = warp - 2;          // epilogue warp index 0..15
   const int quarter = warp & 3;     // TMEM lanes this warp may read
   const int col_part = ew >> 2;
+  const int gid = 1 + col_part;     // named barrier of this warp's group
+  const bool issuer_warp = quarter == 0;
+  const bool issuer = issuer_warp && lane == 0;
+  volatile int* grp_abort = grp_abort_all + col_part;
   const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+  const uint32_t row_off_bytes = static_cast<uint32_t>(quarter * 32 + lane) * 32u;
+  const uint32_t sw = static_cast<uint32_t>((lane >> 2) & 1) << 4;
   const T* const in0 = static_cast<const T*>(args.in0);
   const T* const in1 = static_cast<const T*>(args.in1);
   const T* const bias0 = static_cast<const T*>(args.bias0);
   const T* const bias1 = static_cast<const T*>(args.bias1);
   const CUtensorMap* const mo1 = (EPI == EPI_STORE_TMA || args.out1) ? mo1_in : nullptr;
   const bool drop_on = args.drop.thresh != 0u;
+  bool ok = true;
+  int local = 0;
+
   auto release_tmem = [&](int acc) {
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
@@ -453,84 +478,107 @@ __device__ __forceinline__ void epilogue_role(
       else mbar_arrive(tempty0 + 8u * acc);
     }
   };
-  bool ok = true;
-  int local = 0;
+  // Wait for the accumulator of the warp's `local`-th tile; false = give up.
+  auto wait_tile = [&](int acc) -> bool {
+    if (!GROUPED) {
+      bool w = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
+      return __all_sync(0xffffffffu, w);
+    }
+    if (issuer_warp) {
+      bool w = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
+      w = __all_sync(0xffffffffu, w);
+      if (lane == 0) *grp_abort = (!w || *abortp != 0) ? 1 : 0;
+    }
+    group_sync(gid);
+    const bool go = *grp_abort == 0;
+    group_sync(gid);  // nobody reads the word after this point until it is written again
+    return go;
+  };
 
   if (EPI != EPI_DHIDDEN) {
-    StoreRing ring{epi_smem + ew * (STAGE_RING * STAGE_BUF_BYTES), 0, lane};
+    StoreRing ring{epi_smem + col_part * (STAGE_RING * STAGE_BUF_BYTES), row_off_bytes, sw, 0, gid, issuer};
     for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
       const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
       const int acc = local & 1;
-      ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = wait_tile(acc);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + lane_addr;
-      const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
-      epilogue_tile<BN, EPI, T>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, ring,
-                                mo0, mo1, mo2, in0, in1, bias0, bias1, drop_on);
+      epilogue_tile<BN, EPI, T>(args, taddr, tc.m_tile * TILE_M + row_off, quarter, lane, tc.batch,
+                                tc.n_tile * TILE_N, col_part, ring, mo0, mo1, mo2, in0, in1, bias0,
+                                bias1, drop_on);
       release_tmem(acc);
     }
-    if (EPI != EPI_STORE) ring.drain();  // shared memory must stay valid until TMA has read it
+    if (GROUPED) ring.drain();  // shared memory must stay valid until TMA has read it
   } else {
-    constexpr int NU = BN / 16 / EPI_PARTS;  // 16-column units per warp and tile
-    const uint32_t my_smem = epi_smem + ew * (DH_PAIRS * DH_PAIR_BYTES);
-    const uint32_t my_bar = lbar0 + 8u * (ew * DH_PAIRS);
-    // (row0, col) of unit ui of `tile`
-    auto unit_origin = [&](int tile, int ui, int& row0, int& col) {
+    constexpr int NU = BN / 16 / EPI_PARTS;  // 16-column units per group and tile
+    const uint32_t grp_smem = epi_smem + col_part * (DH_PAIRS * DH_PAIR_BYTES);
+    const uint32_t grp_bar = lbar0 + 8u * (col_part * DH_PAIRS);
+    // Origin (first row of this CTA's 128-row slab, first column of this group's part) of
+    // `tile`: decoded once per tile, never per unit (decode_tile divides by run-time values).
+    auto tile_origin = [&](int tile, int& row0, int& col0) {
       const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
-      row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
-      col = tc.n_tile * TILE_N + (col_part * NU + ui) * 16;
+      row0 = tc.m_tile * TILE_M + row_off;
+      col0 = tc.n_tile * TILE_N + col_part * NU * 16;
     };
-    // Issue the G / U loads of unit number k (lane 0 only).
-    auto issue_load = [&](int k, int tile, int ui) {
-      int row0, col;
-      unit_origin(tile, ui, row0, col);
+    // Issue the G / U loads of unit number k, block origin (col, row0) (issuer only).
+    auto issue_load = [&](int k, int row0, int col) {
       const int p = k % DH_PAIRS;
       // This runs before the stores of unit k-1 are issued. The pair was last read by the
       // two stores of unit k-3; the only groups committed since are the two of unit k-2.
       tma_store_wait_read<2>();
-      const uint32_t buf = my_smem + p * DH_PAIR_BYTES;
-      const uint32_t bar = my_bar + 8u * p;
+      const uint32_t buf = grp_smem + p * DH_PAIR_BYTES;
+      const uint32_t bar = grp_bar + 8u * p;
       mbar_expect_tx(bar, DH_PAIR_BYTES);
       tma_load_2d(buf, mi0, bar, col, row0);
       tma_load_2d(buf + STAGE_BUF_BYTES, mi1, bar, col, row0);
     };
     int k = 0;
-    if (first_tile < total_tiles && lane == 0) issue_load(0, first_tile, 0);
+    int row0 = 0, col0 = 0, next_row0 = 0, next_col0 = 0;
+    if (first_tile < total_tiles) {
+      tile_origin(first_tile, row0, col0);
+      if (issuer) issue_load(0, row0, col0);
+    }
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++local) {
+      const bool has_next = tile + tile_stride < total_tiles;
+      if (has_next) tile_origin(tile + tile_stride, next_row0, next_col0);
       const int acc = local & 1;
-      ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = wait_tile(acc);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + lane_addr + col_part * NU * 16;
+      const long long grow = args.drop.row0_global + row0 + quarter * 32 + lane;
 #pragma unroll 1
       for (int ui = 0; ui < NU; ++ui, ++k) {
         // prefetch the next unit's G and U (possibly the first unit of the next tile)
-        if (lane == 0) {
-          if (ui + 1 < NU) issue_load(k + 1, tile, ui + 1);
-          else if (tile + tile_stride < total_tiles) issue_load(k + 1, tile + tile_stride, 0);
+        if (issuer) {
+          if (ui + 1 < NU) issue_load(k + 1, row0, col0 + (ui + 1) * 16);
+          else if (has_next) issue_load(k + 1, next_row0, next_col0);
         }
-        int row0, col;
-        unit_origin(tile, ui, row0, col);
+        const int col = col0 + ui * 16;
         uint32_t acc_r[16];
         tmem_ld_32x16(taddr + ui * 16, acc_r);
         const int p = k % DH_PAIRS;
-        ok = mbar_wait(my_bar + 8u * p, (k / DH_PAIRS) & 1, abortp);
-        ok = __all_sync(0xffffffffu, ok);
+        if (issuer_warp) {
+          bool w = mbar_wait(grp_bar + 8u * p, (k / DH_PAIRS) & 1, abortp);
+          w = __all_sync(0xffffffffu, w);
+          if (lane == 0) *grp_abort = (!w || *abortp != 0) ? 1 : 0;
+        }
+        group_sync(gid);  // G and U of this unit have landed (or the group gives up)
         tmem_ld_wait();
-        if (!ok) break;
-        const uint32_t gbuf = my_smem + p * DH_PAIR_BYTES + lane * 32;
+        if (*grp_abort != 0) {
+          ok = false;
+          break;
+        }
+        const uint32_t gbuf = grp_smem + p * DH_PAIR_BYTES + row_off_bytes;
         const uint32_t ubuf = gbuf + STAGE_BUF_BYTES;
-        const long long grow = args.drop.row0_global + row0 + lane;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           float dh[8], g[8], u[8], dg[8], du[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(acc_r[j * 8 + i]);
-          unpack8<T>(ld_shared_v4(gbuf + j * 16), g);
-          unpack8<T>(ld_shared_v4(ubuf + j * 16), u);
+          unpack8<T>(ld_shared_v4(gbuf + ((j * 16) ^ sw)), g);
+          unpack8<T>(ld_shared_v4(ubuf + ((j * 16) ^ sw)), u);
           if (drop_on) {
             float f[8];
             dropout_factors8(args.drop, grow, args.drop.col0_global + col + j * 8, f);
@@ -543,24 +591,25 @@ __device__ __forceinline__ void epilogue_role(
             du[i] = dh[i] * g[i] * sg;
             dg[i] = dh[i] * u[i] * sg * (1.0f + g[i] * (1.0f - sg));
           }
-          st_shared_v4(gbuf + j * 16, pack8<T>(dg));
-          st_shared_v4(ubuf + j * 16, pack8<T>(du));
+          st_shared_v4(gbuf + ((j * 16) ^ sw), pack8<T>(dg));
+          st_shared_v4(ubuf + ((j * 16) ^ sw), pack8<T>(du));
         }
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
-        __syncwarp();
-        if (lane == 0) {
-          // Blocks entirely outside the matrix are clipped by the hardware.
-          tma_store_2d(mo0, my_smem + p * DH_PAIR_BYTES, col, row0);
+        group_sync(gid);
+        if (issuer) {
+          // Rows >= M and columns >= N of a block are clipped by the hardware.
+          tma_store_2d(mo0, grp_smem + p * DH_PAIR_BYTES, col, row0);
           tma_store_commit();
-          tma_store_2d(mo1_in, my_smem + p * DH_PAIR_BYTES + STAGE_BUF_BYTES, col, row0);
+          tma_store_2d(mo1_in, grp_smem + p * DH_PAIR_BYTES + STAGE_BUF_BYTES, col, row0);
           tma_store_commit();
         }
       }
       if (!ok) break;
       release_tmem(acc);
+      row0 = next_row0;
+      col0 = next_col0;
     }
-    if (lane == 0) tma_store_wait_all();
-    __syncwarp();
+    if (issuer) tma_store_wait_all();
   }
   if (!ok && lane == 0) {
     *abort_flag = 1;
@@ -598,8 +647,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
-  // dH epilogue only: one barrier per (epilogue warp, G/U buffer pair)
-  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_WARPS * DH_PAIRS : 1];
+  // dH epilogue only: one barrier per (epilogue group, G/U buffer pair)
+  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_PARTS * DH_PAIRS : 1];
+  __shared__ int grp_abort[EPI_PARTS];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -618,6 +668,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    for (int i = 0; i < EPI_PARTS; ++i) grp_abort[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -627,7 +678,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(tempty_bar(a), EPI_WARPS);  // one arrival per epilogue warp
     }
     if (EPI == EPI_DHIDDEN)
-      for (int i = 0; i < EPI_WARPS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
+      for (int i = 0; i < EPI_PARTS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -741,8 +792,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
     // ------------------------------------------------------------ epilogue --
     epilogue_role<BN, EPI, T, BM, false>(args, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
                                          n_tiles, 0, tmem_base, tfull_bar(0), tempty_bar(0),
-                                         smem_base + STAGES * STAGE_BYTES, smem_u32(lbars), &tmO0, &tmO1,
-                                         &tmO2, &tmI0, &tmI1, &abort_flag);
+                                         smem_base + STAGES * STAGE_BYTES, smem_u32(lbars), grp_abort, &tmO0,
+                                         &tmO1, &tmO2, &tmI0, &tmI1, &abort_flag);
   }
 
   tc_fence_before_sync();
@@ -803,8 +854,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
-  // dH epilogue only: one barrier per (epilogue warp, G/U buffer pair)
-  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_WARPS * DH_PAIRS : 1];
+  // dH epilogue only: one barrier per (epilogue group, G/U buffer pair)
+  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_PARTS * DH_PAIRS : 1];
+  __shared__ int grp_abort[EPI_PARTS];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -826,6 +878,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    for (int i = 0; i < EPI_PARTS; ++i) grp_abort[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -835,7 +888,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(tempty_bar(a), 2 * EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
     if (EPI == EPI_DHIDDEN)
-      for (int i = 0; i < EPI_WARPS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
+      for (int i = 0; i < EPI_PARTS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -952,8 +1005,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
     epilogue_role<BN, EPI, T, PAIR_M, true>(args, warp, lane, pair, num_pairs, total_tiles, m_tiles,
                                             n_tiles, static_cast<int>(rank) * BM, tmem_base, tfull_bar(0),
                                             tempty_bar(0), smem_base + STAGES * STAGE_BYTES,
-                                            smem_u32(lbars), &tmO0, &tmO1, &tmO2, &tmI0, &tmI1,
-                                            &abort_flag);
+                                            smem_u32(lbars), grp_abort, &tmO0, &tmO1, &tmO2, &tmI0,
+                                            &tmI1, &abort_flag);
   }
 
   // Neither CTA may exit (or free TMEM) while its peer can still read its shared

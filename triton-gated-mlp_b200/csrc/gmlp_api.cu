@@ -86,10 +86,11 @@ static int device_info(const DeviceInfo** out) {
 
 // ------------------------------------------------------------- tensor maps --
 // 2-D row-major matrix [outer, inner] of 16-bit elements; operand maps use the
-// 128-byte swizzle (out-of-bounds elements read as zero), output maps none.
+// 128-byte swizzle (out-of-bounds elements read as zero), epilogue block maps the 32-byte one.
 static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
                       int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype,
                       bool swizzle128 = true) {
+  // swizzle128 = false: the epilogue's [128 x 16] staging blocks, 32-byte rows, 32-byte swizzle
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
   const cuuint32_t box[2] = {box_inner, box_outer};
@@ -98,7 +99,7 @@ static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t o
       dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -175,22 +176,22 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   } else {
     mB1 = mB0;
   }
-  // Outputs leave through TMA stores of [32 rows x 16 columns] blocks.
+  // Outputs leave through TMA stores of [128 rows x 16 columns] blocks.
   CUtensorMap mO0, mO1, mO2;
   if (!ep.out0 || !aligned16(ep.out0) || (ep.ld_out % 8) != 0)
     return fail(GMLP_ERR_ALIGN, "output base / pitch not 16-byte aligned");
-  if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 16, 32, dtype, false))) return rc;
+  if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
   mO1 = mO0;
   mO2 = mO0;
-  if (ep.out1 && (rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 16, 32, dtype, false))) return rc;
-  if (ep.out2 && (rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 16, 32, dtype, false))) return rc;
+  if (ep.out1 && (rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
+  if (ep.out2 && (rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
   // The dH epilogue also reads G and U through TMA, in the same block shape.
   CUtensorMap mI0 = mO0, mI1 = mO0;
   if (EPI == EPI_DHIDDEN) {
     if (!ep.in0 || !ep.in1 || !aligned16(ep.in0) || !aligned16(ep.in1) || (ep.ld_in % 8) != 0)
       return fail(GMLP_ERR_ALIGN, "G / U base or pitch not 16-byte aligned");
-    if ((rc = encode_map(&mI0, ep.in0, N, M, ep.ld_in, 16, 32, dtype, false))) return rc;
-    if ((rc = encode_map(&mI1, ep.in1, N, M, ep.ld_in, 16, 32, dtype, false))) return rc;
+    if ((rc = encode_map(&mI0, ep.in0, N, M, ep.ld_in, 16, 128, dtype, false))) return rc;
+    if ((rc = encode_map(&mI1, ep.in1, N, M, ep.ld_in, 16, 128, dtype, false))) return rc;
   }
   GemmArgs args;
   memset(&args, 0, sizeof(args));
@@ -291,9 +292,9 @@ static int check_problem(const gmlp_problem_t* p) {
   if (!(p->dropout_p >= 0.0f && p->dropout_p < 1.0f))
     return fail(GMLP_ERR_ARG, "dropout_p=%f outside [0, 1)", static_cast<double>(p->dropout_p));
   const int64_t ng = p->N_global ? p->N_global : p->N;
-  if (p->dropout_p > 0.0f && ((ng % 4) != 0 || (p->col0_global % 4) != 0 || p->row0_global < 0 ||
+  if (p->dropout_p > 0.0f && ((ng % 8) != 0 || (p->col0_global % 8) != 0 || p->row0_global < 0 ||
                               p->col0_global < 0 || p->col0_global + p->N > ng))
-    return fail(GMLP_ERR_SHAPE, "dropout needs N_global and col0_global multiples of 4 and the "
+    return fail(GMLP_ERR_SHAPE, "dropout needs N_global and col0_global multiples of 8 and the "
                                 "local columns inside [0, N_global)");
   return GMLP_OK;
 }
@@ -306,9 +307,9 @@ static DropoutParams make_dropout(const gmlp_problem_t* p) {
   d.col0_global = p->col0_global;
   d.ncols_global = p->N_global ? p->N_global : p->N;
   if (p->dropout_p > 0.0f) {
-    // floor(p * 2^32), evaluated in double so the CPU restatement agrees bit for bit.
-    double t = static_cast<double>(p->dropout_p) * 4294967296.0;
-    if (t > 4294967295.0) t = 4294967295.0;
+    // floor(p * 2^16), evaluated in double so the CPU restatement agrees bit for bit.
+    double t = static_cast<double>(p->dropout_p) * 65536.0;
+    if (t > 65535.0) t = 65535.0;
     d.thresh = static_cast<uint32_t>(t);
     d.scale = 1.0f / (1.0f - p->dropout_p);
     d.seed_lo = static_cast<uint32_t>(p->seed);
@@ -536,12 +537,12 @@ int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if (!mask) return fail(GMLP_ERR_ARG, "NULL mask pointer");
-  if ((reinterpret_cast<uintptr_t>(mask) & 3u) != 0)
-    return fail(GMLP_ERR_ALIGN, "mask must be 4-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(mask) & 7u) != 0)
+    return fail(GMLP_ERR_ALIGN, "mask must be 8-byte aligned");
   const DeviceInfo* dev;
   if ((rc = device_info(&dev))) return rc;
   const DropoutParams d = make_dropout(p);
-  const long long quads = p->M * (p->N / 4);
+  const long long quads = p->M * (p->N / 8);
   long long blocks = (quads + 255) / 256;
   const long long cap = static_cast<long long>(dev->sm_count) * 16;
   if (blocks > cap) blocks = cap;

@@ -3,12 +3,15 @@
 //
 //   e      = global_row * N_global + global_col        (element index in the
 //            un-sharded hidden state H[M_global, N_global])
-//   r[0:4] = Philox4x32-10(counter = (lo32(e>>2), hi32(e>>2), lo32(offset),
+//   r[0:4] = Philox4x32-10(counter = (lo32(e>>3), hi32(e>>3), lo32(offset),
 //            hi32(offset)), key = (lo32(seed), hi32(seed)))
-//   keep   = r[e & 3] >= floor(p * 2^32);   kept values are scaled by 1/(1-p)
+//   u16    = the (e & 1)-th 16-bit half (0 = low) of word r[(e & 7) >> 1]
+//   keep   = u16 >= floor(p * 2^16);   kept values are scaled by 1/(1-p)
 //
-// The mask depends only on (seed, offset, e): not on tiling, not on forward
-// versus backward, not on how tokens or intermediate columns are sharded.
+// One Philox call serves 8 consecutive elements (sixteen random bits each, so p is
+// honoured to within 2^-16). The mask depends only on (seed, offset, e): not on
+// tiling, not on forward versus backward, not on how tokens or intermediate columns
+// are sharded.
 #pragma once
 #include <stdint.h>
 
@@ -42,7 +45,7 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t 
 }
 
 struct DropoutParams {
-  uint32_t thresh;      // floor(p * 2^32); 0 disables dropout
+  uint32_t thresh;      // floor(p * 2^16); 0 disables dropout
   float scale;          // 1 / (1 - p)
   uint32_t seed_lo, seed_hi, off_lo, off_hi;
   long long row0_global;   // global row of local row 0
@@ -50,10 +53,10 @@ struct DropoutParams {
   long long ncols_global;  // N_global
 };
 
-// Four random words for the 4 consecutive elements starting at element index
-// e4 * 4 (e4 = e >> 2).
-__device__ __forceinline__ Philox4 dropout_words(const DropoutParams& d, unsigned long long e4) {
-  return philox4x32_10(static_cast<uint32_t>(e4), static_cast<uint32_t>(e4 >> 32), d.off_lo,
+// Four random words (eight 16-bit lanes) for the 8 consecutive elements starting at
+// element index e8 * 8 (e8 = e >> 3).
+__device__ __forceinline__ Philox4 dropout_words(const DropoutParams& d, unsigned long long e8) {
+  return philox4x32_10(static_cast<uint32_t>(e8), static_cast<uint32_t>(e8 >> 32), d.off_lo,
                        d.off_hi, d.seed_lo, d.seed_hi);
 }
 
