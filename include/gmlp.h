@@ -168,12 +168,6 @@ int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, i
  * tcgen05 cta_group::2). Returns the previous mode; other values only query. */
 int gmlp_set_cta_pair_mode(int mode);
 
-/* Tuning / test hook with no counterpart in the reference: how the plain-store GEMMs
- * (down projection, dX, weight gradients) write their output. 0 (default) = per problem
- * (row-wise direct stores behind long reductions, TMA-staged block stores behind short
- * ones), 1 = always direct, 2 = always TMA-staged. Returns the previous mode. */
-int gmlp_set_store_mode(int mode);
-
 /* Tuning hook with no counterpart in the reference (the reference autotunes its
  * GROUP_SIZE_M, src/triton_gated_mlp/ops/fwd.py:48-62): row tiles per raster
  * group of the persistent tile order; 0 restores the built-in default. Returns

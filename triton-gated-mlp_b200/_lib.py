@@ -18,7 +18,7 @@ GMLP_BF16, GMLP_FP16 = 0, 1
 EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
-    "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group", "gmlp_set_store_mode",
+    "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group",
     "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
 
@@ -62,7 +62,6 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_decode_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_set_cta_pair_mode.argtypes = [i32]
     lib.gmlp_set_raster_group.argtypes = [i32]
-    lib.gmlp_set_store_mode.argtypes = [i32]
     lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]
     lib.gmlp_last_error.restype = C.c_char_p
     lib.gmlp_version.restype = C.c_int
@@ -139,8 +138,3 @@ def set_cta_pair_mode(mode: int) -> int:
 def set_raster_group(row_tiles: int) -> int:
     """Row tiles per raster group of the persistent tile order (0 = default); returns the previous value."""
     return load().gmlp_set_raster_group(int(row_tiles))
-
-
-def set_store_mode(mode: int) -> int:
-    """Plain-store GEMM output path: 0 = per problem, 1 = direct stores, 2 = TMA-staged; returns the previous mode."""
-    return load().gmlp_set_store_mode(int(mode))

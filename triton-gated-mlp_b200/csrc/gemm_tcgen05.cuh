@@ -24,7 +24,6 @@ enum : int {
   EPI_STORE = 0,    // C (+ bias[n]) (+ residual[m, n])            -> out0 / out1 (per batch)
   EPI_SWIGLU = 1,   // accumulator = [gate | up] per tile; H = dropout(silu(g) * u)
   EPI_DHIDDEN = 2,  // accumulator = dH; reads G, U; writes dGate, dUp
-  EPI_STORE_TMA = 3,  // EPI_STORE through staged TMA stores (short reductions, see below)
 };
 
 enum : int {
@@ -64,20 +63,16 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
          : (2 * bn <= 256) ? 256u : 512u;
 }
 
-// Epilogue warps and their staging buffers (see epilogue_tile below). The four warps
-// that share a column part (one per TMEM lane quarter) form a GROUP: together they
-// own all 128 rows of a 16-column unit, stage it as one [128 x 16] block (4 KB) and
-// one of them issues one TMA operation for it.
+// Epilogue warps and their staging buffers (see "Epilogue I/O" below).
 constexpr int EPI_WARPS = 16;
-constexpr int EPI_PARTS = EPI_WARPS / 4;                  // groups
-constexpr int STAGE_BUF_BYTES = 128 * 32;                 // 128 rows x 16 sixteen-bit values
-constexpr int STAGE_RING = 4;                             // buffers per group
-constexpr int STAGING_BYTES = EPI_PARTS * STAGE_RING * STAGE_BUF_BYTES;  // 64 KB
+constexpr int EPI_PARTS = EPI_WARPS / 4;                  // column parts of a tile
+constexpr int BLK_BYTES = 32 * 32;                        // one warp's [32 rows x 16 columns] 16-bit block
+constexpr int STAGING_BYTES = EPI_WARPS * 2 * BLK_BYTES;  // two blocks per warp: 32 KB
 
-// Operand ring + (for the staged epilogues) the store staging area + alignment slack.
-template <int BN, int STAGES, int EPI>
+// Operand ring + the epilogue warps' staging blocks + alignment slack.
+template <int BN, int STAGES>
 constexpr size_t gemm_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + (EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? 96 * 1024 : STAGING_BYTES)) + 1024;
+  return static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + STAGING_BYTES + 1024;
 }
 
 // ------------------------------------------------------------ small helpers --
@@ -170,19 +165,25 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
   return c;
 }
 
-// Epilogue warps: EPI_WARPS = 16, four per TMEM lane quarter. Warp e (0..15) reads
-// lanes 32 * (e & 3) and column part (e >> 2) of the tile.
+// ------------------------------------------------------------ Epilogue I/O ----
+// EPI_WARPS = 16 epilogue warps, four per TMEM lane quarter: warp e (0..15) reads TMEM
+// lanes 32 * (e & 3) and column part (e >> 2) of the tile, in units of 16 columns.
 //
-// Output path. A thread owns one output ROW, so writing its values straight to global
-// memory makes every store instruction touch 32 different cache lines with 16 bytes
-// each; measured on the training shape, each extra output matrix written that way cost
-// as much as a third of the whole GEMM. Instead the four warps of a group stage a
-// [128 rows x 16 columns] block (4 KB, 32-byte rows, 32-byte swizzle) in shared memory
-// and one thread hands it to the TMA store engine, which writes full 32-byte sectors,
-// clips rows >= M and columns >= N by itself and runs asynchronously. Blocks are this
-// large because the TMA engine of an SM retires roughly one operation per 90 cycles:
-// with one [32 x 16] block per warp the dH epilogue alone needed 256 operations per
-// tile and ran at exactly that rate.
+// After tcgen05.ld a thread owns one output ROW. Moving data between global memory and
+// that layout directly makes every 16-byte access of a warp touch 32 different cache
+// lines, half a sector each; measured on the training shape, each extra matrix written
+// that way cost a third of the whole GEMM. Routing the blocks through the TMA engine
+// instead ran into its request rate (about one row of a box per cycle, so 32-byte rows
+// waste three quarters of it and the dH kernel's epilogue alone used up the whole
+// budget its operand loads need). So the epilogue keeps to the load/store unit and
+// fixes the access pattern: every warp owns two 1 KB staging blocks ([32 rows x 16
+// columns], 32-byte rows) in shared memory and transposes through them, so that in
+// global memory two neighbouring lanes cover one row's 32 bytes and one instruction
+// moves 16 full sectors.
+//   row view        lane r holds row r:            bytes [32 r, 32 r + 32)
+//   coalesced view  lane l, step t in {0, 1}:      row (l >> 1) + 16 t, 16-byte half l & 1
+// The two halves of a row swap places in rows 4..7 of every group of 8 (a 32-byte
+// swizzle), which keeps both views free of bank conflicts.
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
   float2 a = Pack2<T>::unpack(q.x), b = Pack2<T>::unpack(q.y), c = Pack2<T>::unpack(q.z),
@@ -199,118 +200,118 @@ __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   q.w = Pack2<T>::pack(v[6], v[7]);
   return q;
 }
-
-__device__ __forceinline__ void group_sync(int gid) {
-  asm volatile("bar.sync %0, 128;" ::"r"(gid) : "memory");  // the four warps of one group
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 q;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+               : "r"(addr)
+               : "memory");
+  return q;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& q) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(q.x), "r"(q.y),
+               "r"(q.z), "r"(q.w)
+               : "memory");
 }
 
-// A group's ring of staging buffers and the bookkeeping for its TMA stores. Every
-// member of the group holds a copy and calls the same sequence of methods.
-struct StoreRing {
-  uint32_t base;     // shared::cta address of this group's STAGE_RING buffers
-  uint32_t row_off;  // byte offset of this thread's row inside a block
-  uint32_t sw;       // 32-byte swizzle of that row: 16 when its two halves swap places
-  int next;          // buffer the next block goes to
-  int gid;           // named barrier of the group
-  bool issuer;       // the one thread of the group that talks to the TMA engine
+// Addressing of one warp's staging blocks for one lane.
+struct BlockView {
+  uint32_t row_lo, row_hi;   // row view: offsets of this lane's two 16-byte halves
+  uint32_t co[2];            // coalesced view: offset of this lane's 16 bytes in step t
+  int crow[2];               // coalesced view: row inside the block in step t
+  int chalf;                 // coalesced view: which 8-column half this lane covers
 
-  __device__ __forceinline__ uint32_t current() const { return base + next * STAGE_BUF_BYTES; }
-  // This thread's 16 values (two 16-byte halves) of its row. In the swizzled layout the
-  // halves swap places in rows 4..7 of every group of 8, which spreads a warp's 16-byte
-  // accesses over all banks.
-  __device__ __forceinline__ void write(uint32_t buf, const uint4& lo, const uint4& hi) const {
-    st_shared_v4(buf + row_off + sw, lo);
-    st_shared_v4(buf + row_off + (16u ^ sw), hi);
-  }
-  // Hand the filled buffer to the TMA engine: block origin (col, row0) in the output.
-  // Before the group barrier the issuer makes sure the buffer that comes NEXT is no
-  // longer being read (it was used STAGE_RING - 1 flushes ago), so after the barrier
-  // every member may start filling it.
-  __device__ __forceinline__ void flush(uint32_t buf, const CUtensorMap* map, int col, int row0) {
-    fence_proxy_async_smem();  // generic-proxy writes above -> visible to the async proxy
-    if (issuer) tma_store_wait_read<STAGE_RING - 2>();
-    group_sync(gid);
-    if (issuer) {
-      tma_store_2d(map, buf, col, row0);
-      tma_store_commit();
+  __device__ __forceinline__ explicit BlockView(int lane) {
+    const uint32_t sw = static_cast<uint32_t>((lane >> 2) & 1) << 4;
+    row_lo = lane * 32 + sw;
+    row_hi = lane * 32 + (16u ^ sw);
+    chalf = lane & 1;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      crow[t] = (lane >> 1) + 16 * t;
+      const uint32_t csw = static_cast<uint32_t>((crow[t] >> 2) & 1) << 4;
+      co[t] = crow[t] * 32 + ((static_cast<uint32_t>(chalf) << 4) ^ csw);
     }
-    next = (next + 1) % STAGE_RING;
-  }
-  __device__ __forceinline__ void drain() const {
-    if (issuer) tma_store_wait_all();
   }
 };
 
+// Store this warp's [32 x 16] block whose row `lane` is (lo, hi): rows row0.. of `out`,
+// columns col..col+15; rows >= M and 8-column halves at or beyond N are skipped.
+// `buf` must not be in use by an earlier call that is not separated from this one by a
+// __syncwarp(); alternate between the warp's two blocks.
+template <typename T>
+__device__ __forceinline__ void store_block(const BlockView& bv, uint32_t buf, T* out, long long ld,
+                                            int row0, int col, int M, int N, const uint4& lo,
+                                            const uint4& hi) {
+  st_shared_v4(buf + bv.row_lo, lo);
+  st_shared_v4(buf + bv.row_hi, hi);
+  __syncwarp();
+  const int c = col + bv.chalf * 8;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const uint4 v = ld_shared_v4(buf + bv.co[t]);
+    const int r = row0 + bv.crow[t];
+    if (r < M && c < N) *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * ld + c) = v;
+  }
+}
+// First half of a block load: this lane's two 16-byte pieces in the coalesced view
+// (zero where the block leaves the matrix). Issued one unit ahead of use.
+template <typename T>
+__device__ __forceinline__ void fetch_block(const BlockView& bv, const T* in, long long ld, int row0,
+                                            int col, int M, int N, uint4 (&v)[2]) {
+  const int c = col + bv.chalf * 8;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r = row0 + bv.crow[t];
+    v[t] = make_uint4(0u, 0u, 0u, 0u);
+    if (r < M && c < N) v[t] = __ldg(reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * ld + c));
+  }
+}
+// Second half: through the staging block into the row view. The caller places a
+// __syncwarp() between spill_block and read_row.
+__device__ __forceinline__ void spill_block(const BlockView& bv, uint32_t buf, const uint4 (&v)[2]) {
+  st_shared_v4(buf + bv.co[0], v[0]);
+  st_shared_v4(buf + bv.co[1], v[1]);
+}
+__device__ __forceinline__ void read_row(const BlockView& bv, uint32_t buf, uint4& lo, uint4& hi) {
+  lo = ld_shared_v4(buf + bv.row_lo);
+  hi = ld_shared_v4(buf + bv.row_hi);
+}
+
 // Epilogue of one 128-row accumulator tile, executed by one warp for its 32 TMEM
-// lanes and its part of the tile's columns: lane i owns output row
-// tile_row0 + 32 * quarter + i and walks the columns in units of 16. `taddr` addresses
-// (lane quarter, first accumulator column of the tile). All four warps of a group
-// execute the same sequence of ring flushes (the conditions around them depend on
-// columns only, never on the warp's rows).
+// lanes and its part of the tile's columns: lane i owns output row row0 + i and walks
+// the columns in units of 16. `taddr` addresses (lane quarter, first accumulator column
+// of the tile); `stage` is the warp's pair of staging blocks.
 template <int BN, int EPI, typename T>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int tile_row0,
-                                              int quarter, int lane, int batch, int n0, int part,
-                                              StoreRing& ring, const CUtensorMap* mo0,
-                                              const CUtensorMap* mo1, const CUtensorMap* mo2,
-                                              const T* in0, const T* in1, const T* bias0,
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row0,
+                                              int lane, int batch, int n0, int part,
+                                              const BlockView& bv, uint32_t stage, const T* bias0,
                                               const T* bias1, bool drop_on) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
   static_assert(NU >= 1, "tile too narrow for the column parts");
-  const int row = tile_row0 + quarter * 32 + lane;
+  const int row = row0 + lane;
   const bool row_ok = row < args.M;
   const int u0 = part * NU;
+  const int M = args.M, N = args.N;
+  int flip = 0;  // which of the two staging blocks the next store uses
+  auto next_block = [&]() {
+    const uint32_t b = stage + flip * BLK_BYTES;
+    flip ^= 1;
+    return b;
+  };
 
   if (EPI == EPI_STORE) {
-    // One output matrix behind a long main loop: direct 16-byte stores keep up (the
-    // tensor pipe stays above 95 % busy), so this path spends no shared memory on
-    // staging and keeps a deeper operand ring instead.
-    T* const out = static_cast<T*>(batch ? args.out1 : args.out0) + static_cast<long long>(row) * args.ld_out;
-    const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
+    T* const out = static_cast<T*>(batch ? args.out1 : args.out0);
+    const T* const res =
+        args.in0 ? static_cast<const T*>(args.in0) + static_cast<long long>(row) * args.ld_in : nullptr;
 #pragma unroll
     for (int ui = 0; ui < NU; ++ui) {
       const int col = n0 + (u0 + ui) * 16;
       uint32_t acc[16];
       tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
       tmem_ld_wait();
-      if (row_ok && col < args.N) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int gc = col + j * 8;
-          if (gc < args.N) {
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
-            if (bias0) {
-              float b[8];
-              load8(bias0 + gc, b);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += b[i];
-            }
-            if (res) {
-              float b[8];
-              load8(res + gc, b);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += b[i];
-            }
-            store8(out + gc, v);
-          }
-        }
-      }
-    }
-  } else if (EPI == EPI_STORE_TMA) {
-    // Same result as EPI_STORE. When the reduction is short the main loop of a tile is
-    // too brief to hide row-wise global stores, so the block goes out through the
-    // staging ring and the TMA store engine instead (at the price of one ring stage).
-    const CUtensorMap* mo = batch ? mo1 : mo0;
-    const T* const res = in0 ? in0 + static_cast<long long>(row) * args.ld_in : nullptr;
-#pragma unroll
-    for (int ui = 0; ui < NU; ++ui) {
-      const int col = n0 + (u0 + ui) * 16;
-      uint32_t acc[16];
-      tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
-      tmem_ld_wait();
-      if (col < args.N) {  // uniform over the group
+      if (col < N && row0 < M) {  // warp-uniform
         uint4 q[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -318,7 +319,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
           float v[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
-          if (gc < args.N) {
+          if (gc < N) {
             if (bias0) {
               float b[8];
               load8(bias0 + gc, b);
@@ -334,12 +335,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
           }
           q[j] = pack8<T>(v);
         }
-        const uint32_t buf = ring.current();
-        ring.write(buf, q[0], q[1]);
-        ring.flush(buf, mo, col, tile_row0);
+        store_block<T>(bv, next_block(), out, args.ld_out, row0, col, M, N, q[0], q[1]);
       }
     }
   } else if (EPI == EPI_SWIGLU) {
+    T* const out_h = static_cast<T*>(args.out0);
+    T* const out_g = static_cast<T*>(args.out1);
+    T* const out_u = static_cast<T*>(args.out2);
     const long long grow = args.drop.row0_global + row;
 #pragma unroll
     for (int ui = 0; ui < NU; ++ui) {
@@ -348,7 +350,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
       tmem_ld_32x16(taddr + (u0 + ui) * 16, rg);
       tmem_ld_32x16(taddr + TILE_N + (u0 + ui) * 16, ru);
       tmem_ld_wait();
-      if (col < args.N) {  // uniform over the group
+      if (col < N && row0 < M) {  // warp-uniform
         uint4 qh[2], qg[2], qu[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -359,7 +361,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
             g[i] = __uint_as_float(rg[j * 8 + i]);
             u[i] = __uint_as_float(ru[j * 8 + i]);
           }
-          if (gc < args.N) {
+          if (gc < N) {
             if (bias0) {
               float b[8];
               load8(bias0 + gc, b);
@@ -373,7 +375,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
               for (int i = 0; i < 8; ++i) u[i] += b[i];
             }
           }
-          if (mo1) {  // keep the pre-activations for the backward pass
+          if (out_g) {  // keep the pre-activations for the backward pass
             qg[j] = pack8<T>(g);
             qu[j] = pack8<T>(u);
           }
@@ -387,87 +389,108 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
           }
           qh[j] = pack8<T>(h);
         }
-        uint32_t buf = ring.current();
-        ring.write(buf, qh[0], qh[1]);
-        ring.flush(buf, mo0, col, tile_row0);
-        if (mo1) {
-          buf = ring.current();
-          ring.write(buf, qg[0], qg[1]);
-          ring.flush(buf, mo1, col, tile_row0);
-          buf = ring.current();
-          ring.write(buf, qu[0], qu[1]);
-          ring.flush(buf, mo2, col, tile_row0);
+        store_block<T>(bv, next_block(), out_h, args.ld_out, row0, col, M, N, qh[0], qh[1]);
+        if (out_g) {
+          store_block<T>(bv, next_block(), out_g, args.ld_out, row0, col, M, N, qg[0], qg[1]);
+          store_block<T>(bv, next_block(), out_u, args.ld_out, row0, col, M, N, qu[0], qu[1]);
         }
       }
     }
+  } else {  // EPI_DHIDDEN
+    T* const out_g = static_cast<T*>(args.out0);
+    T* const out_u = static_cast<T*>(args.out1);
+    const T* const in_g = static_cast<const T*>(args.in0);
+    const T* const in_u = static_cast<const T*>(args.in1);
+    const long long grow = args.drop.row0_global + row;
+    const uint32_t buf_g = stage, buf_u = stage + BLK_BYTES;
+    uint4 pg[2], pu[2];  // G and U of the next unit, coalesced view, in flight
+    fetch_block<T>(bv, in_g, args.ld_in, row0, n0 + u0 * 16, M, N, pg);
+    fetch_block<T>(bv, in_u, args.ld_in, row0, n0 + u0 * 16, M, N, pu);
+#pragma unroll
+    for (int ui = 0; ui < NU; ++ui) {
+      const int col = n0 + (u0 + ui) * 16;
+      uint32_t acc[16];
+      tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
+      __syncwarp();  // the previous unit's coalesced reads of both blocks are done
+      spill_block(bv, buf_g, pg);
+      spill_block(bv, buf_u, pu);
+      if (ui + 1 < NU) {
+        fetch_block<T>(bv, in_g, args.ld_in, row0, col + 16, M, N, pg);
+        fetch_block<T>(bv, in_u, args.ld_in, row0, col + 16, M, N, pu);
+      }
+      __syncwarp();
+      uint4 gq[2], uq[2];
+      read_row(bv, buf_g, gq[0], gq[1]);
+      read_row(bv, buf_u, uq[0], uq[1]);
+      tmem_ld_wait();
+      uint4 qg[2], qu[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int gc = col + j * 8;
+        float dh[8], g[8], u[8], dg[8], du[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(acc[j * 8 + i]);
+        unpack8<T>(gq[j], g);
+        unpack8<T>(uq[j], u);
+        if (drop_on) {
+          float f[8];
+          dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dh[i] *= f[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float sg = sigmoid_f(g[i]);
+          du[i] = dh[i] * g[i] * sg;
+          dg[i] = dh[i] * u[i] * sg * (1.0f + g[i] * (1.0f - sg));
+        }
+        qg[j] = pack8<T>(dg);
+        qu[j] = pack8<T>(du);
+      }
+      // In place: each lane overwrites the row it has just read, then the block leaves in
+      // the coalesced view.
+      store_block<T>(bv, buf_g, out_g, args.ld_out, row0, col, M, N, qg[0], qg[1]);
+      store_block<T>(bv, buf_u, out_u, args.ld_out, row0, col, M, N, qu[0], qu[1]);
+    }
   }
-}
-
-// --------------------------------------------------------- dH epilogue (B1) ----
-// The dH epilogue needs G and U at the accumulator's positions. Reading them row by
-// row from global memory has the same problem as writing row by row, so each group
-// brings them in with TMA as [128 x 16] blocks, one 8 KB (G, U) buffer pair per
-// 16-column unit, computes dGate / dUp in place (each thread overwrites exactly the 32
-// bytes of G and of U it has just read) and hands the same buffers to the TMA store
-// engine. Three pairs per group: the loads of unit k+1 are in flight while unit k is
-// computed and while the stores of unit k-1 drain. The prefetch runs across tile
-// boundaries, since G and U do not depend on the GEMM.
-constexpr int DH_PAIRS = 3;
-constexpr int DH_PAIR_BYTES = 2 * STAGE_BUF_BYTES;
-constexpr int DH_STAGING_BYTES = EPI_PARTS * DH_PAIRS * DH_PAIR_BYTES;  // 96 KB
-static_assert(DH_STAGING_BYTES == 96 * 1024, "keep gemm_smem_bytes in step");
-
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 q;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-               : "r"(addr)
-               : "memory");
-  return q;
 }
 
 // The epilogue role of one warp for all tiles of its CTA (or CTA pair).
 //   TILE_M     rows per tile: 128, or 256 for a CTA pair (row_off = cluster rank * 128)
 //   tfull0 / tempty0   shared::cta addresses of tfull[0] / tempty[0] ([1] is 8 bytes on)
 //   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
-//   epi_smem   this CTA's epilogue staging area; lbar0: DH_PAIRS load barriers per group
-//   grp_abort  one word per group, written by the group's issuer warp only
-//
-// Staged epilogues synchronise the four warps of a group with named barriers, which
-// have no time limit. To keep every wait in the kernel bounded, only the group's issuer
-// warp (lane quarter 0) waits on mbarriers; it publishes the outcome in grp_abort before
-// the next group barrier and all four warps act on that one word, so they always take
-// the same way out.
+//   epi_smem   this CTA's epilogue staging area (two blocks per epilogue warp)
 template <int BN, int EPI, typename T, int TILE_M, bool REMOTE>
-__device__ __forceinline__ void epilogue_role(
-    const GemmArgs& args, int warp, int lane, int first_tile, int tile_stride, int total_tiles,
-    int m_tiles, int n_tiles, int row_off, uint32_t tmem_base, uint32_t tfull0, uint32_t tempty0,
-    uint32_t epi_smem, uint32_t lbar0, int* grp_abort_all, const CUtensorMap* mo0,
-    const CUtensorMap* mo1_in, const CUtensorMap* mo2, const CUtensorMap* mi0,
-    const CUtensorMap* mi1, int* abort_flag) {
+__device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, int lane,
+                                              int first_tile, int tile_stride, int total_tiles,
+                                              int m_tiles, int n_tiles, int row_off,
+                                              uint32_t tmem_base, uint32_t tfull0,
+                                              uint32_t tempty0, uint32_t epi_smem,
+                                              int* abort_flag) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-  constexpr bool GROUPED = (EPI != EPI_STORE);
   volatile int* abortp = abort_flag;
-  const int ew = warp - 2;          // epilogue warp index 0..15
-  const int quarter = warp & 3;     // TMEM lanes this warp may read
+  const int ew = warp - 2;       // epilogue warp index 0..15
+  const int quarter = warp & 3;  // TMEM lanes this warp may read
   const int col_part = ew >> 2;
-  const int gid = 1 + col_part;     // named barrier of this warp's group
-  const bool issuer_warp = quarter == 0;
-  const bool issuer = issuer_warp && lane == 0;
-  volatile int* grp_abort = grp_abort_all + col_part;
   const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-  const uint32_t row_off_bytes = static_cast<uint32_t>(quarter * 32 + lane) * 32u;
-  const uint32_t sw = static_cast<uint32_t>((lane >> 2) & 1) << 4;
-  const T* const in0 = static_cast<const T*>(args.in0);
-  const T* const in1 = static_cast<const T*>(args.in1);
   const T* const bias0 = static_cast<const T*>(args.bias0);
   const T* const bias1 = static_cast<const T*>(args.bias1);
-  const CUtensorMap* const mo1 = (EPI == EPI_STORE_TMA || args.out1) ? mo1_in : nullptr;
   const bool drop_on = args.drop.thresh != 0u;
+  const BlockView bv(lane);
+  const uint32_t stage = epi_smem + ew * (2 * BLK_BYTES);
   bool ok = true;
   int local = 0;
-
-  auto release_tmem = [&](int acc) {
+  for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
+    const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+    const int acc = local & 1;
+    ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem_base + acc * BN + lane_addr;
+    const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
+    epilogue_tile<BN, EPI, T>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
+                              bias0, bias1, drop_on);
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
     // semantics; no fence is placed here on purpose, since a fence would also wait for
@@ -477,139 +500,6 @@ __device__ __forceinline__ void epilogue_role(
       if (REMOTE) mbar_arrive_cluster(mapa_shared(tempty0 + 8u * acc, 0));
       else mbar_arrive(tempty0 + 8u * acc);
     }
-  };
-  // Wait for the accumulator of the warp's `local`-th tile; false = give up.
-  auto wait_tile = [&](int acc) -> bool {
-    if (!GROUPED) {
-      bool w = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
-      return __all_sync(0xffffffffu, w);
-    }
-    if (issuer_warp) {
-      bool w = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
-      w = __all_sync(0xffffffffu, w);
-      if (lane == 0) *grp_abort = (!w || *abortp != 0) ? 1 : 0;
-    }
-    group_sync(gid);
-    const bool go = *grp_abort == 0;
-    group_sync(gid);  // nobody reads the word after this point until it is written again
-    return go;
-  };
-
-  if (EPI != EPI_DHIDDEN) {
-    StoreRing ring{epi_smem + col_part * (STAGE_RING * STAGE_BUF_BYTES), row_off_bytes, sw, 0, gid, issuer};
-    for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
-      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
-      const int acc = local & 1;
-      ok = wait_tile(acc);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + lane_addr;
-      epilogue_tile<BN, EPI, T>(args, taddr, tc.m_tile * TILE_M + row_off, quarter, lane, tc.batch,
-                                tc.n_tile * TILE_N, col_part, ring, mo0, mo1, mo2, in0, in1, bias0,
-                                bias1, drop_on);
-      release_tmem(acc);
-    }
-    if (GROUPED) ring.drain();  // shared memory must stay valid until TMA has read it
-  } else {
-    constexpr int NU = BN / 16 / EPI_PARTS;  // 16-column units per group and tile
-    const uint32_t grp_smem = epi_smem + col_part * (DH_PAIRS * DH_PAIR_BYTES);
-    const uint32_t grp_bar = lbar0 + 8u * (col_part * DH_PAIRS);
-    // Origin (first row of this CTA's 128-row slab, first column of this group's part) of
-    // `tile`: decoded once per tile, never per unit (decode_tile divides by run-time values).
-    auto tile_origin = [&](int tile, int& row0, int& col0) {
-      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
-      row0 = tc.m_tile * TILE_M + row_off;
-      col0 = tc.n_tile * TILE_N + col_part * NU * 16;
-    };
-    // Issue the G / U loads of unit number k, block origin (col, row0) (issuer only).
-    auto issue_load = [&](int k, int row0, int col) {
-      const int p = k % DH_PAIRS;
-      // This runs before the stores of unit k-1 are issued. The pair was last read by the
-      // two stores of unit k-3; the only groups committed since are the two of unit k-2.
-      tma_store_wait_read<2>();
-      const uint32_t buf = grp_smem + p * DH_PAIR_BYTES;
-      const uint32_t bar = grp_bar + 8u * p;
-      mbar_expect_tx(bar, DH_PAIR_BYTES);
-      tma_load_2d(buf, mi0, bar, col, row0);
-      tma_load_2d(buf + STAGE_BUF_BYTES, mi1, bar, col, row0);
-    };
-    int k = 0;
-    int row0 = 0, col0 = 0, next_row0 = 0, next_col0 = 0;
-    if (first_tile < total_tiles) {
-      tile_origin(first_tile, row0, col0);
-      if (issuer) issue_load(0, row0, col0);
-    }
-    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++local) {
-      const bool has_next = tile + tile_stride < total_tiles;
-      if (has_next) tile_origin(tile + tile_stride, next_row0, next_col0);
-      const int acc = local & 1;
-      ok = wait_tile(acc);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * BN + lane_addr + col_part * NU * 16;
-      const long long grow = args.drop.row0_global + row0 + quarter * 32 + lane;
-#pragma unroll 1
-      for (int ui = 0; ui < NU; ++ui, ++k) {
-        // prefetch the next unit's G and U (possibly the first unit of the next tile)
-        if (issuer) {
-          if (ui + 1 < NU) issue_load(k + 1, row0, col0 + (ui + 1) * 16);
-          else if (has_next) issue_load(k + 1, next_row0, next_col0);
-        }
-        const int col = col0 + ui * 16;
-        uint32_t acc_r[16];
-        tmem_ld_32x16(taddr + ui * 16, acc_r);
-        const int p = k % DH_PAIRS;
-        if (issuer_warp) {
-          bool w = mbar_wait(grp_bar + 8u * p, (k / DH_PAIRS) & 1, abortp);
-          w = __all_sync(0xffffffffu, w);
-          if (lane == 0) *grp_abort = (!w || *abortp != 0) ? 1 : 0;
-        }
-        group_sync(gid);  // G and U of this unit have landed (or the group gives up)
-        tmem_ld_wait();
-        if (*grp_abort != 0) {
-          ok = false;
-          break;
-        }
-        const uint32_t gbuf = grp_smem + p * DH_PAIR_BYTES + row_off_bytes;
-        const uint32_t ubuf = gbuf + STAGE_BUF_BYTES;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          float dh[8], g[8], u[8], dg[8], du[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) dh[i] = __uint_as_float(acc_r[j * 8 + i]);
-          unpack8<T>(ld_shared_v4(gbuf + ((j * 16) ^ sw)), g);
-          unpack8<T>(ld_shared_v4(ubuf + ((j * 16) ^ sw)), u);
-          if (drop_on) {
-            float f[8];
-            dropout_factors8(args.drop, grow, args.drop.col0_global + col + j * 8, f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dh[i] *= f[i];
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float sg = sigmoid_f(g[i]);
-            du[i] = dh[i] * g[i] * sg;
-            dg[i] = dh[i] * u[i] * sg * (1.0f + g[i] * (1.0f - sg));
-          }
-          st_shared_v4(gbuf + ((j * 16) ^ sw), pack8<T>(dg));
-          st_shared_v4(ubuf + ((j * 16) ^ sw), pack8<T>(du));
-        }
-        fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA store
-        group_sync(gid);
-        if (issuer) {
-          // Rows >= M and columns >= N of a block are clipped by the hardware.
-          tma_store_2d(mo0, grp_smem + p * DH_PAIR_BYTES, col, row0);
-          tma_store_commit();
-          tma_store_2d(mo1_in, grp_smem + p * DH_PAIR_BYTES + STAGE_BUF_BYTES, col, row0);
-          tma_store_commit();
-        }
-      }
-      if (!ok) break;
-      release_tmem(acc);
-      row0 = next_row0;
-      col0 = next_col0;
-    }
-    if (issuer) tma_store_wait_all();
   }
   if (!ok && lane == 0) {
     *abort_flag = 1;
@@ -623,12 +513,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
                     const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0,
-                    const __grid_constant__ CUtensorMap tmB1,
-                    const __grid_constant__ CUtensorMap tmO0,
-                    const __grid_constant__ CUtensorMap tmO1,
-                    const __grid_constant__ CUtensorMap tmO2,
-                    const __grid_constant__ CUtensorMap tmI0,
-                    const __grid_constant__ CUtensorMap tmI1, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N range for M = 128");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 64 == 0, "MN-major B arrives in 64-column boxes");
@@ -647,9 +532,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
-  // dH epilogue only: one barrier per (epilogue group, G/U buffer pair)
-  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_PARTS * DH_PAIRS : 1];
-  __shared__ int grp_abort[EPI_PARTS];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -668,7 +550,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < EPI_PARTS; ++i) grp_abort[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -677,8 +558,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), EPI_WARPS);  // one arrival per epilogue warp
     }
-    if (EPI == EPI_DHIDDEN)
-      for (int i = 0; i < EPI_PARTS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -792,8 +671,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
     // ------------------------------------------------------------ epilogue --
     epilogue_role<BN, EPI, T, BM, false>(args, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
                                          n_tiles, 0, tmem_base, tfull_bar(0), tempty_bar(0),
-                                         smem_base + STAGES * STAGE_BYTES, smem_u32(lbars), grp_abort, &tmO0,
-                                         &tmO1, &tmO2, &tmI0, &tmI1, &abort_flag);
+                                         smem_base + STAGES * STAGE_BYTES, &abort_flag);
   }
 
   tc_fence_before_sync();
@@ -821,9 +699,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 //   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
 //              both copies at once.
 //   tempty[a]  lives in the leader, 32 arrivals: the 16 epilogue warps of each CTA.
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES>
 constexpr size_t gemm_pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + (EPI == EPI_STORE ? 0 : (EPI == EPI_DHIDDEN ? 96 * 1024 : STAGING_BYTES)) + 1024;
+  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + STAGING_BYTES + 1024;
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
@@ -831,12 +709,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
                          const __grid_constant__ CUtensorMap tmA1,
                          const __grid_constant__ CUtensorMap tmB0,
-                         const __grid_constant__ CUtensorMap tmB1,
-                         const __grid_constant__ CUtensorMap tmO0,
-                         const __grid_constant__ CUtensorMap tmO1,
-                         const __grid_constant__ CUtensorMap tmO2,
-                    const __grid_constant__ CUtensorMap tmI0,
-                    const __grid_constant__ CUtensorMap tmI1, const GemmArgs args) {
+                         const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tcgen05 N range for M = 256");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
@@ -854,9 +727,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
-  // dH epilogue only: one barrier per (epilogue group, G/U buffer pair)
-  __shared__ __align__(8) uint64_t lbars[EPI == EPI_DHIDDEN ? EPI_PARTS * DH_PAIRS : 1];
-  __shared__ int grp_abort[EPI_PARTS];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -878,7 +748,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < EPI_PARTS; ++i) grp_abort[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -887,8 +756,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 2 * EPI_WARPS);  // the epilogue warps of both CTAs of the pair
     }
-    if (EPI == EPI_DHIDDEN)
-      for (int i = 0; i < EPI_PARTS * DH_PAIRS; ++i) mbar_init(smem_u32(lbars) + 8u * i, 1);
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA0);
@@ -1004,9 +871,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
     // ------------------------------------------------------------ epilogue --
     epilogue_role<BN, EPI, T, PAIR_M, true>(args, warp, lane, pair, num_pairs, total_tiles, m_tiles,
                                             n_tiles, static_cast<int>(rank) * BM, tmem_base, tfull_bar(0),
-                                            tempty_bar(0), smem_base + STAGES * STAGE_BYTES,
-                                            smem_u32(lbars), grp_abort, &tmO0, &tmO1, &tmO2, &tmI0,
-                                            &tmI1, &abort_flag);
+                                            tempty_bar(0), smem_base + STAGES * STAGE_BYTES, &abort_flag);
   }
 
   // Neither CTA may exit (or free TMEM) while its peer can still read its shared

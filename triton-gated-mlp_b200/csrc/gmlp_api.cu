@@ -85,12 +85,10 @@ static int device_info(const DeviceInfo** out) {
 }
 
 // ------------------------------------------------------------- tensor maps --
-// 2-D row-major matrix [outer, inner] of 16-bit elements; operand maps use the
-// 128-byte swizzle (out-of-bounds elements read as zero), epilogue block maps the 32-byte one.
+// 2-D row-major matrix [outer, inner] of 16-bit elements, 128-byte swizzle,
+// out-of-bounds elements read as zero.
 static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
-                      int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype,
-                      bool swizzle128 = true) {
-  // swizzle128 = false: the epilogue's [128 x 16] staging blocks, 32-byte rows, 32-byte swizzle
+                      int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
   const cuuint32_t box[2] = {box_inner, box_outer};
@@ -99,7 +97,7 @@ static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t o
       dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_32B,
+                              CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -157,10 +155,9 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // The CTA-pair kernel works on 256-row tiles; with a single row tile there is
   // nothing for the second CTA to do.
   const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && M > BM);
-  // Shared memory: the operand ring, plus 64 KB of store staging for the epilogues that
-  // write through TMA (everything but the plain store).
-  constexpr int STAGES = (EPI == EPI_STORE) ? 4 : (EPI == EPI_DHIDDEN ? 2 : 3);
-  constexpr int PAIR_STAGES = (EPI == EPI_STORE) ? 6 : (EPI == EPI_DHIDDEN ? 4 : 5);
+  // Shared memory: the operand ring plus 32 KB of staging blocks for the epilogue warps.
+  constexpr int STAGES = 4;
+  constexpr int PAIR_STAGES = 6;
   const uint32_t b_rows = pair ? BN / 2 : ((EPI == EPI_SWIGLU) ? BN / 2 : BN);
   CUtensorMap mA0, mA1, mB0, mB1;
   int rc;
@@ -176,23 +173,8 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   } else {
     mB1 = mB0;
   }
-  // Outputs leave through TMA stores of [128 rows x 16 columns] blocks.
-  CUtensorMap mO0, mO1, mO2;
   if (!ep.out0 || !aligned16(ep.out0) || (ep.ld_out % 8) != 0)
     return fail(GMLP_ERR_ALIGN, "output base / pitch not 16-byte aligned");
-  if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
-  mO1 = mO0;
-  mO2 = mO0;
-  if (ep.out1 && (rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
-  if (ep.out2 && (rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 16, 128, dtype, false))) return rc;
-  // The dH epilogue also reads G and U through TMA, in the same block shape.
-  CUtensorMap mI0 = mO0, mI1 = mO0;
-  if (EPI == EPI_DHIDDEN) {
-    if (!ep.in0 || !ep.in1 || !aligned16(ep.in0) || !aligned16(ep.in1) || (ep.ld_in % 8) != 0)
-      return fail(GMLP_ERR_ALIGN, "G / U base or pitch not 16-byte aligned");
-    if ((rc = encode_map(&mI0, ep.in0, N, M, ep.ld_in, 16, 128, dtype, false))) return rc;
-    if ((rc = encode_map(&mI1, ep.in1, N, M, ep.ld_in, 16, 128, dtype, false))) return rc;
-  }
   GemmArgs args;
   memset(&args, 0, sizeof(args));
   args.M = static_cast<int>(M);
@@ -227,53 +209,37 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   if (pair) {
     const int64_t max_pairs = dev->sm_count / 2;
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-    constexpr size_t smem = gemm_pair_smem_bytes<BN, PAIR_STAGES, EPI>();
+    constexpr size_t smem = gemm_pair_smem_bytes<BN, PAIR_STAGES>();
     auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
     if (e != cudaSuccess)
       return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, mI0, mI1, args);
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
   } else {
     const int grid = static_cast<int>(tiles < dev->sm_count ? tiles : dev->sm_count);
-    constexpr size_t smem = gemm_smem_bytes<BN, STAGES, EPI>();
+    constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
     auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
     if (e != cudaSuccess)
       return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, mI0, mI1, args);
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
 }
 
-// 0 = choose per problem, 1 = plain stores always direct, 2 = always through TMA staging.
-static int g_store_mode = 0;
-
-template <int BN, bool A_MN, bool B_MN, int EPI_IN>
+template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, const Operand& a0,
                        const Operand* a1, const Operand& b0, const Operand* b1, int64_t k1,
                        int batches, const Epilogue& ep, cudaStream_t stream) {
-  if (EPI_IN == EPI_STORE) {
-    // Plain stores: with at most 64 reduction blocks (4096 elements) per tile the main
-    // loop is too short to hide row-wise global stores; use the TMA-staged variant.
-    const int64_t kb = (a0.k + BK - 1) / BK + (k1 + BK - 1) / BK;
-    const bool staged = g_store_mode == 2 || (g_store_mode == 0 && kb <= 64 && M > BM);
-    if (staged) {
-      if (dtype == GMLP_BF16)
-        return launch_gemm_t<BN, A_MN, B_MN, EPI_STORE_TMA, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1,
-                                                                         k1, batches, ep, stream);
-      return launch_gemm_t<BN, A_MN, B_MN, EPI_STORE_TMA, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1,
-                                                                  batches, ep, stream);
-    }
-  }
   if (dtype == GMLP_BF16)
-    return launch_gemm_t<BN, A_MN, B_MN, EPI_IN, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1, k1,
-                                                                batches, ep, stream);
-  return launch_gemm_t<BN, A_MN, B_MN, EPI_IN, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
-                                                       ep, stream);
+    return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1, k1,
+                                                             batches, ep, stream);
+  return launch_gemm_t<BN, A_MN, B_MN, EPI, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
+                                                    ep, stream);
 }
 
 static int check_problem(const gmlp_problem_t* p) {
@@ -339,12 +305,6 @@ int gmlp_version(void) { return 101; }
 int gmlp_set_cta_pair_mode(int mode) {
   const int prev = g_pair_mode;
   if (mode >= 0 && mode <= 2) g_pair_mode = mode;
-  return prev;
-}
-
-int gmlp_set_store_mode(int mode) {
-  const int prev = g_store_mode;
-  if (mode >= 0 && mode <= 2) g_store_mode = mode;
   return prev;
 }
 
@@ -825,4 +785,3 @@ extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, con
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
 }
-

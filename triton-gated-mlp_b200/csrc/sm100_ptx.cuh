@@ -277,34 +277,3 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 }
 
 }  // namespace gmlp
-
-// ------------------------------------------------ TMA stores (smem -> global) --
-namespace gmlp {
-
-// 2-D tiled store of one box from this CTA's shared memory; rows / columns of the
-// box that fall outside the tensor are clipped by the hardware. Issued by one thread;
-// completion is tracked through that thread's bulk async-groups.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// Wait until at most N of this thread's committed groups still READ shared memory.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-// Wait until all of this thread's committed groups have completed.
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& q) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(q.x), "r"(q.y),
-               "r"(q.z), "r"(q.w)
-               : "memory");
-}
-
-}  // namespace gmlp
