@@ -92,3 +92,26 @@ def test_results_are_bitwise_repeatable(pkg, cuda_dev):
     a, _ = _run(pkg, cuda_dev, case, torch.bfloat16, p=0.1, seed=1)
     b, _ = _run(pkg, cuda_dev, case, torch.bfloat16, p=0.1, seed=1)
     assert all(torch.equal(a[k], b[k]) for k in a)
+
+
+def test_host_pipeline_streams_distinct_batches(pkg, cuda_dev):
+    """Pinned host batches through HostPipeline (copies and compute on three streams) give the
+    same bits as calling the module on each batch directly."""
+    case = orc.make_case(256, 256, 512, True, torch.bfloat16, seed=8, w_std=0.03)
+    m = build_module(pkg, case, torch.bfloat16, cuda_dev).eval()
+
+    def step(x_dev):
+        with torch.no_grad():
+            return m(x_dev)
+
+    g = torch.Generator().manual_seed(0)
+    xs = [torch.randn((256, 256), generator=g).to(torch.bfloat16).pin_memory() for _ in range(7)]
+    ys = [torch.empty((256, 256), dtype=torch.bfloat16).pin_memory() for _ in range(7)]
+    pipe = pkg.host_pipeline.HostPipeline(step, cuda_dev, depth=3)
+    for x, y in zip(xs, ys):
+        pipe.submit(y, x)
+    pipe.drain()
+    for x, y in zip(xs, ys):
+        assert torch.equal(y, step(x.to(cuda_dev)).cpu())
+    with pytest.raises(ValueError):
+        pipe.submit(torch.empty(4, 4), torch.empty(4, 4))

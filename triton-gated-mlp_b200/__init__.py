@@ -6,10 +6,10 @@ importable name `triton_gated_mlp_b200` by `load_package()` in the repository's
 `from triton_gated_mlp_b200.gated_mlp import FusedGatedMLP` is the one-line swap
 for `from triton_gated_mlp.gated_mlp import FusedGatedMLP`.
 """
-from . import _lib, build, parallel  # noqa: F401
+from . import _lib, build, host_pipeline, parallel  # noqa: F401
 from .gated_mlp import FusedGatedMLP, FusedGatedMLPFunction, mlp_hidden_states_bwd, mlp_hidden_states_fwd  # noqa: F401
 
 __all__ = [
     "FusedGatedMLP", "FusedGatedMLPFunction", "mlp_hidden_states_fwd", "mlp_hidden_states_bwd",
-    "parallel", "build",
+    "parallel", "build", "host_pipeline",
 ]

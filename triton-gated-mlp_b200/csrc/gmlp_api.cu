@@ -590,7 +590,7 @@ template <int MPAD, bool DUAL, typename T>
 static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
                            const void* w0, const void* w1, const void* act, int64_t act_ld,
                            const void* bias0, const void* bias1, void* out, int64_t ld_out,
-                           float* slots, int* counters, cudaStream_t stream) {
+                           float* slots, int* counters, bool dependent, cudaStream_t stream) {
   CUtensorMap mW0, mW1, mAct;
   int rc;
   if ((rc = encode_map(&mW0, w0, red, rows, red, BK, 128, dtype))) return rc;
@@ -613,6 +613,7 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   a.ld_out = ld_out;
   a.slots = slots;
   a.counters = counters;
+  a.dependent = dependent ? 1 : 0;
   const long long total = ((rows + 127) / 128) * static_cast<long long>(a.kbt);
   const int grid = static_cast<int>(total < dev->sm_count ? total : dev->sm_count);
   constexpr size_t smem = decode_smem_bytes<MPAD, DUAL>();
@@ -621,7 +622,22 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
                                        static_cast<int>(smem));
   if (e != cudaSuccess)
     return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  kfn<<<grid, DECODE_THREADS, smem, stream>>>(mW0, mW1, mAct, a);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(DECODE_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {
+    // Let this grid's CTAs start (and stream weights) while the preceding grid drains.
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  e = cudaLaunchKernelEx(&cfg, kfn, mW0, mW1, mAct, a);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
@@ -671,13 +687,13 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   // H[M,N] = silu(x Wg^T + bg) * (x Wu^T + bu): weight rows = N, reduction = K
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
                            b_gate, b_up, h, p->N, slots,
-                           reinterpret_cast<int*>(sc + l.counters1_off), st);
+                           reinterpret_cast<int*>(sc + l.counters1_off), false, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
                               static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
                               static_cast<const void*>(nullptr), y, p->K, slots,
-                              reinterpret_cast<int*>(sc + l.counters2_off), st);
+                              reinterpret_cast<int*>(sc + l.counters2_off), true, st);
 }
 
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,
