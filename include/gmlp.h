@@ -43,6 +43,19 @@ typedef enum gmlp_status_t {
 
 typedef enum gmlp_dtype_t { GMLP_BF16 = 0, GMLP_FP16 = 1 } gmlp_dtype_t;
 
+/* Gate activations: the names the reference's module accepts (ACT_FWD,
+ * src/triton_gated_mlp/gated_mlp.py:27-37); its fused kernels implement only silu and
+ * no_act (ops/act.py:7-12) and its backward only silu (gated_mlp.py:46-55). */
+typedef enum gmlp_act_t {
+  GMLP_ACT_SILU = 0,       /* also "swish" */
+  GMLP_ACT_NONE = 1,       /* "no_act": h = g * u */
+  GMLP_ACT_RELU = 2,
+  GMLP_ACT_GELU = 3,       /* exact (erf) form, nn.GELU's default */
+  GMLP_ACT_SIGMOID = 4,
+  GMLP_ACT_TANH = 5,
+  GMLP_ACT_LEAKY_RELU = 6  /* negative slope 0.01, nn.LeakyReLU's default */
+} gmlp_act_t;
+
 /* One gated-MLP problem (or one rank's shard of it).
  * Dropout uses the Philox4x32-10 contract of oracle/philox.py: the keep bit of
  * hidden element (row, col) depends only on (seed, offset) and on its GLOBAL
@@ -59,9 +72,11 @@ typedef struct gmlp_problem_t {
   int64_t row0_global;  /* global index of local row 0 (token sharding) */
   int64_t col0_global;  /* global index of local intermediate column 0 (TP sharding) */
   int64_t N_global;     /* un-sharded intermediate size; 0 means N */
+  int32_t act;          /* gmlp_act_t of the gate (0 = SiLU) */
+  int32_t reserved;     /* must be 0 */
 } gmlp_problem_t;
 
-/* H[M,N] = dropout(silu(x W_gate^T + b_gate) * (x W_up^T + b_up)).
+/* H[M,N] = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)), act = p->act (SiLU by default).
  * Replaces mlp_hidden_states_fwd (src/triton_gated_mlp/ops/fwd.py:198-279, kernel
  * :65-166) with the bias and dropout that EagerGatedMLP applies
  * (src/triton_gated_mlp/gated_mlp.py:96). b_gate / b_up may be NULL.
@@ -134,8 +149,8 @@ int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* sr
                        void* dst, void* stream);
 
 /* Skinny-M (decode) forward for M <= 64 tokens, K and N multiples of 64:
- * h[M,N] = silu(x W_gate^T + b_gate) * (x W_up^T + b_up), then y[M,K] = h W_down^T +
- * b_down, as two weight-streaming kernels (HBM-bound; every weight byte is read
+ * h[M,N] = act(x W_gate^T + b_gate) * (x W_up^T + b_up), then y[M,K] = h W_down^T +
+ * b_down (+ residual[M,K], may be NULL), as two weight-streaming kernels (HBM-bound; every weight byte is read
  * once). Covers the same reference interfaces as gmlp_hidden_fwd + gmlp_down_fwd
  * (src/triton_gated_mlp/ops/fwd.py:198-279 and gated_mlp.py:236) for the token
  * counts at which the reference's smallest tile (BLOCK_SIZE_M = 16, ops/fwd.py:49)
@@ -147,8 +162,8 @@ int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* sr
 size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p);
 int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
-                    const void* b_down, void* h, void* y, void* scratch, size_t scratch_bytes,
-                    void* stream);
+                    const void* b_down, const void* residual, void* h, void* y, void* scratch,
+                    size_t scratch_bytes, void* stream);
 
 /* mask[M,N] (one byte per element, 1 = kept) for the problem's dropout settings:
  * the device side of the bit-exact mask check. */

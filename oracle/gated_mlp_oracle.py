@@ -44,7 +44,48 @@ def silu_prime(b: Tensor) -> Tensor:
     return sigma * (1 + b * (1 - sigma))
 
 
-def hidden_forward(x, w_gate, b_gate, w_up, b_up, keep_scale: Optional[Tensor] = None):
+# Gate activations by the names of the reference's ACT_FWD table (gated_mlp.py:27-37): value and
+# derivative. The reference defines a derivative for SiLU only (ACT_BWD, gated_mlp.py:46-55); the
+# others are the textbook forms of the torch modules that table holds (nn.GELU is the erf form,
+# nn.LeakyReLU has slope 0.01).
+def act_value(name: str, b: Tensor) -> Tensor:
+    if name in ("silu", "swish"):
+        return silu(b)
+    if name == "no_act":
+        return b
+    if name == "relu":
+        return torch.relu(b)
+    if name == "gelu":
+        return 0.5 * b * (1 + torch.erf(b / 2 ** 0.5))
+    if name == "sigmoid":
+        return torch.sigmoid(b)
+    if name == "tanh":
+        return torch.tanh(b)
+    if name == "leaky_relu":
+        return torch.where(b > 0, b, 0.01 * b)
+    raise NotImplementedError(name)
+
+
+def act_prime(name: str, b: Tensor) -> Tensor:
+    if name in ("silu", "swish"):
+        return silu_prime(b)
+    if name == "no_act":
+        return torch.ones_like(b)
+    if name == "relu":
+        return (b > 0).to(b.dtype)
+    if name == "gelu":
+        return 0.5 * (1 + torch.erf(b / 2 ** 0.5)) + b * torch.exp(-0.5 * b * b) / (2 * torch.pi) ** 0.5
+    if name == "sigmoid":
+        s = torch.sigmoid(b)
+        return s * (1 - s)
+    if name == "tanh":
+        return 1 - torch.tanh(b) ** 2
+    if name == "leaky_relu":
+        return torch.where(b > 0, torch.ones_like(b), torch.full_like(b, 0.01))
+    raise NotImplementedError(name)
+
+
+def hidden_forward(x, w_gate, b_gate, w_up, b_up, keep_scale: Optional[Tensor] = None, act: str = "silu"):
     """(H, G, U): hidden state after dropout and the biased pre-activations."""
     g = x @ w_gate.T
     if b_gate is not None:
@@ -52,41 +93,42 @@ def hidden_forward(x, w_gate, b_gate, w_up, b_up, keep_scale: Optional[Tensor] =
     u = x @ w_up.T
     if b_up is not None:
         u = u + b_up
-    h = silu(g) * u
+    h = act_value(act, g) * u
     if keep_scale is not None:
         h = h * keep_scale
     return h, g, u
 
 
-def forward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, keep_scale: Optional[Tensor] = None) -> Tensor:
+def forward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, keep_scale: Optional[Tensor] = None,
+            act: str = "silu") -> Tensor:
     shapes = x.shape
     x2 = x.reshape(-1, shapes[-1])
-    h, _, _ = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale)
+    h, _, _ = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale, act)
     y = h @ w_down.T
     if b_down is not None:
         y = y + b_down
     return y.reshape(shapes[:-1] + (w_down.shape[0],))
 
 
-def hidden_backward(x, w_gate, w_up, g, u, dh):
+def hidden_backward(x, w_gate, w_up, g, u, dh, act: str = "silu"):
     """(dx, dW_up, dW_gate, d_gate, d_up) from dH; eager_bwd's closed form, gated_mlp.py:143-154."""
-    c = silu(g)
-    d_gate = (dh * u) * silu_prime(g)   # grad_output_a_act_prime
+    c = act_value(act, g)
+    d_gate = (dh * u) * act_prime(act, g)   # grad_output_a_act_prime
     d_up = dh * c                       # grad_output_c
     dx = d_up @ w_up + d_gate @ w_gate
     return dx, d_up.T @ x, d_gate.T @ x, d_gate, d_up
 
 
-def backward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, dy, keep_scale: Optional[Tensor] = None
-             ) -> Dict[str, Tensor]:
+def backward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, dy, keep_scale: Optional[Tensor] = None,
+             act: str = "silu") -> Dict[str, Tensor]:
     """All gradients of forward() for upstream gradient dy. Keys follow nn.Module parameter names."""
     x2 = x.reshape(-1, x.shape[-1])
     dy2 = dy.reshape(-1, dy.shape[-1])
-    h, g, u = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale)
+    h, g, u = hidden_forward(x2, w_gate, b_gate, w_up, b_up, keep_scale, act)
     dh = dy2 @ w_down
     if keep_scale is not None:
         dh = dh * keep_scale
-    dx, dw_up, dw_gate, d_gate, d_up = hidden_backward(x2, w_gate, w_up, g, u, dh)
+    dx, dw_up, dw_gate, d_gate, d_up = hidden_backward(x2, w_gate, w_up, g, u, dh, act)
     out = {
         "dx": dx.reshape(x.shape),
         "dgate_proj.weight": dw_gate,
@@ -180,14 +222,15 @@ def make_case(M: int, K: int, N: int, bias: bool, dtype: torch.dtype, seed: int 
 
 
 def forward_backward(case: Case, dropout_p: float = 0.0, seed: int = 0, offset: int = 0, *, row0: int = 0,
-                     col0: int = 0, n_global: Optional[int] = None, grads: bool = True) -> Dict[str, Tensor]:
+                     col0: int = 0, n_global: Optional[int] = None, grads: bool = True,
+                     act: str = "silu") -> Dict[str, Tensor]:
     """fp32 oracle outputs for a case: {"y", "dx", "dgate_proj.weight", ...}."""
     x, wg, bg, wu, bu, wd, bd, dy = case.f32()
     rows = x.numel() // x.shape[-1]
     ks = keep_scale_tensor(rows, wg.shape[0], dropout_p, seed, offset, row0=row0, col0=col0, n_global=n_global)
-    out = {"y": forward(x, wg, bg, wu, bu, wd, bd, ks)}
+    out = {"y": forward(x, wg, bg, wu, bu, wd, bd, ks, act)}
     if grads:
-        out.update(backward(x, wg, bg, wu, bu, wd, bd, dy, ks))
+        out.update(backward(x, wg, bg, wu, bu, wd, bd, dy, ks, act))
     return out
 
 

@@ -62,9 +62,9 @@ def np16(t: torch.Tensor, dt: torch.dtype) -> np.ndarray:
 
 
 def module_case(ref, name, K, N, bias, x_shape, dt, seed_w, seed_x, seed_dy, x_uniform, dy_std=1.0,
-                dropout=None):
+                dropout=None, hidden_act="silu"):
     torch.manual_seed(seed_w)
-    m = ref.EagerGatedMLP(hidden_size=K, intermediate_size=N, bias=bias, dropout_p=0.0)
+    m = ref.EagerGatedMLP(hidden_size=K, intermediate_size=N, bias=bias, dropout_p=0.0, hidden_act=hidden_act)
     with torch.no_grad():
         for p in m.parameters():
             p.copy_(rounded(p, dt))
@@ -73,7 +73,7 @@ def module_case(ref, name, K, N, bias, x_shape, dt, seed_w, seed_x, seed_dy, x_u
     x = rounded(x, dt).requires_grad_(True)
     torch.manual_seed(seed_dy)
     dy = rounded(torch.randn(x_shape) * dy_std, dt)
-    meta = {"dtype": str(dt).split(".")[-1], "bias": bias}
+    meta = {"dtype": str(dt).split(".")[-1], "bias": bias, "act": hidden_act}
     if dropout is not None:
         p, seed, offset = dropout
         rows = x.numel() // K
@@ -130,6 +130,11 @@ def main():
     # Bias + dropout with the externally supplied Philox mask; ragged M (not a multiple of the tile).
     module_case(ref, "dropout_bias_bf16", K=128, N=384, bias=True, x_shape=(200, 128), dt=torch.bfloat16,
                 seed_w=20, seed_x=21, seed_dy=22, x_uniform=False, dy_std=0.1, dropout=(0.1, 0x5EED, 7))
+    # The other gate activations of the reference's ACT_FWD table, through its eager module and
+    # torch autograd (small shapes; one fixture per activation).
+    for i, act in enumerate(("gelu", "relu", "sigmoid", "tanh", "leaky_relu", "no_act")):
+        module_case(ref, f"act_{act}_bf16", K=64, N=128, bias=True, x_shape=(40, 64), dt=torch.bfloat16,
+                    seed_w=30 + i, seed_x=40 + i, seed_dy=50 + i, x_uniform=False, dy_std=0.1, hidden_act=act)
     ops_case(ref, "ops_closed_form_bf16")
 
 

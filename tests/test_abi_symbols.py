@@ -38,7 +38,8 @@ def test_argument_checks_run_before_any_device_call(pkg):
     """Bad descriptors are rejected on the host with a status code and a message (no GPU needed)."""
     L = pkg._lib
     lib = L.load()
-    ok = dict(M=4, K=64, N=64, dtype=0, dropout_p=0.0, seed=0, offset=0, row0_global=0, col0_global=0, N_global=0)
+    ok = dict(M=4, K=64, N=64, dtype=0, dropout_p=0.0, seed=0, offset=0, row0_global=0, col0_global=0, N_global=0,
+              act=0, reserved=0)
 
     def rc(**kw):
         p = L.Problem(**{**ok, **kw})
@@ -48,6 +49,7 @@ def test_argument_checks_run_before_any_device_call(pkg):
     assert rc(K=60) == -1
     assert rc(dtype=7) == -3
     assert rc(dropout_p=1.0) == -6
+    assert rc(act=9) == -6
     p = L.Problem(**ok)
     assert lib.gmlp_down_fwd(ctypes.byref(p), None, 16, None, None, 16, None) == -6   # NULL h
     assert lib.gmlp_down_fwd(ctypes.byref(p), 8, 16, None, None, 16, None) == -2      # misaligned h

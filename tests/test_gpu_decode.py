@@ -41,6 +41,19 @@ def test_decode_equals_gemm_path_and_is_repeatable(pkg, cuda_dev):
     orc.assert_parity(ys[0].cpu(), y_gemm.float().cpu(), "decode vs gemm", max_abs=2e-2, mean_rel=1e-2)
 
 
+@pytest.mark.parametrize("act", ["gelu", "relu", "no_act"])
+def test_decode_other_activations(pkg, cuda_dev, act):
+    case = orc.make_case(16, 256, 1024, True, torch.bfloat16, seed=31, w_std=0.03)
+    K, N = 256, 1024
+    m = pkg.FusedGatedMLP(K, N, bias=True, hidden_act=act)
+    m.load_state_dict(case.state_dict())
+    m = m.to(cuda_dev).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        y = m(case.x.to(cuda_dev))
+    assert m._decode_scratch is not None
+    orc.assert_parity(y.cpu(), orc.forward_backward(case, grads=False, act=act)["y"], "y")
+
+
 def test_decode_fp16_and_3d_input(pkg, cuda_dev):
     case = orc.make_case(0, 256, 512, True, torch.float16, seed=9, lead_shape=(2, 5), w_std=0.03)
     m = build_module(pkg, case, torch.float16, cuda_dev).eval()
@@ -58,3 +71,25 @@ def test_decode_rejects_what_it_cannot_do(pkg, cuda_dev):
     with pytest.raises(pkg._lib.GmlpError, match="scratch"):
         K_.decode_fwd(z(4, 128), z(256, 128), None, z(256, 128), None, z(128, 256), None,
                       scratch=torch.zeros(64, dtype=torch.int32, device=cuda_dev))
+
+
+def test_decode_replays_from_a_cuda_graph(pkg, cuda_dev):
+    """The decode path makes no allocation or synchronisation inside the C calls, so a caller can
+    capture it once and replay it (what a serving loop with a few tokens per step wants)."""
+    K_ = pkg.ops.kernels
+    case = orc.make_case(8, 512, 1536, True, torch.bfloat16, seed=21, w_std=0.03)
+    t = [v.to(cuda_dev) if v is not None else None
+         for v in (case.x, case.w_gate, case.b_gate, case.w_up, case.b_up, case.w_down, case.b_down)]
+    scratch = K_.decode_scratch(8, 512, 1536, torch.bfloat16, cuda_dev)
+    want = K_.decode_fwd(*t, scratch=scratch)          # also warms up (function attributes, module load)
+    torch.cuda.synchronize()
+    x_static = t[0].clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = K_.decode_fwd(x_static, *t[1:], scratch=scratch)
+    for scale in (1.0, 0.5):
+        x_static.copy_(t[0] * scale)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y_static, K_.decode_fwd(t[0] * scale, *t[1:], scratch=scratch))
+    assert torch.equal(K_.decode_fwd(*t, scratch=scratch), want)

@@ -9,12 +9,15 @@ from _util import load_golden
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name", ["c1_readme_fp16", "default_bias_3d_bf16", "dropout_bias_bf16"])
+ACT_FIXTURES = [f"act_{a}_bf16" for a in ("gelu", "relu", "sigmoid", "tanh", "leaky_relu", "no_act")]
+
+
+@pytest.mark.parametrize("name", ["c1_readme_fp16", "default_bias_3d_bf16", "dropout_bias_bf16"] + ACT_FIXTURES)
 def test_module_matches_reference_outputs(pkg, cuda_dev, name):
     t, meta, dt = load_golden(name)
     K, N = t["p.gate_proj.weight"].shape[1], t["p.gate_proj.weight"].shape[0]
     p = meta.get("dropout_p", 0.0)
-    m = pkg.FusedGatedMLP(K, N, bias=meta["bias"], dropout_p=p)
+    m = pkg.FusedGatedMLP(K, N, bias=meta["bias"], dropout_p=p, hidden_act=meta.get("act", "silu"))
     m.load_state_dict({k[2:]: v.float() for k, v in t.items() if k.startswith("p.")})
     m = m.to(cuda_dev).to(dt).train()
     m.set_philox(meta.get("seed", 0), meta.get("offset", 0))

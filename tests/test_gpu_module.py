@@ -115,3 +115,23 @@ def test_host_pipeline_streams_distinct_batches(pkg, cuda_dev):
         assert torch.equal(y, step(x.to(cuda_dev)).cpu())
     with pytest.raises(ValueError):
         pipe.submit(torch.empty(4, 4), torch.empty(4, 4))
+
+
+@pytest.mark.parametrize("M", [8, 300])   # 8 tokens without grad takes the decode kernels, 300 the tile GEMMs
+def test_fused_residual(pkg, cuda_dev, M):
+    case = orc.make_case(M, 256, 512, True, torch.bfloat16, seed=M, w_std=0.03, dy_std=0.05)
+    m = build_module(pkg, case, torch.bfloat16, cuda_dev).eval()
+    res = (torch.randn((M, 256), generator=torch.Generator().manual_seed(5)) * 0.5).to(torch.bfloat16)
+    want = orc.forward_backward(case)
+    with torch.no_grad():
+        y = m(case.x.to(cuda_dev), residual=res.to(cuda_dev))
+    orc.assert_parity(y.cpu(), want["y"] + res.float(), "y + residual (no grad)")
+    x = case.x.to(cuda_dev).requires_grad_(True)
+    r = res.to(cuda_dev).requires_grad_(True)
+    y = m(x, residual=r)
+    y.backward(case.dy.to(cuda_dev))
+    orc.assert_parity(y.cpu(), want["y"] + res.float(), "y + residual")
+    orc.assert_parity(x.grad.cpu(), want["dx"], "dx")
+    assert torch.equal(r.grad, case.dy.to(cuda_dev))
+    with pytest.raises(ValueError):
+        m(x, residual=r[:, :128])

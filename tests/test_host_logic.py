@@ -22,7 +22,10 @@ def test_module_surface_matches_reference(pkg):
 
 def test_unsupported_activation_and_modes(pkg):
     with pytest.raises(NotImplementedError):
-        pkg.FusedGatedMLP(hidden_act="gelu")
+        pkg.FusedGatedMLP(hidden_act="mish")
+    for name in ("gelu", "relu", "sigmoid", "tanh", "leaky_relu", "no_act", "swish"):
+        m = pkg.FusedGatedMLP(64, 128, hidden_act=name)
+        assert m.act_fn == name and isinstance(m.act, torch.nn.Module)
     with pytest.raises(ValueError):
         pkg.FusedGatedMLP(parallel_mode="pipeline")
 
@@ -46,7 +49,7 @@ def test_op_level_preconditions(pkg):
         pkg.mlp_hidden_states_fwd(torch.zeros(4, 24), torch.zeros(128, 24), None, torch.zeros(128, 24), None,
                                   "silu", 0.0)
     with pytest.raises(NotImplementedError):
-        pkg.mlp_hidden_states_fwd(x, w, None, w, None, "gelu", 0.0)
+        pkg.mlp_hidden_states_fwd(x, w, None, w, None, "softplus", 0.0)
 
 
 def test_dtype_code(pkg):

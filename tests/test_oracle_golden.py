@@ -6,7 +6,8 @@ import torch
 from oracle import gated_mlp_oracle as orc
 from _util import golden_params, load_golden
 
-MODULE_FIXTURES = ["c1_readme_fp16", "default_bias_3d_bf16", "dropout_bias_bf16"]
+ACTS = ["gelu", "relu", "sigmoid", "tanh", "leaky_relu", "no_act"]
+MODULE_FIXTURES = ["c1_readme_fp16", "default_bias_3d_bf16", "dropout_bias_bf16"] + [f"act_{a}_bf16" for a in ACTS]
 
 
 @pytest.mark.parametrize("name", MODULE_FIXTURES)
@@ -18,9 +19,10 @@ def test_oracle_matches_reference_module(name):
     rows = x.numel() // x.shape[-1]
     ks = orc.keep_scale_tensor(rows, wg.shape[0], meta.get("dropout_p", 0.0), meta.get("seed", 0),
                                meta.get("offset", 0))
-    y = orc.forward(x, wg, bg, wu, bu, wd, bd, ks)
+    act = meta.get("act", "silu")
+    y = orc.forward(x, wg, bg, wu, bu, wd, bd, ks, act)
     torch.testing.assert_close(y, t["y"], rtol=1e-5, atol=1e-5)
-    grads = orc.backward(x, wg, bg, wu, bu, wd, bd, dy, ks)
+    grads = orc.backward(x, wg, bg, wu, bu, wd, bd, dy, ks, act)
     for k, v in grads.items():
         torch.testing.assert_close(v, t[k], rtol=2e-5, atol=2e-5, msg=lambda m, k=k: f"{k}: {m}")
     expected = {k for k in t if k.startswith("d") and k != "dy"}

@@ -14,6 +14,9 @@ LIB_PATH = Path(__file__).resolve().parent / "libgmlp.so"
 
 GMLP_BF16, GMLP_FP16 = 0, 1
 
+# gmlp_act_t by the names the reference's module accepts (gated_mlp.py:27-37)
+ACT_CODES = {"silu": 0, "swish": 0, "no_act": 1, "relu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5, "leaky_relu": 6}
+
 # Every symbol include/gmlp.h declares; tests check that the library exports all of them.
 EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
@@ -35,6 +38,7 @@ class Problem(C.Structure):
         ("dtype", C.c_int32), ("dropout_p", C.c_float),
         ("seed", C.c_uint64), ("offset", C.c_uint64),
         ("row0_global", C.c_int64), ("col0_global", C.c_int64), ("N_global", C.c_int64),
+        ("act", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -59,7 +63,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_gemm.argtypes = [i32, i32, i32, i64, i64, i64, vp, i64, vp, i64, vp, i64, vp, vp]
     lib.gmlp_decode_scratch_bytes.argtypes = [pp]
     lib.gmlp_decode_scratch_bytes.restype = C.c_size_t
-    lib.gmlp_decode_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
+    lib.gmlp_decode_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_set_cta_pair_mode.argtypes = [i32]
     lib.gmlp_set_raster_group.argtypes = [i32]
     lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]

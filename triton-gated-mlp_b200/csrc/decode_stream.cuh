@@ -34,9 +34,11 @@ struct DecodeArgs {
   const void* bias0;  // per weight row (gate bias, or down bias)
   const void* bias1;  // up bias (DUAL)
   void* out;          // H[M, rows] or Y[M, rows]
+  const void* residual;  // optional [M, rows] added to the output (down projection only)
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
   int* counters;      // [row tiles], zero on entry and on exit
+  int act;            // gate activation (ACT_*), DUAL only
   int dependent;      // 1: launched with programmatic stream serialization behind the kernel
                       //    that produces the activations (and last used slots / counters)
 };
@@ -245,6 +247,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int ep_tid = threadIdx.x - 64;  // 0..127 among the epilogue warps
     T* const out = static_cast<T*>(args.out);
+    const T* const residual = static_cast<const T*>(args.residual);
     const T* const bias0 = static_cast<const T*>(args.bias0);
     const T* const bias1 = static_cast<const T*>(args.bias1);
     constexpr long long SLOT_FLOATS = static_cast<long long>(NACC) * 128 * MPAD;
@@ -351,11 +354,13 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
               float o;
               if (DUAL) {
                 const float g = v[0][m] + b0;
-                o = g * sigmoid_f(g) * (v[NACC - 1][m] + b1);
+                o = act_value(args.act, g) * (v[NACC - 1][m] + b1);
               } else {
                 o = v[0][m] + b0;
               }
-              out[static_cast<long long>(m) * args.ld_out + wrow] = static_cast<T>(o);
+              const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
+              if (!DUAL && residual) o += static_cast<float>(residual[oi]);
+              out[oi] = static_cast<T>(o);
             }
           }
         }

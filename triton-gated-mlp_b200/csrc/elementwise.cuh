@@ -6,13 +6,13 @@
 
 namespace gmlp {
 
-// d_gate = dH' * u * silu'(g), d_up = dH' * silu(g), dH' = dH * keep / (1-p).
+// d_gate = dH' * u * act'(g), d_up = dH' * act(g), dH' = dH * keep / (1-p).
 // One thread per 8 consecutive columns; grid-stride over the [M, N] matrix.
 template <typename T>
 __global__ void __launch_bounds__(256)
 dact_kernel(const T* __restrict__ dh, const T* __restrict__ g, const T* __restrict__ u,
             T* __restrict__ d_gate, T* __restrict__ d_up, long long M, long long N,
-            DropoutParams drop) {
+            DropoutParams drop, int act) {
   const long long groups_per_row = N / 8;
   const long long total = M * groups_per_row;
   const bool drop_on = drop.thresh != 0u;
@@ -33,9 +33,10 @@ dact_kernel(const T* __restrict__ dh, const T* __restrict__ g, const T* __restri
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
-      const float s = sigmoid_f(gv[k]);
-      du[k] = a[k] * gv[k] * s;
-      dg[k] = a[k] * uv[k] * s * (1.0f + gv[k] * (1.0f - s));
+      float f, df;
+      act_value_grad(act, gv[k], f, df);
+      du[k] = a[k] * f;
+      dg[k] = a[k] * uv[k] * df;
     }
     store8(d_gate + o, dg);
     store8(d_up + o, du);

@@ -39,6 +39,7 @@ struct GemmArgs {
   int kb1;      // 64-element reduction blocks taken from (A1, B1) afterwards (0 = unused)
   int batches;  // 1, or 2: two problems (A0 -> out0, A1 -> out1) that share B0
   int group_m;  // row tiles per raster group
+  int act;      // gate activation (ACT_*)
   uint32_t idesc;
   int* status;  // device word; a role that gives up a wait stores its code here
   void* out0;
@@ -124,6 +125,75 @@ __device__ __forceinline__ float sigmoid_f(float x) {
   float t;
   asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
   return fmaf(t, 0.5f, 0.5f);
+}
+
+// Gate activations (the names the reference's module accepts, gated_mlp.py:17-37).
+enum : int {
+  ACT_SILU = 0,
+  ACT_NONE = 1,
+  ACT_RELU = 2,
+  ACT_GELU = 3,  // exact (erf) form, nn.GELU's default
+  ACT_SIGMOID = 4,
+  ACT_TANH = 5,
+  ACT_LEAKY_RELU = 6,  // negative slope 0.01, nn.LeakyReLU's default
+};
+__device__ __forceinline__ float tanh_f(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+  return t;
+}
+// f(x) and f'(x) of the gate activation. `act` is uniform over the launch, so the switch
+// never diverges.
+__device__ __forceinline__ void act_value_grad(int act, float x, float& f, float& df) {
+  switch (act) {
+    case ACT_SILU: {
+      const float s = sigmoid_f(x);
+      f = x * s;
+      df = s * (1.0f + x * (1.0f - s));
+      break;
+    }
+    case ACT_RELU:
+      f = fmaxf(x, 0.0f);
+      df = x > 0.0f ? 1.0f : 0.0f;
+      break;
+    case ACT_GELU: {
+      const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+      f = x * cdf;
+      df = cdf + x * 0.39894228040143268f * __expf(-0.5f * x * x);
+      break;
+    }
+    case ACT_SIGMOID: {
+      const float s = sigmoid_f(x);
+      f = s;
+      df = s * (1.0f - s);
+      break;
+    }
+    case ACT_TANH: {
+      const float t = tanh_f(x);
+      f = t;
+      df = 1.0f - t * t;
+      break;
+    }
+    case ACT_LEAKY_RELU:
+      f = x > 0.0f ? x : 0.01f * x;
+      df = x > 0.0f ? 1.0f : 0.01f;
+      break;
+    default:  // ACT_NONE
+      f = x;
+      df = 1.0f;
+      break;
+  }
+}
+__device__ __forceinline__ float act_value(int act, float x) {
+  switch (act) {
+    case ACT_SILU: return x * sigmoid_f(x);
+    case ACT_RELU: return fmaxf(x, 0.0f);
+    case ACT_GELU: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    case ACT_SIGMOID: return sigmoid_f(x);
+    case ACT_TANH: return tanh_f(x);
+    case ACT_LEAKY_RELU: return x > 0.0f ? x : 0.01f * x;
+    default: return x;
+  }
 }
 
 // keep/scale factors for the 8 consecutive columns starting at (grow, gcol), gcol a
@@ -380,7 +450,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
             qu[j] = pack8<T>(u);
           }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) h[i] = g[i] * sigmoid_f(g[i]) * u[i];
+          for (int i = 0; i < 8; ++i) h[i] = act_value(args.act, g[i]) * u[i];
           if (drop_on) {
             float f[8];
             dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
@@ -440,9 +510,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float sg = sigmoid_f(g[i]);
-          du[i] = dh[i] * g[i] * sg;
-          dg[i] = dh[i] * u[i] * sg * (1.0f + g[i] * (1.0f - sg));
+          float f, df;
+          act_value_grad(args.act, g[i], f, df);
+          du[i] = dh[i] * f;
+          dg[i] = dh[i] * u[i] * df;
         }
         qg[j] = pack8<T>(dg);
         qu[j] = pack8<T>(du);

@@ -130,6 +130,7 @@ static int encode_operand(CUtensorMap* m, const Operand& o, uint32_t kmajor_box_
 
 // --------------------------------------------------------------- launching --
 struct Epilogue {
+  int act = ACT_SILU;
   void* out0 = nullptr;
   void* out1 = nullptr;
   void* out2 = nullptr;
@@ -182,6 +183,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.kb0 = static_cast<int>((a0.k + BK - 1) / BK);
   args.kb1 = static_cast<int>((k1 + BK - 1) / BK);
   args.batches = batches;
+  args.act = ep.act;
   args.idesc = make_idesc_f16(pair ? 2 * BM : BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
   args.status = dev->status_ptr;
   args.out0 = ep.out0;
@@ -255,6 +257,8 @@ static int check_problem(const gmlp_problem_t* p) {
   if ((p->K % 8) != 0 || (p->N % 8) != 0)
     return fail(GMLP_ERR_SHAPE, "K=%lld and N=%lld must be multiples of 8",
                 static_cast<long long>(p->K), static_cast<long long>(p->N));
+  if (p->act < ACT_SILU || p->act > ACT_LEAKY_RELU)
+    return fail(GMLP_ERR_ARG, "act=%d is not a gmlp_act_t value", p->act);
   if (!(p->dropout_p >= 0.0f && p->dropout_p < 1.0f))
     return fail(GMLP_ERR_ARG, "dropout_p=%f outside [0, 1)", static_cast<double>(p->dropout_p));
   const int64_t ng = p->N_global ? p->N_global : p->N;
@@ -359,6 +363,7 @@ int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   ep.bias1 = b_up;
   ep.ld_out = p->N;
   ep.drop = make_dropout(p);
+  ep.act = p->act;
   return launch_gemm<256, false, false, EPI_SWIGLU>(dev, p->dtype, p->M, p->N, a, nullptr, bg, &bu,
                                                     0, 1, ep, static_cast<cudaStream_t>(stream));
 }
@@ -403,6 +408,7 @@ int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down
   ep.ld_out = p->N;
   ep.ld_in = p->N;
   ep.drop = make_dropout(p);
+  ep.act = p->act;
   return launch_gemm<256, false, true, EPI_DHIDDEN>(dev, p->dtype, p->M, p->N, a, nullptr, b,
                                                     nullptr, 0, 1, ep,
                                                     static_cast<cudaStream_t>(stream));
@@ -482,12 +488,12 @@ int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const 
     dact_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(dh), static_cast<const __nv_bfloat16*>(g),
         static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(d_gate),
-        static_cast<__nv_bfloat16*>(d_up), p->M, p->N, d);
+        static_cast<__nv_bfloat16*>(d_up), p->M, p->N, d, p->act);
   else
     dact_kernel<__half><<<static_cast<int>(blocks), 256, 0, st>>>(
         static_cast<const __half*>(dh), static_cast<const __half*>(g),
         static_cast<const __half*>(u), static_cast<__half*>(d_gate), static_cast<__half*>(d_up),
-        p->M, p->N, d);
+        p->M, p->N, d, p->act);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
@@ -589,8 +595,9 @@ static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
 template <int MPAD, bool DUAL, typename T>
 static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
                            const void* w0, const void* w1, const void* act, int64_t act_ld,
-                           const void* bias0, const void* bias1, void* out, int64_t ld_out,
-                           float* slots, int* counters, bool dependent, cudaStream_t stream) {
+                           const void* bias0, const void* bias1, const void* residual, void* out,
+                           int64_t ld_out, float* slots, int* counters, bool dependent, int gate_act,
+                           cudaStream_t stream) {
   CUtensorMap mW0, mW1, mAct;
   int rc;
   if ((rc = encode_map(&mW0, w0, red, rows, red, BK, 128, dtype))) return rc;
@@ -610,10 +617,12 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   a.bias0 = bias0;
   a.bias1 = bias1;
   a.out = out;
+  a.residual = residual;
   a.ld_out = ld_out;
   a.slots = slots;
   a.counters = counters;
   a.dependent = dependent ? 1 : 0;
+  a.act = gate_act;
   const long long total = ((rows + 127) / 128) * static_cast<long long>(a.kbt);
   const int grid = static_cast<int>(total < dev->sm_count ? total : dev->sm_count);
   constexpr size_t smem = decode_smem_bytes<MPAD, DUAL>();
@@ -665,8 +674,8 @@ size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p) {
 
 int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
-                    const void* b_down, void* h, void* y, void* scratch, size_t scratch_bytes,
-                    void* stream) {
+                    const void* b_down, const void* residual, void* h, void* y, void* scratch,
+                    size_t scratch_bytes, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if (p->M > 64) return fail(GMLP_ERR_SHAPE, "decode path takes at most 64 tokens, got %lld",
@@ -686,14 +695,14 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   const int M = static_cast<int>(p->M);
   // H[M,N] = silu(x Wg^T + bg) * (x Wu^T + bu): weight rows = N, reduction = K
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
-                           b_gate, b_up, h, p->N, slots,
-                           reinterpret_cast<int*>(sc + l.counters1_off), false, st);
+                           b_gate, b_up, static_cast<const void*>(nullptr), h, p->N, slots,
+                           reinterpret_cast<int*>(sc + l.counters1_off), false, p->act, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
                               static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
-                              static_cast<const void*>(nullptr), y, p->K, slots,
-                              reinterpret_cast<int*>(sc + l.counters2_off), true, st);
+                              static_cast<const void*>(nullptr), residual, y, p->K, slots,
+                              reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
 }
 
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,

@@ -29,6 +29,13 @@ from .ops.kernels import Dropout, Shard
 from . import parallel
 
 
+# torch twins of the gate activations, kept as `module.act` like the reference does (gated_mlp.py:218).
+_ACT_MODULES = {
+    "silu": nn.SiLU, "swish": nn.SiLU, "no_act": nn.Identity, "relu": nn.ReLU, "gelu": nn.GELU,
+    "sigmoid": nn.Sigmoid, "tanh": nn.Tanh, "leaky_relu": nn.LeakyReLU,
+}
+
+
 class FusedGatedMLPFunction(Function):
     """y = down(dropout(silu(gate(x)) * up(x))) with hand-written forward and backward.
 
@@ -39,22 +46,23 @@ class FusedGatedMLPFunction(Function):
     @staticmethod
     def forward(ctx, x: Tensor, W_gate: Tensor, b_gate: Optional[Tensor], W_up: Tensor,
                 b_up: Optional[Tensor], W_down: Tensor, b_down: Optional[Tensor],
-                drop: Dropout, shard: Shard, tp_group) -> Tensor:
+                drop: Dropout, shard: Shard, tp_group, act: str = "silu",
+                residual: Optional[Tensor] = None) -> Tensor:
         need_bwd = any(ctx.needs_input_grad)
         if need_bwd:
-            h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True)
+            h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True, act=act)
         else:
-            h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False)
+            h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False, act=act)
             g = u = None
         # With the intermediate dimension sharded, every rank holds a partial sum
         # of y; the output bias is added once, by the rank that owns column 0.
-        add_bias = b_down if (tp_group is None or shard.col0 == 0) else None
-        y = kernels.down_fwd(h, W_down, add_bias)
+        owner = tp_group is None or shard.col0 == 0
+        y = kernels.down_fwd(h, W_down, b_down if owner else None, residual if owner else None)
         if tp_group is not None:
             parallel.all_reduce_sum(y, tp_group)
         if need_bwd:
             ctx.save_for_backward(x, W_gate, W_up, W_down, g, u, h)
-            ctx.drop, ctx.shard, ctx.tp_group = drop, shard, tp_group
+            ctx.drop, ctx.shard, ctx.tp_group, ctx.act = drop, shard, tp_group, act
             ctx.has_bias = (b_gate is not None, b_up is not None, b_down is not None)
         return y
 
@@ -66,7 +74,7 @@ class FusedGatedMLPFunction(Function):
         dx = dW_gate = db_gate = dW_up = db_up = dW_down = db_down = None
         need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
         if need_hidden:
-            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard)
+            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act)
             if need[0]:
                 dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
                 if ctx.tp_group is not None:
@@ -81,7 +89,8 @@ class FusedGatedMLPFunction(Function):
             dW_down = kernels.bwd_dw_down(dy, h)
         if need[6] and ctx.has_bias[2]:
             db_down = kernels.colsum(dy)
-        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None
+        d_res = dy if (len(need) > 11 and need[11]) else None  # y = ... + residual
+        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res
 
 
 class FusedGatedMLP(nn.Module):
@@ -116,7 +125,7 @@ class FusedGatedMLP(nn.Module):
     ):
         super().__init__()
         if hidden_act not in SUPPORTED_ACTS:
-            raise NotImplementedError(f"gate activation {hidden_act!r}: only SiLU is implemented")
+            raise NotImplementedError(f"gate activation {hidden_act!r}: supported are {sorted(SUPPORTED_ACTS)}")
         if parallel_mode not in ("none", "token", "tp"):
             raise ValueError(f"parallel_mode {parallel_mode!r} not in ('none', 'token', 'tp')")
         self.hidden_size = hidden_size
@@ -124,7 +133,7 @@ class FusedGatedMLP(nn.Module):
         self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=bias)
         self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=bias)
         self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=bias)
-        self.act = nn.SiLU()
+        self.act = _ACT_MODULES[hidden_act]()
         self.act_fn = hidden_act
         self.dropout = nn.Dropout(dropout_p)
         self.parallel_mode = parallel_mode
@@ -149,7 +158,7 @@ class FusedGatedMLP(nn.Module):
             return Shard(row0=int(self.token_row0), col0=0, n_global=self.intermediate_size)
         return Shard()
 
-    def _decode_forward(self, x: Tensor, tp_group) -> Tensor:
+    def _decode_forward(self, x: Tensor, tp_group, residual: Optional[Tensor]) -> Tensor:
         """Inference with at most 64 tokens: the weight-streaming kernels (HBM-bound)."""
         key = (x.device, x.dtype)
         if self._decode_scratch is None or self._decode_scratch[0] != key:
@@ -158,15 +167,22 @@ class FusedGatedMLP(nn.Module):
         own_bias = tp_group is None or self.tp_rank == 0
         y = kernels.decode_fwd(x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight,
                                self.up_proj.bias, self.down_proj.weight,
-                               self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1])
+                               self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1],
+                               act=self.act_fn, residual=residual if own_bias else None)
         if tp_group is not None:
             parallel.all_reduce_sum(y, tp_group)
         return y
 
-    def forward(self, x: Tensor) -> Tensor:
+    def forward(self, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
+        """y = down(dropout(act(gate(x)) * up(x))) (+ residual, fused into the down projection's epilogue;
+        the reference adds a residual outside the module, after gated_mlp.py:236-237)."""
         shapes = x.shape
         if len(shapes) > 2:
             x = x.reshape(-1, shapes[-1])
+        if residual is not None:
+            if residual.shape != shapes:
+                raise ValueError(f"residual shape {tuple(residual.shape)} != input shape {tuple(shapes)}")
+            residual = residual.reshape(-1, shapes[-1])
         p = float(self.dropout.p) if self.training else 0.0
         drop = Dropout(p, self.philox_seed, self.philox_offset)
         if p > 0.0:
@@ -175,13 +191,14 @@ class FusedGatedMLP(nn.Module):
         if self.parallel_mode == "tp" and tp_group is None:
             tp_group = parallel.default_group()
         needs_grad = torch.is_grad_enabled() and (
-            x.requires_grad or any(q.requires_grad for q in self.parameters()))
+            x.requires_grad or any(q.requires_grad for q in self.parameters())
+            or (residual is not None and residual.requires_grad))
         if (not needs_grad and p == 0.0 and x.is_cuda
                 and kernels.decode_supported(x.shape[0], self.hidden_size, self.intermediate_size)):
-            y = self._decode_forward(x, tp_group)
+            y = self._decode_forward(x, tp_group, residual)
             return y.view(shapes) if len(shapes) > 2 else y
         y = FusedGatedMLPFunction.apply(
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
-            self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group,
+            self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group, self.act_fn, residual,
         )
         return y.view(shapes) if len(shapes) > 2 else y

@@ -15,7 +15,11 @@ from torch import Tensor
 from . import kernels
 from .kernels import Dropout, Shard, NO_SHARD
 
-SUPPORTED_ACTS = ("silu", "swish")
+from .._lib import ACT_CODES
+
+# The reference's module accepts these names (gated_mlp.py:27-37); its own fused kernel
+# implements only "silu" and "no_act" (ops/act.py:7-12).
+SUPPORTED_ACTS = tuple(ACT_CODES)
 
 
 def validate_dimensions(x: Tensor, WT_up: Tensor, b_up: Optional[Tensor], WT_gp: Tensor,
@@ -50,7 +54,7 @@ def mlp_hidden_states_fwd(
     """
     validate_dimensions(x, WT_up, b_up, WT_gp, b_gp)
     if act_fn not in SUPPORTED_ACTS:
-        raise NotImplementedError(f"gate activation {act_fn!r}: only SiLU is implemented")
+        raise NotImplementedError(f"gate activation {act_fn!r}: supported are {sorted(SUPPORTED_ACTS)}")
     K = x.shape[1]
     N = WT_up.shape[0]
     if K % 16 != 0:
@@ -58,4 +62,4 @@ def mlp_hidden_states_fwd(
     if N % 16 != 0:
         raise NotImplementedError()
     drop = Dropout(float(dropout_p), seed, offset)
-    return kernels.hidden_fwd(x, WT_gp, b_gp, WT_up, b_up, drop=drop, shard=shard, save=save_preact)
+    return kernels.hidden_fwd(x, WT_gp, b_gp, WT_up, b_up, drop=drop, shard=shard, save=save_preact, act=act_fn)

@@ -13,7 +13,7 @@ import torch
 from torch import Tensor
 
 from .. import _lib
-from .._lib import Problem, check, dtype_code, load, ptr, require_cuda, stream_of
+from .._lib import ACT_CODES, Problem, check, dtype_code, load, ptr, require_cuda, stream_of
 
 
 @dataclass(frozen=True)
@@ -38,11 +38,18 @@ NO_DROPOUT = Dropout()
 NO_SHARD = Shard()
 
 
-def _problem(M: int, K: int, N: int, dt: torch.dtype, drop: Dropout, shard: Shard) -> Problem:
+def act_code(act: str) -> int:
+    """gmlp_act_t for one of the reference's activation names; NotImplementedError otherwise."""
+    if act not in ACT_CODES:
+        raise NotImplementedError(f"gate activation {act!r}: supported are {sorted(ACT_CODES)}")
+    return ACT_CODES[act]
+
+
+def _problem(M: int, K: int, N: int, dt: torch.dtype, drop: Dropout, shard: Shard, act: str = "silu") -> Problem:
     return Problem(
         M=M, K=K, N=N, dtype=dtype_code(dt), dropout_p=float(drop.p),
         seed=int(drop.seed) & 0xFFFFFFFFFFFFFFFF, offset=int(drop.offset) & 0xFFFFFFFFFFFFFFFF,
-        row0_global=shard.row0, col0_global=shard.col0, N_global=shard.n_global,
+        row0_global=shard.row0, col0_global=shard.col0, N_global=shard.n_global, act=act_code(act), reserved=0,
     )
 
 
@@ -64,8 +71,8 @@ def _same_dtype(*ts: Tensor | None) -> torch.dtype:
 
 
 def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
-               drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False):
-    """H = dropout(silu(x W_gate^T + b_gate) * (x W_up^T + b_up)); with save=True also
+               drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False, act: str = "silu"):
+    """H = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)); with save=True also
     returns the biased pre-activations (G, U)."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up)
     dt = _same_dtype(x, w_gate, b_gate, w_up, b_up)
@@ -76,7 +83,7 @@ def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     g = torch.empty((M, N), dtype=dt, device=dev) if save else None
     u = torch.empty((M, N), dtype=dt, device=dev) if save else None
     if M > 0:
-        prob = _problem(M, K, N, dt, drop, shard)
+        prob = _problem(M, K, N, dt, drop, shard, act)
         with torch.cuda.device(dev):
             check(load().gmlp_hidden_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up),
                                          ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
@@ -100,7 +107,7 @@ def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor 
 
 
 def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT,
-                shard: Shard = NO_SHARD):
+                shard: Shard = NO_SHARD, act: str = "silu"):
     """(d_gate, d_up) from dy through W_down and the SiLU/multiply derivative."""
     dev = require_cuda(dy, w_down, g, u)
     dt = _same_dtype(dy, w_down, g, u)
@@ -110,14 +117,15 @@ def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout 
     d_gate = torch.empty((M, N), dtype=dt, device=dev)
     d_up = torch.empty((M, N), dtype=dt, device=dev)
     if M > 0:
-        prob = _problem(M, K, N, dt, drop, shard)
+        prob = _problem(M, K, N, dt, drop, shard, act)
         with torch.cuda.device(dev):
             check(load().gmlp_bwd_dhidden(C.byref(prob), ptr(dy), ptr(w_down), ptr(g), ptr(u),
                                           ptr(d_gate), ptr(d_up), stream_of(dy)))
     return d_gate, d_up
 
 
-def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD):
+def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD,
+             act: str = "silu"):
     """(d_gate, d_up) from a caller-supplied dH."""
     dev = require_cuda(dh, g, u)
     dt = _same_dtype(dh, g, u)
@@ -126,7 +134,7 @@ def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard
     d_gate = torch.empty((M, N), dtype=dt, device=dev)
     d_up = torch.empty((M, N), dtype=dt, device=dev)
     if M > 0:
-        prob = _problem(M, 8, N, dt, drop, shard)
+        prob = _problem(M, 8, N, dt, drop, shard, act)
         with torch.cuda.device(dev):
             check(load().gmlp_bwd_dact(C.byref(prob), ptr(dh), ptr(g), ptr(u), ptr(d_gate), ptr(d_up),
                                        stream_of(dh)))
@@ -204,10 +212,12 @@ def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device
 
 
 def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
-               w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None) -> Tensor:
-    """y = (silu(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down for M <= 64 tokens."""
-    dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down)
-    dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down)
+               w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
+               residual: Tensor | None = None) -> Tensor:
+    """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens."""
+    dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
+    dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
+    residual = _c(residual)
     x, w_gate, w_up, w_down = _c(x), _c(w_gate), _c(w_up), _c(w_down)
     b_gate, b_up, b_down = _c(b_gate), _c(b_up), _c(b_down)
     M, K = x.shape
@@ -218,10 +228,10 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
         scratch = decode_scratch(M, K, N, dt, dev)
     h = torch.empty((M, N), dtype=dt, device=dev)
     y = torch.empty((M, K), dtype=dt, device=dev)
-    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
     with torch.cuda.device(dev):
         check(load().gmlp_decode_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),
-                                     ptr(w_down), ptr(b_down), ptr(h), ptr(y), ptr(scratch),
+                                     ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(y), ptr(scratch),
                                      scratch.numel() * scratch.element_size(), stream_of(x)))
     return y
 
