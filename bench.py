@@ -41,7 +41,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes (read + write) of one launch of the gate/up kernel at the default workload,
 # from the ncu capture summarised in profiles/gateup_pair_kernel_llama8b_fwd.md.
-K1_DRAM_TRAFFIC_BYTES = 1.272e9
+K1_DRAM_TRAFFIC_BYTES = 1.265e9
 
 
 def flops_per_step(w) -> float:
