@@ -120,7 +120,9 @@ def ops_case(ref, name):
 
 
 def main():
-    ref = import_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = import_reference(sys.argv[1])
     # README / benchmark configuration 1: M=128, K=512, N=256, no bias, fp16 engine.
     module_case(ref, "c1_readme_fp16", K=512, N=256, bias=False, x_shape=(128, 512), dt=torch.float16,
                 seed_w=0, seed_x=0, seed_dy=1, x_uniform=True)

@@ -1,5 +1,5 @@
 // Skinny-M (decode) forward: M <= 64 tokens, so the cost is one pass over the
-// weights and the kernels are judged on HBM bandwidth, not tensor throughput.
+// weights and the kernels are bound by HBM bandwidth, not by tensor throughput.
 //
 // Layout of the work ("swap-AB"): the 128 TMEM lanes / MMA rows are 128 WEIGHT rows
 // and the (padded) token count MPAD in {16, 32, 64} is the MMA N dimension, so a
