@@ -36,6 +36,7 @@ WORKLOADS = {
     "llama3-8b-mlp-fwd-bf16": dict(M=8192, K=4096, N=14336, bias=False, p=0.0, mode="fwd"),
     "train-fwd-bwd-bf16": dict(M=16384, K=2048, N=8192, bias=True, p=0.1, mode="fwd+bwd"),
     "prefill-fwd-bf16": dict(M=65536, K=8192, N=28672, bias=False, p=0.0, mode="fwd"),
+    "prefill-fwd-bwd-bf16": dict(M=65536, K=8192, N=28672, bias=False, p=0.0, mode="fwd+bwd"),
 }
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
@@ -337,6 +338,61 @@ def run_gpu(args, w, name):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """The reference's own benchmark (src/triton_gated_mlp/benchmark.py:26-123): M = N = K = 2**5 .. 2**12, fp16,
+    bias=False, dropout 0, one step = forward + out.sum().backward(), TFLOP/s = 18*M*N*K / t (:86) and peak
+    memory (:96-116), for torch-eager (cuBLAS) and for this engine. One JSON line per size."""
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+
+    def eager_module(K, N):
+        class Eager(torch.nn.Module):   # the reference's EagerGatedMLP, restated with torch modules
+            def __init__(self):
+                super().__init__()
+                self.gate_proj = torch.nn.Linear(K, N, bias=False)
+                self.up_proj = torch.nn.Linear(K, N, bias=False)
+                self.down_proj = torch.nn.Linear(N, K, bias=False)
+
+            def forward(self, x):
+                return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+        return Eager()
+
+    def measure(mod, x):
+        def step():
+            mod.zero_grad(set_to_none=True)
+            x.grad = None
+            mod(x).sum().backward()
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(dev)
+        times = []
+        for _ in range(20):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2], times[len(times) // 5], times[(4 * len(times)) // 5], \
+            torch.cuda.max_memory_allocated(dev) / 2 ** 20
+
+    for e in range(5, 13):
+        n = 2 ** e
+        x = torch.randn((n, n), device=dev, dtype=torch.float16, requires_grad=True)
+        row = {"M": n, "N": n, "K": n, "dtype": "fp16"}
+        for name, mod in (("torch_eager", eager_module(n, n)), ("b200", pkg.FusedGatedMLP(n, n, bias=False))):
+            mod = mod.to(dev).to(torch.float16)
+            ms, lo, hi, mem = measure(mod, x)
+            row[name] = {"ms": ms, "ms_p20": lo, "ms_p80": hi, "tflops": 18.0 * n ** 3 / (ms * 1e-3) / 1e12,
+                         "peak_mem_mib": mem}
+        print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -344,9 +400,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="run the reference benchmark's M=N=K sweep (fp16, fwd+bwd) instead of the headline workload")
     ap.add_argument("--workload", default="llama3-8b-mlp-fwd-bf16", choices=sorted(WORKLOADS))
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
+    if args.sweep:
+        return run_sweep(args)
     if args.impl == "reference":
         run_reference(args, w, args.workload)
     else:

@@ -263,8 +263,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       const bool complete = (u == tile_begin) && (seg_end == tile_end);
       const int acc = seg & 1;
       const uint32_t acc_phase = (seg >> 1) & 1;
-      ok = mbar_wait(tfull_bar(acc), acc_phase, abortp);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = mbar_wait_warp(tfull_bar(acc), acc_phase, abortp, lane);
       if (!ok && lane == 0) {
         abort_flag = 1;
         atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);

@@ -554,8 +554,7 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, in
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
     const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
     const int acc = local & 1;
-    ok = mbar_wait(tfull0 + 8u * acc, (local >> 1) & 1, abortp);
-    ok = __all_sync(0xffffffffu, ok);
+    ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane);
     if (!ok) break;
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + acc * BN + lane_addr;

@@ -50,18 +50,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the
+// phase is incomplete, instead of returning at once.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait. `abort_flag` lives in shared memory and is set by whichever role
 // first gives up, so the other roles stop within one poll instead of each
-// sitting out its own limit.
+// sitting out its own limit. Waiting threads are parked by the hardware between polls
+// (suspend hint): eighteen warps spinning on barriers cost enough power on a
+// power-capped part to lower the clock the tensor pipe runs at.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
   }
+}
+// The same for a whole warp: lane 0 waits, the others sleep at the warp barrier.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // --------------------------------------------------------------------- TMA --
