@@ -10,7 +10,8 @@
  *     [N, K]; W_down is [K, N]; every matrix is row-major with the row pitch
  *     given in elements (a multiple of 8) and a 16-byte aligned base address.
  *   - All pointers are DEVICE pointers owned by the caller. Nothing is allocated
- *     or freed by the library and nothing is retained after a call returns.
+ *     or freed by the library and nothing is retained after a call returns (the
+ *     one exception, gmlp_peer_alloc / gmlp_peer_free, is a set-up call and says so).
  *   - `stream` is a cudaStream_t passed as void*. Work is enqueued on it and the
  *     call returns without synchronising. The caller makes the right device
  *     current before calling.
@@ -188,6 +189,43 @@ int gmlp_set_cta_pair_mode(int mode);
  * group of the persistent tile order; 0 restores the built-in default. Returns
  * the previous value; values outside [0, 4096] only query. */
 int gmlp_set_raster_group(int row_tiles);
+
+/* ---- tensor-parallel output sum over peer memory (no reference counterpart: the
+ * reference is single-GPU; this replaces an NCCL all-reduce after gmlp_down_fwd /
+ * gmlp_decode_fwd when the intermediate dimension is sharded) ----
+ *
+ * Each rank owns one REGION of gmlp_peer_region_bytes(max_elems, world) bytes that
+ * every other rank of the group has mapped: inbox slots the peers push their
+ * partials into, flag words and the rank's own call counters (layout in
+ * csrc/peer_reduce.cuh). gmlp_peer_alloc is a control-plane call, once per group:
+ * it cudaMalloc's `bytes` of zeroed device memory on the current device and exports
+ * it as 64 opaque bytes (a CUDA IPC handle) that the other ranks' processes pass to
+ * gmlp_peer_open to map it (peer access over NVLink is enabled on first use).
+ * gmlp_peer_close unmaps, gmlp_peer_free releases. The hosts exchange the handles
+ * themselves (torch.distributed.all_gather_object in the Python layer) and must
+ * not start reducing before every rank has allocated and mapped.
+ *
+ * gmlp_peer_allreduce: dst[i] = sum over ranks of src[i] (fp32 accumulation in rank
+ * order, so every rank gets the same bits) for n <= max_elems elements (a multiple
+ * of 8) of `dtype`; dst may be src. `regions` is a HOST array of `world` device
+ * pointers, regions[p] = rank p's region (local for p == rank, else as mapped by
+ * gmlp_peer_open); max_elems is the capacity the regions were sized with. Every
+ * rank of the group must make the same sequence of calls (same n). The call number
+ * is kept on the device, so a call carries no per-call host state. src must be
+ * complete on `stream` before the call. `dependent` != 0 launches the kernel as a
+ * programmatic dependent of the preceding kernel on the stream (which must be the
+ * one that wrote src). One kernel, no allocation, no host synchronisation. The
+ * wait for the peers is bounded (about a second); on expiry dst is left unwritten
+ * and gmlp_status_read returns 4. Calls that share regions must not overlap on a
+ * GPU (one stream per group). */
+size_t gmlp_peer_region_bytes(int64_t max_elems, int32_t world);
+int gmlp_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int gmlp_peer_open(const void* handle64, void** ptr);
+int gmlp_peer_close(void* ptr);
+int gmlp_peer_free(void* ptr);
+int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
+                        void* const* regions, int32_t rank, int32_t world, void* dst,
+                        int32_t dependent, void* stream);
 
 /* Reads and clears the current device's status word (synchronises the device).
  * 0 = no kernel gave up a wait since the last read. */

@@ -58,6 +58,65 @@ def main():
         assert md._decode_scratch is not None
         orc.assert_parity(yd.cpu(), orc.forward_backward(cased, grads=False)["y"], "tp decode y")
 
+        # ---------------- one-shot sum over peer memory: bit-exact against the rank-ordered fp32 sum,
+        # many calls in flight (no host synchronisation between them: the two inbox parities
+        # and the epoch flags alone keep the ranks apart), out of place and in place
+        comm = P.PeerAllReduce(dist.group.WORLD, 64 * 1024, dt, dev)
+        for shape in ((1, 8), (8, 512), (64, 1024), (3, 1000)):
+            gen = torch.Generator().manual_seed(1000 + shape[1])
+            steps = 24
+            vals = torch.randn((steps, world) + shape, generator=gen).to(dt)      # every rank's partials
+            acc = torch.zeros((steps,) + shape)
+            for r in range(world):                                                # rank order, fp32
+                acc += vals[:, r].float()
+            want_sum = acc.to(dt)
+            mine = vals[:, rank].to(dev)
+            outs = []
+            for it in range(steps):
+                if it % 2:
+                    buf = mine[it].clone()
+                    outs.append(comm.all_reduce(buf, out=buf))
+                else:
+                    outs.append(comm.all_reduce(mine[it]))
+            got = torch.stack(outs).cpu()
+            assert torch.equal(got.view(torch.int16), want_sum.view(torch.int16)), f"peer all-reduce {shape}"
+
+        # the same calls captured once in a CUDA graph and replayed: the call number lives on the device
+        shape = (16, 512)
+        gen = torch.Generator().manual_seed(4242)
+        vals = torch.randn((2, world) + shape, generator=gen).to(dt)
+        src = [vals[i, rank].to(dev) for i in range(2)]
+        dst = [torch.empty(shape, dtype=dt, device=dev) for _ in range(2)]
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            comm.all_reduce(src[0], out=dst[0])     # warm-up outside the capture, on every rank alike
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                comm.all_reduce(src[0], out=dst[0])
+                comm.all_reduce(src[1], out=dst[1])
+                comm.all_reduce(src[0], out=dst[0])
+        torch.cuda.current_stream(dev).wait_stream(side)
+        for _ in range(5):
+            graph.replay()
+        for i in range(2):
+            want_i = sum(vals[i, r].float() for r in range(world)).to(dt)
+            assert torch.equal(dst[i].cpu().view(torch.int16), want_i.view(torch.int16)), "peer all-reduce replay"
+
+        # ---------------- the decode path with the peer sum chained to the down projection
+        y_nccl = yd.clone()
+        md.enable_peer_allreduce(max_tokens=64)
+        with torch.no_grad():
+            for it in range(4):
+                yp = md(cased.x.to(dev))
+        orc.assert_parity(yp.cpu(), orc.forward_backward(cased, grads=False)["y"], "tp decode y (peer sum)")
+        assert (yp.float() - y_nccl.float()).abs().max().item() <= 2e-2
+        every = [torch.empty_like(yp) for _ in range(world)]
+        dist.all_gather(every, yp)
+        assert all(torch.equal(e, every[0]) for e in every), "ranks disagree on the summed output"
+        md._peer.close()
+        comm.close()
+
         # ---------------- token sharding: no collective, mask rows offset
         Mt = 256 * world
         caset = orc.make_case(Mt, K, 512, False, dt, seed=13, w_std=0.5 * K ** -0.5, dy_std=0.05)

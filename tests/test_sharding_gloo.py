@@ -13,6 +13,61 @@ ROOT = Path(__file__).resolve().parent.parent
 WORLD = 2
 
 
+class _FakePeerBackend:
+    """Stands in for the CUDA IPC + kernel side of PeerAllReduce: recorded calls, no device."""
+
+    def __init__(self, rank):
+        self.rank, self.launches, self.closed, self.freed = rank, [], [], []
+
+    def region_bytes(self, max_elems, world):
+        return 2 * world * max_elems * 2 + 4096
+
+    def alloc(self, nbytes):
+        self.nbytes = nbytes
+        return 0x7000 + self.rank, bytes([self.rank]) * 64
+
+    def open(self, handle):
+        return 0x10000000 * (handle[0] + 1)
+
+    def allreduce(self, dtype, n, max_elems, src, regions, rank, world, dst, dependent):
+        self.launches.append((n, max_elems, src.data_ptr(), list(regions), rank, world, dst.data_ptr(), dependent))
+
+    def close(self, ptr):
+        self.closed.append(ptr)
+
+    def free(self, ptr):
+        self.freed.append(ptr)
+
+
+def _peer_host_logic(P, rank):
+    """Handle exchange, argument checks and teardown of PeerAllReduce (no GPU involved)."""
+    fake = _FakePeerBackend(rank)
+    comm = P.PeerAllReduce(dist.group.WORLD, 64 * 24, torch.bfloat16, torch.device("cpu"), backend=fake)
+    other = 1 - rank
+    assert fake.nbytes == fake.region_bytes(64 * 24, WORLD)
+    assert comm.regions[rank] == 0x7000 + rank and comm.regions[other] == 0x10000000 * (other + 1)
+    part = torch.zeros((8, 24), dtype=torch.bfloat16)
+    out = comm.all_reduce(part, dependent=True)
+    assert out.shape == (8, 24) and out.data_ptr() != part.data_ptr()
+    assert fake.launches[-1] == (192, 64 * 24, part.data_ptr(), comm.regions, rank, WORLD, out.data_ptr(), True)
+    assert comm.all_reduce(part, out=part) is part            # in place
+    assert fake.launches[-1][2] == fake.launches[-1][6] == part.data_ptr() and comm.calls == 2
+    for bad in (torch.zeros((65, 24), dtype=torch.bfloat16),     # more than max_elems
+                torch.zeros((1, 12), dtype=torch.bfloat16),      # not a multiple of 8 elements
+                torch.zeros((8, 24), dtype=torch.float16),       # not the group's dtype
+                torch.zeros((8, 48), dtype=torch.bfloat16)[:, ::2]):   # not contiguous
+        assert not comm.supports(bad)
+        with pytest.raises(ValueError):
+            comm.all_reduce(bad)
+    with pytest.raises(ValueError):
+        comm.all_reduce(part, out=torch.zeros((4, 24), dtype=torch.bfloat16))
+    comm.close()
+    assert fake.closed == [0x10000000 * (other + 1)] and fake.freed == [0x7000 + rank]
+    comm.close()                                              # idempotent
+    with pytest.raises(RuntimeError):
+        comm.all_reduce(part)
+
+
 def _worker(rank, port, mode, ret):
     sys.path.insert(0, str(ROOT))
     sys.path.insert(0, str(ROOT / "tests"))
@@ -47,6 +102,8 @@ def _worker(rank, port, mode, ret):
             torch.testing.assert_close(g["dx"], want["dx"], rtol=1e-4, atol=1e-5)
             for k, v in full.items():
                 torch.testing.assert_close(v, want["d" + k], rtol=1e-4, atol=1e-5)
+        elif mode == "peer":
+            _peer_host_logic(P, rank)
         else:
             r0, rows = P.token_shard_range(M, rank, WORLD)
             ks = orc.keep_scale_tensor(rows, N, p, seed, offset, row0=r0)
@@ -65,9 +122,9 @@ def _worker(rank, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "token"])
+@pytest.mark.parametrize("mode", ["tp", "token", "peer"])
 def test_two_rank_sharding(mode):
-    port = 29500 + (os.getpid() % 2000) + (0 if mode == "tp" else 1)
+    port = 29500 + (os.getpid() % 2000) + {"tp": 0, "token": 1, "peer": 2}[mode]
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(port, mode, ret), nprocs=WORLD, join=True)

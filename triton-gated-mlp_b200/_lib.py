@@ -22,7 +22,8 @@ EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group",
-    "gmlp_status_read", "gmlp_last_error", "gmlp_version",
+    "gmlp_peer_region_bytes", "gmlp_peer_alloc", "gmlp_peer_open", "gmlp_peer_close", "gmlp_peer_free",
+    "gmlp_peer_allreduce", "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
 
 
@@ -66,6 +67,13 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_decode_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_set_cta_pair_mode.argtypes = [i32]
     lib.gmlp_set_raster_group.argtypes = [i32]
+    lib.gmlp_peer_region_bytes.argtypes = [i64, i32]
+    lib.gmlp_peer_region_bytes.restype = C.c_size_t
+    lib.gmlp_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), vp]
+    lib.gmlp_peer_open.argtypes = [vp, C.POINTER(vp)]
+    lib.gmlp_peer_close.argtypes = [vp]
+    lib.gmlp_peer_free.argtypes = [vp]
+    lib.gmlp_peer_allreduce.argtypes = [i32, i64, i64, vp, C.POINTER(vp), i32, i32, vp, i32, vp]
     lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]
     lib.gmlp_last_error.restype = C.c_char_p
     lib.gmlp_version.restype = C.c_int

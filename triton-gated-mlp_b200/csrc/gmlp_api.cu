@@ -12,6 +12,7 @@
 #include "decode_stream.cuh"
 #include "elementwise.cuh"
 #include "gemm_tcgen05.cuh"
+#include "peer_reduce.cuh"
 
 namespace gmlp {
 
@@ -812,6 +813,129 @@ extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, con
     colsum_final_kernel<__half><<<fin_blocks, 256, 0, st>>>(part, cols, rb,
                                                             static_cast<__half*>(dst));
   }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+// ------------------------------------------------- peer memory + all-reduce --
+extern "C" size_t gmlp_peer_region_bytes(int64_t max_elems, int32_t world) {
+  if (max_elems <= 0 || world < 2 || world > gmlp::PEER_MAX_WORLD) return 0;
+  return static_cast<size_t>(gmlp::peer_region_bytes(max_elems, world));
+}
+
+extern "C" int gmlp_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+  using namespace gmlp;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI carries the handle as 64 opaque bytes");
+  if (!ptr || !handle64 || bytes == 0) return fail(GMLP_ERR_ARG, "NULL pointer or zero size");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+  e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(GMLP_ERR_LAUNCH, "peer buffer set-up: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *ptr = p;
+  return GMLP_OK;
+}
+
+extern "C" int gmlp_peer_open(const void* handle64, void** ptr) {
+  using namespace gmlp;
+  if (!ptr || !handle64) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+  *ptr = p;
+  return GMLP_OK;
+}
+
+extern "C" int gmlp_peer_close(void* ptr) {
+  using namespace gmlp;
+  if (!ptr) return GMLP_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+extern "C" int gmlp_peer_free(void* ptr) {
+  using namespace gmlp;
+  if (!ptr) return GMLP_OK;
+  const cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaFree: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
+                                   void* const* regions, int32_t rank, int32_t world, void* dst,
+                                   int32_t dependent, void* stream) {
+  using namespace gmlp;
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (world < 2 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+    return fail(GMLP_ERR_ARG, "peer all-reduce needs 2 <= world <= %d and 0 <= rank < world; got rank %d of %d",
+                PEER_MAX_WORLD, rank, world);
+  if (n <= 0 || (n % 8) != 0 || n > max_elems)
+    return fail(GMLP_ERR_SHAPE,
+                "peer all-reduce needs a positive element count that is a multiple of 8 and at most the "
+                "regions' capacity of %lld; got %lld",
+                static_cast<long long>(max_elems), static_cast<long long>(n));
+  if (!src || !regions || !dst) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(src) || !aligned16(dst))
+    return fail(GMLP_ERR_ALIGN, "src and dst must be 16-byte aligned");
+  PeerReduceArgs a;
+  memset(&a, 0, sizeof(a));
+  for (int p = 0; p < world; ++p) {
+    if (!regions[p]) return fail(GMLP_ERR_ARG, "NULL region for rank %d", p);
+    if (!aligned16(regions[p])) return fail(GMLP_ERR_ALIGN, "region of rank %d must be 16-byte aligned", p);
+    a.region[p] = static_cast<char*>(regions[p]);
+  }
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  a.src = src;
+  a.dst = dst;
+  a.n = n;
+  a.max_elems = max_elems;
+  a.rank = rank;
+  a.world = world;
+  a.dependent = dependent ? 1 : 0;
+  a.status = dev->status_ptr;
+  // The grid depends on n alone, so that block b means the same slice on every rank.
+  const long long vecs = n / 8;
+  long long blocks = (vecs + PEER_THREADS - 1) / PEER_THREADS;
+  if (blocks > PEER_MAX_BLOCKS) blocks = PEER_MAX_BLOCKS;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(PEER_THREADS);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = dtype == GMLP_BF16
+                      ? cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__nv_bfloat16>, a)
+                      : cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__half>, a);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;

@@ -146,6 +146,7 @@ class FusedGatedMLP(nn.Module):
         self.philox_seed = int(philox_seed)
         self.philox_offset = 0
         self._decode_scratch = None
+        self._peer = None
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -170,8 +171,24 @@ class FusedGatedMLP(nn.Module):
                                self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1],
                                act=self.act_fn, residual=residual if own_bias else None)
         if tp_group is not None:
-            parallel.all_reduce_sum(y, tp_group)
+            if self._peer is not None and self._peer.supports(y):
+                # the partial outputs are summed through the peers' memory, in place, chained to
+                # the down-projection kernel as a programmatic dependent
+                self._peer.all_reduce(y, out=y, dependent=True)
+            else:
+                parallel.all_reduce_sum(y, tp_group)
         return y
+
+    def enable_peer_allreduce(self, max_tokens: int = 64) -> "parallel.PeerAllReduce":
+        """Collective over the tensor-parallel group: from now on the decode path sums its partial
+        outputs with the one-shot peer-memory kernel instead of an NCCL all-reduce. Call after the
+        module has been moved to its device and dtype."""
+        if self.parallel_mode != "tp":
+            raise ValueError("enable_peer_allreduce applies to parallel_mode='tp'")
+        group = self.process_group if self.process_group is not None else parallel.default_group()
+        w = self.down_proj.weight
+        self._peer = parallel.PeerAllReduce(group, int(max_tokens) * self.hidden_size, w.dtype, w.device)
+        return self._peer
 
     def forward(self, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
         """y = down(dropout(act(gate(x)) * up(x))) (+ residual, fused into the down projection's epilogue;

@@ -90,14 +90,23 @@ def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     return (h, g, u) if save else h
 
 
-def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor | None = None) -> Tensor:
-    """y = h W_down^T (+ b_down) (+ residual)."""
+def _out_buffer(out: Tensor | None, shape, dt: torch.dtype, dev: torch.device) -> Tensor:
+    if out is None:
+        return torch.empty(shape, dtype=dt, device=dev)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dt or out.device != dev or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {tuple(shape)} {dt} tensor on {dev}")
+    return out
+
+
+def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor | None = None,
+             out: Tensor | None = None) -> Tensor:
+    """y = h W_down^T (+ b_down) (+ residual), written into `out` when given."""
     dev = require_cuda(h, w_down, b_down, residual)
     dt = _same_dtype(h, w_down, b_down, residual)
     h, w_down, b_down, residual = _c(h), _c(w_down), _c(b_down), _c(residual)
     M, N = h.shape
     K = w_down.shape[0]
-    y = torch.empty((M, K), dtype=dt, device=dev)
+    y = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
         prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
         with torch.cuda.device(dev):
@@ -213,8 +222,9 @@ def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device
 
 def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
                w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
-               residual: Tensor | None = None) -> Tensor:
-    """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens."""
+               residual: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+    """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens,
+    written into `out` when given."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
     dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
     residual = _c(residual)
@@ -227,7 +237,7 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     if scratch is None:
         scratch = decode_scratch(M, K, N, dt, dev)
     h = torch.empty((M, N), dtype=dt, device=dev)
-    y = torch.empty((M, K), dtype=dt, device=dev)
+    y = _out_buffer(out, (M, K), dt, dev)
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
     with torch.cuda.device(dev):
         check(load().gmlp_decode_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),

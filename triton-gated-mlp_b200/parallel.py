@@ -96,3 +96,127 @@ def all_reduce_sum(t: Tensor, group) -> Tensor:
     if dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
+
+
+class _LibPeerBackend:
+    """The libgmlp side of PeerAllReduce: CUDA IPC regions and the one-shot reduction kernel."""
+
+    def __init__(self, device: torch.device):
+        import ctypes as C
+
+        from . import _lib
+        self._C, self._lib_mod, self.device = C, _lib, device
+        self.lib = _lib.load()
+
+    def region_bytes(self, max_elems: int, world: int) -> int:
+        return int(self.lib.gmlp_peer_region_bytes(max_elems, world))
+
+    def alloc(self, nbytes: int):
+        C = self._C
+        p, handle = C.c_void_p(), C.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_alloc(nbytes, C.byref(p), handle))
+        return int(p.value), bytes(handle.raw)
+
+    def open(self, handle: bytes) -> int:
+        C = self._C
+        p = C.c_void_p()
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_open(handle, C.byref(p)))
+        return int(p.value)
+
+    def close(self, ptr: int) -> None:
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_close(ptr))
+
+    def free(self, ptr: int) -> None:
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_free(ptr))
+
+    def allreduce(self, dtype: torch.dtype, n: int, max_elems: int, src: Tensor, regions, rank: int, world: int,
+                  dst: Tensor, dependent: bool) -> None:
+        C = self._C
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_allreduce(
+                self._lib_mod.dtype_code(dtype), n, max_elems, src.data_ptr(), (C.c_void_p * world)(*regions),
+                rank, world, dst.data_ptr(), 1 if dependent else 0,
+                torch.cuda.current_stream(self.device).cuda_stream))
+
+
+class PeerAllReduce:
+    """Sum of a small tensor over the tensor-parallel group through the peers' memory.
+
+    For the partial outputs of the down projection at decode sizes (up to about 1 MB),
+    where a ring all-reduce is dominated by its latency: one kernel per rank pushes its
+    partial into every peer's inbox over NVLink (plain peer stores), exchanges flags and
+    adds the partials in rank order, so the ranks get identical bits. Construction is
+    collective over `group`: every rank allocates one peer-mappable region and maps
+    everyone else's. Then, on every rank alike and on one stream:
+
+        y = comm.all_reduce(y_partial)            # or out=y_partial for in place
+
+    The call number lives on the device, so calls can be captured in a CUDA graph and
+    replayed (by all ranks alike). The reference has no multi-GPU path; this replaces
+    parallel.all_reduce_sum (NCCL) on the decode path only.
+    """
+
+    def __init__(self, group, max_elems: int, dtype: torch.dtype, device: torch.device, backend=None):
+        if dtype not in (torch.bfloat16, torch.float16):
+            raise NotImplementedError(f"peer all-reduce sums bfloat16 or float16 partials; got {dtype}")
+        if max_elems <= 0:
+            raise ValueError("max_elems must be positive")
+        self.group, self.dtype, self.device = group, dtype, device
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError(f"peer all-reduce covers 2 to 8 ranks of one NVLink domain; group has {self.world}")
+        self.backend = backend if backend is not None else _LibPeerBackend(device)
+        self.max_elems = int(max_elems)
+        self.region_bytes = self.backend.region_bytes(self.max_elems, self.world)
+        self.local_ptr, handle = self.backend.alloc(self.region_bytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.regions = [self.local_ptr if r == self.rank else self.backend.open(handles[r])
+                        for r in range(self.world)]
+        # Nobody may push into a region before its owner has zeroed it and everyone has mapped it.
+        dist.barrier(group=group)
+        self.calls = 0
+
+    def supports(self, t: Tensor) -> bool:
+        n = t.numel()
+        return t.dtype == self.dtype and t.is_contiguous() and 0 < n <= self.max_elems and n % 8 == 0
+
+    def all_reduce(self, partial: Tensor, out: Optional[Tensor] = None, dependent: bool = False) -> Tensor:
+        """Sum of `partial` over the ranks, enqueued on the current stream; returns `out` (allocated if None,
+        may be `partial` itself).
+
+        `dependent=True` launches the reduction as a programmatic dependent of the
+        preceding kernel on the stream, which must be the one that wrote `partial`.
+        """
+        if self.regions is None:
+            raise RuntimeError("this PeerAllReduce has been closed")
+        if not self.supports(partial):
+            raise ValueError(
+                f"partial must be a contiguous {self.dtype} tensor of a positive multiple of 8 elements, "
+                f"at most {self.max_elems}; got {tuple(partial.shape)} {partial.dtype}")
+        if out is None:
+            out = torch.empty_like(partial)
+        elif out.numel() != partial.numel() or out.dtype != self.dtype or not out.is_contiguous():
+            raise ValueError("out must be a contiguous tensor of the partial's size and dtype")
+        self.calls += 1
+        self.backend.allreduce(self.dtype, partial.numel(), self.max_elems, partial, self.regions, self.rank,
+                               self.world, out, dependent)
+        return out
+
+    def close(self) -> None:
+        """Collective: unmap the peers' regions and free this rank's (after everyone has stopped using them)."""
+        if self.regions is None:
+            return
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for r, b in enumerate(self.regions):
+            if r != self.rank:
+                self.backend.close(b)
+        dist.barrier(group=self.group)
+        self.backend.free(self.local_ptr)
+        self.regions = None
