@@ -190,6 +190,14 @@ int gmlp_set_cta_pair_mode(int mode);
  * the previous value; values outside [0, 4096] only query. */
 int gmlp_set_raster_group(int row_tiles);
 
+/* Scheduling hook with no counterpart in the reference: the number of SMs the
+ * persistent GEMM grids of the calls above may occupy (0 = all, the default). A host
+ * that overlaps a collective (NCCL) with the GEMMs lowers it for those launches so
+ * that the collective's CTAs find free SMs; with every SM held by a persistent CTA
+ * they would wait for the GEMM to end. Returns the previous value; values outside
+ * [0, 4096] only query. Decode and elementwise kernels are not affected. */
+int gmlp_set_sm_limit(int sms);
+
 /* ---- tensor-parallel output sum over peer memory (no reference counterpart: the
  * reference is single-GPU; this replaces an NCCL all-reduce after gmlp_down_fwd /
  * gmlp_decode_fwd when the intermediate dimension is sharded) ----

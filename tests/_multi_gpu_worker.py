@@ -46,6 +46,21 @@ def main():
         for n, g in full.items():
             orc.assert_parity(g.cpu(), want["d" + n], "tp d" + n)
 
+        # ---------------- the same step with the down projection and dx computed in chunks of 128 rows,
+        # each chunk's all-reduce overlapping the next chunk's GEMM
+        m.tp_chunk_rows = 128
+        m.zero_grad(set_to_none=True)
+        m.set_philox(seed, offset)
+        x2 = case.x.to(dev).requires_grad_(True)
+        y2 = m(x2)
+        y2.backward(case.dy.to(dev))
+        orc.assert_parity(y2.cpu(), want["y"], "tp y (chunked)")
+        orc.assert_parity(x2.grad.cpu(), want["dx"], "tp dx (chunked)")
+        full2 = P.gather_tp_grads({n: q.grad for n, q in m.named_parameters()})
+        for n, g in full2.items():
+            assert torch.equal(g, full[n]), f"chunking changed d{n}"
+        assert pkg._lib.set_sm_limit(0) == 0, "the SM limit must be back to 0 after a chunked step"
+
         # ---------------- tensor parallel, decode path (M <= 64, no grad)
         Md, Kd, Nd = 8, 512, 256 * world
         cased = orc.make_case(Md, Kd, Nd, True, dt, seed=12, w_std=0.5 * Kd ** -0.5)

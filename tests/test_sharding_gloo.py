@@ -104,6 +104,24 @@ def _worker(rank, port, mode, ret):
                 torch.testing.assert_close(v, want["d" + k], rtol=1e-4, atol=1e-5)
         elif mode == "peer":
             _peer_host_logic(P, rank)
+        elif mode == "overlap":
+            # chunked partial sums with the all-reduce of chunk i started before chunk i+1 is produced
+            assert P.chunk_ranges(10, 4) == [(0, 4), (4, 8), (8, 10)] and P.chunk_ranges(10, 0) == [(0, 10)]
+            assert P.chunk_ranges(10, 10) == [(0, 10)] and P.chunk_ranges(0, 4) == []
+            sd = P.shard_tp_state_dict(case.state_dict(), rank, WORLD)
+            h = orc.hidden_forward(x, sd["gate_proj.weight"], sd["gate_proj.bias"], sd["up_proj.weight"],
+                                   sd["up_proj.bias"])[0]
+            y = torch.empty((M, K))
+            log = []
+
+            def produce(r0, r1):
+                log.append(("rows", r0, r1))
+                y[r0:r1] = h[r0:r1] @ sd["down_proj.weight"].T + (bd if rank == 0 else 0.0)
+
+            works = P.overlapped_all_reduce(y, produce, dist.group.WORLD, 20, lambda on: log.append(("limit", on)))
+            assert log == [("rows", 0, 20), ("limit", True), ("rows", 20, 40), ("rows", 40, 48)] and len(works) == 3
+            P.wait_all(works)
+            torch.testing.assert_close(y, orc.forward_backward(case, grads=False)["y"], rtol=1e-4, atol=1e-5)
         else:
             r0, rows = P.token_shard_range(M, rank, WORLD)
             ks = orc.keep_scale_tensor(rows, N, p, seed, offset, row0=r0)
@@ -122,9 +140,9 @@ def _worker(rank, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["tp", "token", "peer"])
+@pytest.mark.parametrize("mode", ["tp", "token", "peer", "overlap"])
 def test_two_rank_sharding(mode):
-    port = 29500 + (os.getpid() % 2000) + {"tp": 0, "token": 1, "peer": 2}[mode]
+    port = 29500 + (os.getpid() % 2000) + {"tp": 0, "token": 1, "peer": 2, "overlap": 3}[mode]
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(port, mode, ret), nprocs=WORLD, join=True)

@@ -292,18 +292,43 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
 
-      bool finish = complete;
-      if (!complete) {
-        // Store this CTA's partial tile to its own slot, then count it.
-        const int which = (u == u_begin) ? 0 : 1;
-        float* slot = args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS;
+      // One output chunk: columns (tokens) [m0, m0 + C) of this thread's weight row.
+      const long long wrow = tile * 128 + r_in_tile;
+      const float b0 = (bias0 && wrow < args.rows) ? static_cast<float>(bias0[wrow]) : 0.f;
+      const float b1 = (DUAL && bias1 && wrow < args.rows) ? static_cast<float>(bias1[wrow]) : 0.f;
+      auto emit = [&](int m0, const float* first, const float* second, int count) {
+        if (wrow >= args.rows) return;
 #pragma unroll
-        for (int a = 0; a < NACC; ++a) {
-          float4* dst = reinterpret_cast<float4*>(slot + (static_cast<long long>(a) * 128 + r_in_tile) * MPAD);
+        for (int i = 0; i < count; ++i) {
+          const int m = m0 + i;
+          if (m < args.M) {
+            float o;
+            if (DUAL) {
+              o = act_value(args.act, first[i] + b0) * (second[i] + b1);
+            } else {
+              o = first[i] + b0;
+            }
+            const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
+            if (!DUAL && residual) o += static_cast<float>(residual[oi]);
+            out[oi] = static_cast<T>(o);
+          }
+        }
+      };
+
+      if (complete) {
+        emit(0, v[0], v[NACC - 1], MPAD);
+      } else {
+        // Store this CTA's partial tile to its own slot, then count it. Slot layout:
+        // float4 (a, i, row) at index (a * MPAD/4 + i) * 128 + row, so that the 32 lanes
+        // of a warp (32 consecutive rows) touch 512 contiguous bytes per access.
+        const int which = (u == u_begin) ? 0 : 1;
+        float4* slot4 = reinterpret_cast<float4*>(args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS);
+#pragma unroll
+        for (int a = 0; a < NACC; ++a)
 #pragma unroll
           for (int i = 0; i < MPAD / 4; ++i)
-            dst[i] = make_float4(v[a][4 * i], v[a][4 * i + 1], v[a][4 * i + 2], v[a][4 * i + 3]);
-        }
+            slot4[(a * (MPAD / 4) + i) * 128 + r_in_tile] =
+                make_float4(v[a][4 * i], v[a][4 * i + 1], v[a][4 * i + 2], v[a][4 * i + 3]);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         if (ep_tid == 0) {
@@ -312,56 +337,59 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
           last_flag = (old + nkb == args.kbt) ? 1 : 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        finish = last_flag != 0;
-        if (finish) {
+        if (last_flag != 0) {
           __threadfence();
-          // Sum every contributor's slot in CTA order (deterministic).
+          // Sum every contributor's slot (this CTA's own included) in CTA order, which
+          // makes the result independent of arrival order. The accumulator registers are
+          // dead by now, so the sum runs chunk by chunk with FIX_BATCH contributors'
+          // loads in flight at once (the tail of a short kernel is this loop's latency).
           const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
           const long long c_last = (tile_end * gridDim.x - 1) / total;
+          constexpr int CHUNK4 = NACC == 2 ? 2 : 4;  // float4 columns per chunk and accumulator
+          constexpr int FIX_BATCH = 8;
+#pragma unroll 1
+          for (int ch = 0; ch < MPAD / (4 * CHUNK4); ++ch) {
+            float sum[NACC][4 * CHUNK4];
 #pragma unroll
-          for (int a = 0; a < NACC; ++a)
+            for (int a = 0; a < NACC; ++a)
 #pragma unroll
-            for (int i = 0; i < MPAD; ++i) v[a][i] = 0.f;
-          for (long long c = c_first; c <= c_last; ++c) {
-            const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
-            const float* src = args.slots + (2LL * c + w) * SLOT_FLOATS;
+              for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
+#pragma unroll 1
+            for (long long cb = c_first; cb <= c_last; cb += FIX_BATCH) {
+              float4 q[FIX_BATCH][NACC][CHUNK4];
 #pragma unroll
-            for (int a = 0; a < NACC; ++a) {
-              const float4* s4 = reinterpret_cast<const float4*>(
-                  src + (static_cast<long long>(a) * 128 + r_in_tile) * MPAD);
+              for (int jc = 0; jc < FIX_BATCH; ++jc) {
+                const long long c = cb + jc;
+                if (c <= c_last) {
+                  const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
+                  const float4* s4 = reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
 #pragma unroll
-              for (int i = 0; i < MPAD / 4; ++i) {
-                const float4 q = __ldcg(s4 + i);
-                v[a][4 * i] += q.x;
-                v[a][4 * i + 1] += q.y;
-                v[a][4 * i + 2] += q.z;
-                v[a][4 * i + 3] += q.w;
+                  for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                    for (int i = 0; i < CHUNK4; ++i)
+                      q[jc][a][i] = __ldcg(s4 + (a * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
+                } else {
+#pragma unroll
+                  for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                    for (int i = 0; i < CHUNK4; ++i) q[jc][a][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
               }
+#pragma unroll
+              for (int jc = 0; jc < FIX_BATCH; ++jc)
+#pragma unroll
+                for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                  for (int i = 0; i < CHUNK4; ++i) {
+                    sum[a][4 * i] += q[jc][a][i].x;
+                    sum[a][4 * i + 1] += q[jc][a][i].y;
+                    sum[a][4 * i + 2] += q[jc][a][i].z;
+                    sum[a][4 * i + 3] += q[jc][a][i].w;
+                  }
             }
+            emit(ch * 4 * CHUNK4, sum[0], sum[NACC - 1], 4 * CHUNK4);
           }
           if (ep_tid == 0) args.counters[tile] = 0;  // leave the scratch ready for the next call
-        }
-      }
-      if (finish) {
-        const long long wrow = tile * 128 + r_in_tile;
-        if (wrow < args.rows) {
-          const float b0 = bias0 ? static_cast<float>(bias0[wrow]) : 0.f;
-          const float b1 = (DUAL && bias1) ? static_cast<float>(bias1[wrow]) : 0.f;
-#pragma unroll
-          for (int m = 0; m < MPAD; ++m) {
-            if (m < args.M) {
-              float o;
-              if (DUAL) {
-                const float g = v[0][m] + b0;
-                o = act_value(args.act, g) * (v[NACC - 1][m] + b1);
-              } else {
-                o = v[0][m] + b0;
-              }
-              const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
-              if (!DUAL && residual) o += static_cast<float>(residual[oi]);
-              out[oi] = static_cast<T>(o);
-            }
-          }
         }
       }
       u = seg_end;

@@ -148,6 +148,13 @@ struct Epilogue {
 static int g_pair_mode = 0;
 // Row tiles per raster group; 0 = the built-in default.
 static int g_group_m = 0;
+// CTAs the persistent GEMM grids may occupy; 0 = every SM. Lowered by a caller that
+// runs a collective's kernels beside the GEMMs and has to leave them SMs to land on.
+static int g_sm_limit = 0;
+static int64_t gemm_cta_budget(int sm_count) {
+  int64_t b = (g_sm_limit > 0 && g_sm_limit < sm_count) ? g_sm_limit : sm_count;
+  return b < 2 ? 2 : b;
+}
 
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
 static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
@@ -213,7 +220,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.group_m = g_group_m > 0 ? g_group_m : (pair ? 16 : 32);
   cudaError_t e;
   if (pair) {
-    const int64_t max_pairs = dev->sm_count / 2;
+    const int64_t max_pairs = gemm_cta_budget(dev->sm_count) / 2;
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     constexpr size_t smem = gemm_pair_smem_bytes<BN, PAIR_STAGES>();
     auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES>;
@@ -223,7 +230,8 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
       return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
   } else {
-    const int grid = static_cast<int>(tiles < dev->sm_count ? tiles : dev->sm_count);
+    const int64_t budget = gemm_cta_budget(dev->sm_count);
+    const int grid = static_cast<int>(tiles < budget ? tiles : budget);
     constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
     auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
     e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -313,6 +321,12 @@ int gmlp_version(void) { return 101; }
 int gmlp_set_cta_pair_mode(int mode) {
   const int prev = g_pair_mode;
   if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+  return prev;
+}
+
+int gmlp_set_sm_limit(int sms) {
+  const int prev = g_sm_limit;
+  if (sms >= 0 && sms <= 4096) g_sm_limit = sms;
   return prev;
 }
 

@@ -26,7 +26,7 @@ from .ops import kernels
 from .ops.fwd import SUPPORTED_ACTS, mlp_hidden_states_fwd  # noqa: F401  (re-exported like the reference)
 from .ops.bwd import mlp_hidden_states_bwd  # noqa: F401
 from .ops.kernels import Dropout, Shard
-from . import parallel
+from . import _lib, parallel
 
 
 # torch twins of the gate activations, kept as `module.act` like the reference does (gated_mlp.py:218).
@@ -34,6 +34,19 @@ _ACT_MODULES = {
     "silu": nn.SiLU, "swish": nn.SiLU, "no_act": nn.Identity, "relu": nn.ReLU, "gelu": nn.GELU,
     "sigmoid": nn.Sigmoid, "tanh": nn.Tanh, "leaky_relu": nn.LeakyReLU,
 }
+
+
+class _SmLimit:
+    """Callable that keeps `comm_sms` SMs free of persistent GEMM CTAs (True) or gives them back (False)."""
+
+    def __init__(self, device: torch.device, comm_sms: int):
+        self.sms = max(2, torch.cuda.get_device_properties(device).multi_processor_count - max(0, int(comm_sms)))
+        self.on = False
+
+    def __call__(self, on: bool) -> None:
+        if on != self.on:
+            _lib.set_sm_limit(self.sms if on else 0)
+            self.on = on
 
 
 class FusedGatedMLPFunction(Function):
@@ -47,7 +60,7 @@ class FusedGatedMLPFunction(Function):
     def forward(ctx, x: Tensor, W_gate: Tensor, b_gate: Optional[Tensor], W_up: Tensor,
                 b_up: Optional[Tensor], W_down: Tensor, b_down: Optional[Tensor],
                 drop: Dropout, shard: Shard, tp_group, act: str = "silu",
-                residual: Optional[Tensor] = None) -> Tensor:
+                residual: Optional[Tensor] = None, tp_chunk_rows: int = 0, tp_comm_sms: int = 16) -> Tensor:
         need_bwd = any(ctx.needs_input_grad)
         if need_bwd:
             h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True, act=act)
@@ -57,12 +70,28 @@ class FusedGatedMLPFunction(Function):
         # With the intermediate dimension sharded, every rank holds a partial sum
         # of y; the output bias is added once, by the rank that owns column 0.
         owner = tp_group is None or shard.col0 == 0
-        y = kernels.down_fwd(h, W_down, b_down if owner else None, residual if owner else None)
-        if tp_group is not None:
-            parallel.all_reduce_sum(y, tp_group)
+        bias, res = (b_down if owner else None), (residual if owner else None)
+        if tp_group is not None and tp_chunk_rows > 0:
+            # Down projection chunk by chunk over the token rows: chunk i's all-reduce
+            # (NCCL, on its own stream) runs beside chunk i+1's GEMM.
+            y = torch.empty((x.shape[0], W_down.shape[0]), dtype=x.dtype, device=x.device)
+            limit = _SmLimit(x.device, tp_comm_sms)
+            try:
+                works = parallel.overlapped_all_reduce(
+                    y, lambda r0, r1: kernels.down_fwd(h[r0:r1], W_down, bias, None if res is None else res[r0:r1],
+                                                       out=y[r0:r1]),
+                    tp_group, tp_chunk_rows, limit)
+            finally:
+                limit(False)
+            parallel.wait_all(works)
+        else:
+            y = kernels.down_fwd(h, W_down, bias, res)
+            if tp_group is not None:
+                parallel.all_reduce_sum(y, tp_group)
         if need_bwd:
             ctx.save_for_backward(x, W_gate, W_up, W_down, g, u, h)
             ctx.drop, ctx.shard, ctx.tp_group, ctx.act = drop, shard, tp_group, act
+            ctx.tp_chunk_rows, ctx.tp_comm_sms = tp_chunk_rows, tp_comm_sms
             ctx.has_bias = (b_gate is not None, b_up is not None, b_down is not None)
         return y
 
@@ -72,25 +101,40 @@ class FusedGatedMLPFunction(Function):
         need = ctx.needs_input_grad
         dy = dy.contiguous()
         dx = dW_gate = db_gate = dW_up = db_up = dW_down = db_down = None
-        need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
-        if need_hidden:
-            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act)
-            if need[0]:
-                dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
-                if ctx.tp_group is not None:
-                    parallel.all_reduce_sum(dx, ctx.tp_group)
-            if need[1] or need[3]:
-                dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
-            if need[2] and ctx.has_bias[0]:
-                db_gate = kernels.colsum(d_gate)
-            if need[4] and ctx.has_bias[1]:
-                db_up = kernels.colsum(d_up)
-        if need[5]:
-            dW_down = kernels.bwd_dw_down(dy, h)
-        if need[6] and ctx.has_bias[2]:
-            db_down = kernels.colsum(dy)
+        limit, works = None, []
+        try:
+            need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
+            if need_hidden:
+                d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act)
+                if need[0]:
+                    if ctx.tp_group is not None and ctx.tp_chunk_rows > 0:
+                        # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
+                        dx = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+                        limit = _SmLimit(x.device, ctx.tp_comm_sms)
+                        works = parallel.overlapped_all_reduce(
+                            dx, lambda r0, r1: kernels.bwd_dx(d_gate[r0:r1], d_up[r0:r1], W_gate, W_up, out=dx[r0:r1]),
+                            ctx.tp_group, ctx.tp_chunk_rows, limit)
+                        limit(True)
+                    else:
+                        dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
+                        if ctx.tp_group is not None:
+                            parallel.all_reduce_sum(dx, ctx.tp_group)
+                if need[1] or need[3]:
+                    dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
+                if need[2] and ctx.has_bias[0]:
+                    db_gate = kernels.colsum(d_gate)
+                if need[4] and ctx.has_bias[1]:
+                    db_up = kernels.colsum(d_up)
+            if need[5]:
+                dW_down = kernels.bwd_dw_down(dy, h)
+            if need[6] and ctx.has_bias[2]:
+                db_down = kernels.colsum(dy)
+        finally:
+            if limit is not None:
+                limit(False)
+        parallel.wait_all(works)
         d_res = dy if (len(need) > 11 and need[11]) else None  # y = ... + residual
-        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res
+        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res, None, None
 
 
 class FusedGatedMLP(nn.Module):
@@ -105,6 +149,14 @@ class FusedGatedMLP(nn.Module):
                      down-projection partial sums are all-reduced over
                      `process_group`.
       process_group  torch.distributed group for "tp".
+    Attributes for "tp" at prefill / training sizes (set after construction):
+      tp_chunk_rows  0 (default): one all-reduce after the whole down projection (and
+                     after the whole dx GEMM). > 0: those GEMMs run in chunks of this
+                     many token rows and each chunk's all-reduce overlaps the next
+                     chunk's GEMM (in backward the last one overlaps the weight
+                     gradients).
+      tp_comm_sms    SMs the persistent GEMM grids leave to the collective's kernels
+                     while one is in flight (default 16).
       philox_seed    dropout seed; `philox_offset` advances by one per training
                      forward call.
     """
@@ -147,6 +199,8 @@ class FusedGatedMLP(nn.Module):
         self.philox_offset = 0
         self._decode_scratch = None
         self._peer = None
+        self.tp_chunk_rows = 0
+        self.tp_comm_sms = 16
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -217,5 +271,6 @@ class FusedGatedMLP(nn.Module):
         y = FusedGatedMLPFunction.apply(
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
             self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group, self.act_fn, residual,
+            int(self.tp_chunk_rows) if tp_group is not None else 0, int(self.tp_comm_sms),
         )
         return y.view(shapes) if len(shapes) > 2 else y

@@ -150,14 +150,14 @@ def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard
     return d_gate, d_up
 
 
-def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor) -> Tensor:
-    """dx = d_gate W_gate + d_up W_up."""
+def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tensor | None = None) -> Tensor:
+    """dx = d_gate W_gate + d_up W_up, written into `out` when given."""
     dev = require_cuda(d_gate, d_up, w_gate, w_up)
     dt = _same_dtype(d_gate, d_up, w_gate, w_up)
     d_gate, d_up, w_gate, w_up = _c(d_gate), _c(d_up), _c(w_gate), _c(w_up)
     M, N = d_gate.shape
     K = w_gate.shape[1]
-    dx = torch.empty((M, K), dtype=dt, device=dev)
+    dx = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
         prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
         with torch.cuda.device(dev):

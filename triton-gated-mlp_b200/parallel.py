@@ -14,7 +14,7 @@ the gloo backend.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -96,6 +96,45 @@ def all_reduce_sum(t: Tensor, group) -> Tensor:
     if dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
     return t
+
+
+def chunk_ranges(m: int, rows: int) -> List[Tuple[int, int]]:
+    """Row ranges [r0, r1) of at most `rows` rows covering [0, m); one range when rows <= 0 or rows >= m."""
+    if m <= 0:
+        return []
+    if rows <= 0 or rows >= m:
+        return [(0, m)]
+    return [(r0, min(m, r0 + rows)) for r0 in range(0, m, rows)]
+
+
+def overlapped_all_reduce(out: Tensor, produce: Callable[[int, int], None], group, chunk_rows: int,
+                          limit_sms: Optional[Callable[[bool], None]] = None) -> list:
+    """Fill `out` chunk by chunk and sum every chunk over `group` while the next one is being computed.
+
+    `produce(r0, r1)` enqueues the kernels that write this rank's partial rows out[r0:r1] on the
+    current stream. Each chunk's all-reduce is started asynchronously right behind its kernels (NCCL
+    runs it on its own stream, ordered after them), so it runs beside the next chunk's kernels.
+    `limit_sms(True)` is called before the first launch that shares the GPU with a collective and
+    `limit_sms(False)` is left to the caller, who may want later kernels to keep sharing: persistent
+    GEMM grids otherwise hold every SM and the collective's CTAs could not start before the GEMM ends.
+    Returns the outstanding work handles; the caller waits on them (`wait_all`) before `out` is read.
+    """
+    works = []
+    if dist.get_world_size(group) == 1:
+        produce(0, out.shape[0])
+        return works
+    for i, (r0, r1) in enumerate(chunk_ranges(out.shape[0], chunk_rows)):
+        if i == 1 and limit_sms is not None:
+            limit_sms(True)
+        produce(r0, r1)
+        works.append(dist.all_reduce(out[r0:r1], op=dist.ReduceOp.SUM, group=group, async_op=True))
+    return works
+
+
+def wait_all(works: list) -> None:
+    """Make the current stream (or, on CPU ranks, the host) wait for the collectives in `works`."""
+    for w in works:
+        w.wait()
 
 
 class _LibPeerBackend:
