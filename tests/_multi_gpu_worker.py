@@ -76,16 +76,20 @@ def main():
         # ---------------- one-shot sum over peer memory: bit-exact against the rank-ordered fp32 sum,
         # many calls in flight (no host synchronisation between them: the two inbox parities
         # and the epoch flags alone keep the ranks apart), out of place and in place
-        comm = P.PeerAllReduce(dist.group.WORLD, 64 * 1024, dt, dev)
-        for shape in ((1, 8), (8, 512), (64, 1024), (3, 1000)):
+        comm = P.PeerAllReduce(dist.group.WORLD, 64 * 8192, dt, dev)
+        # up to 128 KB: every partial pushed to every peer; from 256 KB: slices reduced by their owners
+        shapes = ((1, 8), (8, 512), (64, 1024), (3, 1000), (40, 4096), (64, 8192))
+        cases = []
+        for shape in shapes:
             gen = torch.Generator().manual_seed(1000 + shape[1])
-            steps = 24
+            steps = 24 if shape[0] * shape[1] <= 65536 else 6
             vals = torch.randn((steps, world) + shape, generator=gen).to(dt)      # every rank's partials
             acc = torch.zeros((steps,) + shape)
             for r in range(world):                                                # rank order, fp32
                 acc += vals[:, r].float()
-            want_sum = acc.to(dt)
-            mine = vals[:, rank].to(dev)
+            cases.append((shape, steps, vals[:, rank].to(dev), acc.to(dt)))
+        pkg._lib.load().gmlp_set_peer_two_shot_bytes(256 * 1024)   # also with two ranks, where the default is one-shot
+        for shape, steps, mine, want_sum in cases:
             outs = []
             for it in range(steps):
                 if it % 2:
@@ -95,6 +99,12 @@ def main():
                     outs.append(comm.all_reduce(mine[it]))
             got = torch.stack(outs).cpu()
             assert torch.equal(got.view(torch.int16), want_sum.view(torch.int16)), f"peer all-reduce {shape}"
+        # the two forms and all sizes interleaved, still without host synchronisation
+        outs = [comm.all_reduce(cases[it % len(cases)][2][it % 6]) for it in range(30)]
+        for it, o in enumerate(outs):
+            want_it = cases[it % len(cases)][3][it % 6]
+            assert torch.equal(o.cpu().view(torch.int16), want_it.view(torch.int16)), f"interleaved call {it}"
+        pkg._lib.load().gmlp_set_peer_two_shot_bytes(0)
 
         # the same calls captured once in a CUDA graph and replayed: the call number lives on the device
         shape = (16, 512)

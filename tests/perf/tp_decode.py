@@ -55,7 +55,8 @@ def main():
         for q in m.parameters():
             q.data.normal_(0, 0.02)
         rows = []
-        for M in (1, 8, 64):
+        hook = pkg._lib.load().gmlp_set_peer_two_shot_bytes
+        for M in (1, 8, 32, 64):
             x = torch.randn((M, K), device=dev, dtype=torch.bfloat16)
             y = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
             with torch.no_grad():
@@ -64,14 +65,19 @@ def main():
                 t_ar_nccl = timed(lambda: dist.all_reduce(y), dev)
                 comm = m.enable_peer_allreduce(64)
                 t_peer = timed(lambda: m(x), dev)
-                t_ar_peer = timed(lambda: comm.all_reduce(y, out=y), dev)
+                hook(-1)   # every partial to every peer
+                t_ar_one = timed(lambda: comm.all_reduce(y, out=y), dev)
+                hook(1)    # slices reduced by their owners
+                t_ar_two = timed(lambda: comm.all_reduce(y, out=y), dev) if y.numel() % (8 * world) == 0 else float("nan")
+                hook(0)
                 comm.close()
-            rows.append((M, t_nccl, t_peer, t_ar_nccl, t_ar_peer))
+            rows.append((M, t_nccl, t_peer, t_ar_nccl, t_ar_one, t_ar_two))
         assert pkg._lib.status_read(dev) == 0
         if rank == 0:
-            for M, a, b, c, d in rows:
+            for M, a, b, c, d, e in rows:
                 print(f"tp{world} decode M={M}: step {a * 1e3:.1f} us with NCCL sum, {b * 1e3:.1f} us with peer sum; "
-                      f"sum alone {c * 1e3:.1f} us NCCL, {d * 1e3:.1f} us peer", flush=True)
+                      f"sum alone {c * 1e3:.1f} us NCCL, {d * 1e3:.1f} us peer one-shot, {e * 1e3:.1f} us peer two-shot",
+                      flush=True)
     finally:
         dist.destroy_process_group()
 

@@ -22,7 +22,7 @@ EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group", "gmlp_set_sm_limit",
-    "gmlp_peer_region_bytes", "gmlp_peer_alloc", "gmlp_peer_open", "gmlp_peer_close", "gmlp_peer_free",
+    "gmlp_peer_region_bytes", "gmlp_set_peer_two_shot_bytes", "gmlp_peer_alloc", "gmlp_peer_open", "gmlp_peer_close", "gmlp_peer_free",
     "gmlp_peer_allreduce", "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
 
@@ -68,6 +68,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_set_cta_pair_mode.argtypes = [i32]
     lib.gmlp_set_raster_group.argtypes = [i32]
     lib.gmlp_set_sm_limit.argtypes = [i32]
+    lib.gmlp_set_peer_two_shot_bytes.argtypes = [C.c_longlong]
+    lib.gmlp_set_peer_two_shot_bytes.restype = C.c_longlong
     lib.gmlp_peer_region_bytes.argtypes = [i64, i32]
     lib.gmlp_peer_region_bytes.restype = C.c_size_t
     lib.gmlp_peer_alloc.argtypes = [C.c_size_t, C.POINTER(vp), vp]

@@ -895,6 +895,15 @@ extern "C" int gmlp_peer_free(void* ptr) {
   return GMLP_OK;
 }
 
+// Size from which gmlp_peer_allreduce takes the two-shot form: 0 = built-in rule,
+// > 0 = that many bytes at any group size, < 0 = never.
+static long long g_two_shot_bytes = 0;
+extern "C" long long gmlp_set_peer_two_shot_bytes(long long bytes) {
+  const long long prev = g_two_shot_bytes;
+  g_two_shot_bytes = bytes;
+  return prev;
+}
+
 extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
                                    void* const* regions, int32_t rank, int32_t world, void* dst,
                                    int32_t dependent, void* stream) {
@@ -930,8 +939,15 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
   a.world = world;
   a.dependent = dependent ? 1 : 0;
   a.status = dev->status_ptr;
-  // The grid depends on n alone, so that block b means the same slice on every rank.
-  const long long vecs = n / 8;
+  // Kernel and grid depend on n and world alone, so that every rank makes the same
+  // choice and block b means the same slice everywhere. From 256 KB on and with four
+  // or more ranks, the two-shot form (each rank reduces one slice and hands it round)
+  // moves world/2 times less data over NVLink than pushing every partial to every
+  // peer; with two ranks it moves the same and only adds a second flag exchange.
+  const bool big = g_two_shot_bytes > 0 ? n * 2 >= g_two_shot_bytes
+                                        : (g_two_shot_bytes == 0 && world >= 4 && n * 2 >= PEER_TWO_SHOT_MIN_BYTES);
+  const bool two_shot = big && (n % (8ll * world)) == 0;
+  const long long vecs = two_shot ? n / 8 / world : n / 8;
   long long blocks = (vecs + PEER_THREADS - 1) / PEER_THREADS;
   if (blocks > PEER_MAX_BLOCKS) blocks = PEER_MAX_BLOCKS;
   cudaLaunchConfig_t cfg;
@@ -946,9 +962,13 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t e = dtype == GMLP_BF16
-                      ? cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__nv_bfloat16>, a)
-                      : cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__half>, a);
+  cudaError_t e;
+  if (two_shot)
+    e = dtype == GMLP_BF16 ? cudaLaunchKernelEx(&cfg, peer_allreduce_twoshot_kernel<__nv_bfloat16>, a)
+                           : cudaLaunchKernelEx(&cfg, peer_allreduce_twoshot_kernel<__half>, a);
+  else
+    e = dtype == GMLP_BF16 ? cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__nv_bfloat16>, a)
+                           : cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<__half>, a);
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
