@@ -14,6 +14,7 @@ pytestmark = pytest.mark.gpu
     (512, 1024, False),     # fewer work units than SMs in the down projection
     (1024, 3584, True),     # the 8-way tensor-parallel shard width of a 28672 intermediate
     (2048, 7168, False),    # many split tiles in both kernels
+    (4096, 128, True),      # one gate/up tile split over 64 CTAs: the fix-up sums 64 partial tiles
 ])
 def test_decode_matches_oracle(pkg, cuda_dev, M, K, N, bias):
     case = orc.make_case(M, K, N, bias, torch.bfloat16, seed=M + K, w_std=0.5 * K ** -0.5)
@@ -35,8 +36,9 @@ def test_decode_equals_gemm_path_and_is_repeatable(pkg, cuda_dev):
     scratch = K_.decode_scratch(48, 1024, 4096, torch.bfloat16, cuda_dev)
     ys = [K_.decode_fwd(*t, scratch=scratch) for _ in range(5)]
     assert all(torch.equal(ys[0], y) for y in ys[1:])
-    # counter area: one int per 128-row weight tile of each kernel, each block padded to 256 bytes
-    n_counters = (256 + 256) // 4
+    # counter area: two ints per 128-row weight tile of each kernel (partials counted, contributors
+    # done), each of the four blocks padded to 256 bytes
+    n_counters = 4 * 256 // 4
     assert int(scratch[:n_counters].abs().sum()) == 0, "counters must be left at zero"
     orc.assert_parity(ys[0].cpu(), y_gemm.float().cpu(), "decode vs gemm", max_abs=2e-2, mean_rel=1e-2)
 
@@ -93,3 +95,17 @@ def test_decode_replays_from_a_cuda_graph(pkg, cuda_dev):
         torch.cuda.synchronize()
         assert torch.equal(y_static, K_.decode_fwd(t[0] * scale, *t[1:], scratch=scratch))
     assert torch.equal(K_.decode_fwd(*t, scratch=scratch), want)
+
+
+def test_decode_writes_into_given_buffer(pkg, cuda_dev):
+    K_ = pkg.ops.kernels
+    g = torch.Generator(device="cpu").manual_seed(9)
+    M, K, N = 8, 256, 512
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16).to(cuda_dev)
+    wg, wu = ((torch.randn((N, K), generator=g) * 0.05).to(torch.bfloat16).to(cuda_dev) for _ in range(2))
+    wd = (torch.randn((K, N), generator=g) * 0.05).to(torch.bfloat16).to(cuda_dev)
+    want = K_.decode_fwd(x, wg, None, wu, None, wd, None)
+    buf = torch.zeros((2 * M, K), dtype=torch.bfloat16, device=cuda_dev)
+    got = K_.decode_fwd(x, wg, None, wu, None, wd, None, out=buf[M:])
+    assert got.data_ptr() == buf[M:].data_ptr() and torch.equal(got, want)
+    assert buf[:M].abs().max().item() == 0

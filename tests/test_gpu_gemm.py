@@ -58,3 +58,39 @@ def test_gemm_is_deterministic(pkg, cuda_dev):
     c1 = pkg.ops.kernels.gemm(a, b, b_mn=True)
     c2 = pkg.ops.kernels.gemm(a, b, b_mn=True)
     assert torch.equal(c1, c2)
+
+
+def test_output_slices_and_sm_limit(pkg, cuda_dev):
+    """The down projection and dx written chunk by chunk into slices of one buffer, on a reduced
+    number of SMs (what the chunked tensor-parallel path does), give the bits of the one-shot call."""
+    K_ = pkg.ops.kernels
+    g = torch.Generator(device="cpu").manual_seed(5)
+    M, K, N = 640, 256, 384
+    h = (torch.randn((M, N), generator=g) * 0.5).to(torch.bfloat16).to(cuda_dev)
+    wd = (torch.randn((K, N), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    bd = (torch.randn((K,), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    res = (torch.randn((M, K), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    whole = K_.down_fwd(h, wd, bd, res)
+    out = torch.empty_like(whole)
+    assert pkg._lib.set_sm_limit(100) == 0
+    try:
+        for r0 in range(0, M, 256):
+            r1 = min(M, r0 + 256)
+            assert K_.down_fwd(h[r0:r1], wd, bd, res[r0:r1], out=out[r0:r1]).data_ptr() == out[r0:r1].data_ptr()
+    finally:
+        assert pkg._lib.set_sm_limit(0) == 100
+    assert torch.equal(out, whole)
+
+    dg = (torch.randn((M, N), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    du = (torch.randn((M, N), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    wg, wu = ((torch.randn((N, K), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev) for _ in range(2))
+    whole = K_.bwd_dx(dg, du, wg, wu)
+    out = torch.empty_like(whole)
+    for r0 in range(0, M, 256):
+        r1 = min(M, r0 + 256)
+        K_.bwd_dx(dg[r0:r1], du[r0:r1], wg, wu, out=out[r0:r1])
+    assert torch.equal(out, whole)
+    with pytest.raises(ValueError):
+        K_.bwd_dx(dg, du, wg, wu, out=out[:128])          # wrong shape
+    with pytest.raises(ValueError):
+        K_.down_fwd(h, wd, bd, out=torch.empty((M, K), dtype=torch.float16, device=cuda_dev))

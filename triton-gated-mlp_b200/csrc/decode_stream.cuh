@@ -37,7 +37,8 @@ struct DecodeArgs {
   const void* residual;  // optional [M, rows] added to the output (down projection only)
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
-  int* counters;      // [row tiles], zero on entry and on exit
+  int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry and on exit
+  int* done;          // [row tiles] contributors that have finished their share of the sum; zero likewise
   int act;            // gate activation (ACT_*), DUAL only
   int dependent;      // 1: launched with programmatic stream serialization behind the kernel
                       //    that produces the activations (and last used slots / counters)
@@ -53,17 +54,37 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 constexpr int DECODE_THREADS = 192;
 
+// Weight sub-tiles (128 rows each) per work unit; they share the unit's activation
+// tile. One is what ships. Two (gate/up) and four (down projection) sub-tiles at
+// MPAD = 64 were measured on the K=8192, N=28672 problem: they cut the activation
+// bytes an SM takes in per weight byte from 8/32 and 8/16 to 8/64, but at 72 KB a
+// stage only three stages fit, every row tile then has two to nine contributors with
+// four times the partial-tile volume, and the forward took 264 us against 247 us.
+template <int MPAD, bool DUAL>
+__host__ __device__ constexpr int decode_subtiles() {
+  return 1;
+}
+template <int MPAD, bool DUAL>
+__host__ __device__ constexpr int decode_stage_bytes() {
+  return (DUAL ? 2 : 1) * decode_subtiles<MPAD, DUAL>() * 16384 + MPAD * 128;
+}
 // As many stages as fit in shared memory: bytes in flight per SM are what hides the
 // DRAM latency (with 8 stages of 16 KB the down-projection kernel streamed at 5.6 TB/s
 // where the gate/up kernel, with 160 KB in flight, reached 6.4 TB/s).
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_stages() {
-  return DUAL ? (MPAD == 64 ? 5 : 6) : (MPAD == 16 ? 12 : (MPAD == 32 ? 11 : 9));
+  constexpr int fit = (232448 - 1024 - 512) / decode_stage_bytes<MPAD, DUAL>();
+  return fit > 12 ? 12 : fit;
 }
 template <int MPAD, bool DUAL>
 constexpr size_t decode_smem_bytes() {
-  return static_cast<size_t>(decode_stages<MPAD, DUAL>()) * ((DUAL ? 2 : 1) * 16384 + MPAD * 128) +
-         1024;
+  return static_cast<size_t>(decode_stages<MPAD, DUAL>()) * decode_stage_bytes<MPAD, DUAL>() + 1024;
+}
+// Rows of one TMA box of weights: all sub-tiles of a matrix in one box when they fit
+// the 256-row limit of a box, else in two.
+template <int MPAD, bool DUAL>
+__host__ __device__ constexpr int decode_box_rows() {
+  return decode_subtiles<MPAD, DUAL>() >= 2 ? 256 : 128;
 }
 
 __device__ __forceinline__ long long unit_start(long long c, long long total, long long g) {
@@ -77,19 +98,24 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
                      const __grid_constant__ CUtensorMap tmAct, const DecodeArgs args) {
   static_assert(MPAD == 16 || MPAD == 32 || MPAD == 64, "token padding");
   constexpr int NACC = DUAL ? 2 : 1;
+  constexpr int SUB = decode_subtiles<MPAD, DUAL>();  // weight sub-tiles per unit
+  constexpr int TILE_ROWS = 128 * SUB;                // weight rows per unit ("row tile")
+  constexpr int BOX_ROWS = decode_box_rows<MPAD, DUAL>();
   constexpr int STAGES = decode_stages<MPAD, DUAL>();
-  constexpr uint32_t W_BYTES = 128 * 128;  // one [128 x 64] 16-bit weight tile
+  constexpr uint32_t W_BYTES = 128 * 128;  // one [128 x 64] 16-bit weight sub-tile
   constexpr uint32_t ACT_BYTES = MPAD * 128;
-  constexpr uint32_t STAGE_BYTES = NACC * W_BYTES + ACT_BYTES;
-  constexpr uint32_t ACC_COLS = NACC * MPAD;  // TMEM columns per accumulator buffer
+  constexpr uint32_t ACT_OFF = NACC * SUB * W_BYTES;  // stage: [W0 sub-tiles][W1 sub-tiles][activations]
+  constexpr uint32_t STAGE_BYTES = ACT_OFF + ACT_BYTES;
+  static_assert(STAGE_BYTES == decode_stage_bytes<MPAD, DUAL>(), "stage layout");
+  constexpr uint32_t ACC_COLS = NACC * SUB * MPAD;  // TMEM columns per accumulator buffer
   constexpr uint32_t TMEM_COLS = (2 * ACC_COLS <= 32) ? 32 : (2 * ACC_COLS <= 64) ? 64
-                                 : (2 * ACC_COLS <= 128) ? 128 : 256;
+                                 : (2 * ACC_COLS <= 128) ? 128 : (2 * ACC_COLS <= 256) ? 256 : 512;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
-  __shared__ int last_flag;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -100,7 +126,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long row_tiles = (args.rows + 127) / 128;
+  const long long row_tiles = (args.rows + TILE_ROWS - 1) / TILE_ROWS;
   const long long total = row_tiles * args.kbt;
   const long long u_begin = unit_start(blockIdx.x, total, gridDim.x);
   const long long u_end = unit_start(blockIdx.x + 1, total, gridDim.x);
@@ -147,13 +173,18 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         const uint32_t sw = smem_base + st * STAGE_BYTES;
         const uint32_t fb = full_bar(st);
         mbar_expect_tx(fb, STAGE_BYTES);
-        tma_load_2d_hint(sw, &tmW0, fb, kb * BK, tile * 128, pol_w);
-        if (DUAL) tma_load_2d_hint(sw + W_BYTES, &tmW1, fb, kb * BK, tile * 128, pol_w);
+        // Rows past the end of the matrix (a last tile that is not full) arrive as zeros.
+#pragma unroll
+        for (int b = 0; b < TILE_ROWS / BOX_ROWS; ++b) {
+          tma_load_2d_hint(sw + b * BOX_ROWS * 128, &tmW0, fb, kb * BK, tile * TILE_ROWS + b * BOX_ROWS, pol_w);
+          if (DUAL)
+            tma_load_2d_hint(sw + SUB * W_BYTES + b * BOX_ROWS * 128, &tmW1, fb, kb * BK,
+                             tile * TILE_ROWS + b * BOX_ROWS, pol_w);
+        }
       };
       auto load_act = [&](long long u, int st) {
         const int kb = static_cast<int>(u % args.kbt);
-        tma_load_2d_hint(smem_base + st * STAGE_BYTES + NACC * W_BYTES, &tmAct, full_bar(st), kb * BK, 0,
-                         pol_a);
+        tma_load_2d_hint(smem_base + st * STAGE_BYTES + ACT_OFF, &tmAct, full_bar(st), kb * BK, 0, pol_a);
       };
       long long u = u_begin;
       if (args.dependent) {
@@ -213,17 +244,20 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
           }
           tc_fence_after_sync();
           const uint32_t sw = smem_base + stage * STAGE_BYTES;
-          const uint64_t w0desc = make_smem_desc(sw, 16, 1024);
-          const uint64_t w1desc = make_smem_desc(sw + W_BYTES, 16, 1024);
-          const uint64_t xdesc = make_smem_desc(sw + NACC * W_BYTES, 16, 1024);
+          const uint64_t xdesc = make_smem_desc(sw + ACT_OFF, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t accum = (first && k == 0) ? 0u : 1u;
-            umma_f16(d_tmem, w0desc + static_cast<uint64_t>(2 * k),
-                     xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
-            if (DUAL)
-              umma_f16(d_tmem + MPAD, w1desc + static_cast<uint64_t>(2 * k),
+          for (int t = 0; t < SUB; ++t) {
+            const uint64_t w0desc = make_smem_desc(sw + t * W_BYTES, 16, 1024);
+            const uint64_t w1desc = make_smem_desc(sw + (SUB + t) * W_BYTES, 16, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint32_t accum = (first && k == 0) ? 0u : 1u;
+              umma_f16(d_tmem + (t * NACC) * MPAD, w0desc + static_cast<uint64_t>(2 * k),
                        xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+              if (DUAL)
+                umma_f16(d_tmem + (t * NACC + 1) * MPAD, w1desc + static_cast<uint64_t>(2 * k),
+                         xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+            }
           }
           first = false;
           umma_commit(empty_bar(stage));
@@ -250,11 +284,14 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
     const T* const residual = static_cast<const T*>(args.residual);
     const T* const bias0 = static_cast<const T*>(args.bias0);
     const T* const bias1 = static_cast<const T*>(args.bias1);
-    constexpr long long SLOT_FLOATS = static_cast<long long>(NACC) * 128 * MPAD;
+    constexpr long long SUB_FLOATS = static_cast<long long>(NACC) * 128 * MPAD;  // one sub-tile's partial
+    constexpr long long SLOT_FLOATS = SUB * SUB_FLOATS;
     if (args.dependent) pdl_wait();  // slots, counters and outputs may still be in use by the preceding grid
     int seg = 0;
     bool ok = true;
     long long u = u_begin;
+    long long pending[2];  // row tiles this CTA holds a partial of: at most its first and its last
+    int npending = 0;
     while (u < u_end) {
       const long long tile = u / args.kbt;
       const long long tile_begin = tile * args.kbt;
@@ -275,28 +312,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       if (*abortp != 0) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * ACC_COLS + lane_addr;
-      float v[NACC][MPAD];
-#pragma unroll
-      for (int a = 0; a < NACC; ++a) {
-#pragma unroll
-        for (int c = 0; c < MPAD / 16; ++c) {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + a * MPAD + c * 16, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[a][c * 16 + i] = __uint_as_float(r[i]);
-        }
-      }
-      // TMEM has been read into registers: the MMA issuer may reuse the buffer.
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
 
-      // One output chunk: columns (tokens) [m0, m0 + C) of this thread's weight row.
-      const long long wrow = tile * 128 + r_in_tile;
-      const float b0 = (bias0 && wrow < args.rows) ? static_cast<float>(bias0[wrow]) : 0.f;
-      const float b1 = (DUAL && bias1 && wrow < args.rows) ? static_cast<float>(bias1[wrow]) : 0.f;
-      auto emit = [&](int m0, const float* first, const float* second, int count) {
+      // One output chunk: tokens [m0, m0 + count) of weight row `wrow`.
+      auto emit = [&](long long wrow, float b0, float b1, int m0, const float* first, const float* second,
+                      int count) {
         if (wrow >= args.rows) return;
 #pragma unroll
         for (int i = 0; i < count; ++i) {
@@ -314,86 +333,170 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
           }
         }
       };
+      auto row_bias = [&](const T* bias, long long wrow) {
+        return (bias && wrow < args.rows) ? static_cast<float>(bias[wrow]) : 0.f;
+      };
+      // Slot layout: float4 (sub-tile t, accumulator a, i, row) at index
+      // ((t * NACC + a) * MPAD/4 + i) * 128 + row, so that the 32 lanes of a warp (32
+      // consecutive rows) touch 512 contiguous bytes per access.
+      const int which = (u == u_begin) ? 0 : 1;
+      float4* const slot4 = reinterpret_cast<float4*>(args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS);
 
-      if (complete) {
-        emit(0, v[0], v[NACC - 1], MPAD);
-      } else {
-        // Store this CTA's partial tile to its own slot, then count it. Slot layout:
-        // float4 (a, i, row) at index (a * MPAD/4 + i) * 128 + row, so that the 32 lanes
-        // of a warp (32 consecutive rows) touch 512 contiguous bytes per access.
-        const int which = (u == u_begin) ? 0 : 1;
-        float4* slot4 = reinterpret_cast<float4*>(args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS);
+#pragma unroll 1
+      for (int t = 0; t < SUB; ++t) {
+        float v[NACC][MPAD];
 #pragma unroll
-        for (int a = 0; a < NACC; ++a)
+        for (int a = 0; a < NACC; ++a) {
 #pragma unroll
-          for (int i = 0; i < MPAD / 4; ++i)
-            slot4[(a * (MPAD / 4) + i) * 128 + r_in_tile] =
-                make_float4(v[a][4 * i], v[a][4 * i + 1], v[a][4 * i + 2], v[a][4 * i + 3]);
+          for (int c = 0; c < MPAD / 16; ++c) {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + (t * NACC + a) * MPAD + c * 16, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[a][c * 16 + i] = __uint_as_float(r[i]);
+          }
+        }
+        if (complete) {
+          const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
+          emit(wrow, row_bias(bias0, wrow), DUAL ? row_bias(bias1, wrow) : 0.f, 0, v[0], v[NACC - 1], MPAD);
+        } else {
+          // this CTA's partial sub-tile goes to its own slot
+#pragma unroll
+          for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int i = 0; i < MPAD / 4; ++i)
+              slot4[((t * NACC + a) * (MPAD / 4) + i) * 128 + r_in_tile] =
+                  make_float4(v[a][4 * i], v[a][4 * i + 1], v[a][4 * i + 2], v[a][4 * i + 3]);
+        }
+      }
+      // TMEM has been read into registers: the MMA issuer may reuse the buffer.
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+
+      if (!complete) {
+        // Publish this CTA's share of the row tile and move on; the sum over the
+        // contributors is taken up after the last segment (below).
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-        if (ep_tid == 0) {
-          const int nkb = static_cast<int>(seg_end - u);
-          const int old = atomicAdd(args.counters + tile, nkb);
-          last_flag = (old + nkb == args.kbt) ? 1 : 0;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (last_flag != 0) {
-          __threadfence();
-          // Sum every contributor's slot (this CTA's own included) in CTA order, which
-          // makes the result independent of arrival order. The accumulator registers are
-          // dead by now, so the sum runs chunk by chunk with FIX_BATCH contributors'
-          // loads in flight at once (the tail of a short kernel is this loop's latency).
-          const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
-          const long long c_last = (tile_end * gridDim.x - 1) / total;
-          constexpr int CHUNK4 = NACC == 2 ? 2 : 4;  // float4 columns per chunk and accumulator
-          constexpr int FIX_BATCH = 8;
-#pragma unroll 1
-          for (int ch = 0; ch < MPAD / (4 * CHUNK4); ++ch) {
-            float sum[NACC][4 * CHUNK4];
-#pragma unroll
-            for (int a = 0; a < NACC; ++a)
-#pragma unroll
-              for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
-#pragma unroll 1
-            for (long long cb = c_first; cb <= c_last; cb += FIX_BATCH) {
-              float4 q[FIX_BATCH][NACC][CHUNK4];
-#pragma unroll
-              for (int jc = 0; jc < FIX_BATCH; ++jc) {
-                const long long c = cb + jc;
-                if (c <= c_last) {
-                  const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
-                  const float4* s4 = reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
-#pragma unroll
-                  for (int a = 0; a < NACC; ++a)
-#pragma unroll
-                    for (int i = 0; i < CHUNK4; ++i)
-                      q[jc][a][i] = __ldcg(s4 + (a * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
-                } else {
-#pragma unroll
-                  for (int a = 0; a < NACC; ++a)
-#pragma unroll
-                    for (int i = 0; i < CHUNK4; ++i) q[jc][a][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-              }
-#pragma unroll
-              for (int jc = 0; jc < FIX_BATCH; ++jc)
-#pragma unroll
-                for (int a = 0; a < NACC; ++a)
-#pragma unroll
-                  for (int i = 0; i < CHUNK4; ++i) {
-                    sum[a][4 * i] += q[jc][a][i].x;
-                    sum[a][4 * i + 1] += q[jc][a][i].y;
-                    sum[a][4 * i + 2] += q[jc][a][i].z;
-                    sum[a][4 * i + 3] += q[jc][a][i].w;
-                  }
-            }
-            emit(ch * 4 * CHUNK4, sum[0], sum[NACC - 1], 4 * CHUNK4);
-          }
-          if (ep_tid == 0) args.counters[tile] = 0;  // leave the scratch ready for the next call
-        }
+        if (ep_tid == 0) atomicAdd(args.counters + tile, static_cast<int>(seg_end - u));
+        pending[npending++] = tile;
       }
       u = seg_end;
       ++seg;
+    }
+
+    // ---- split row tiles: every contributor sums an equal share of the tile ----
+    // All of this CTA's partials are published by now, so nobody waits for a CTA
+    // that is itself waiting. Contributor j of c (in CTA order) takes chunks
+    // [j * P / c, (j + 1) * P / c) of the tile's P chunks (a chunk = 128 rows x 8 or
+    // 16 tokens of one sub-tile), waits until every contributor's partial has been
+    // counted (they all finish at about the same time: the unit ranges are equal),
+    // adds the slots in CTA order, which makes the result independent of arrival
+    // order, and applies the epilogue. The last contributor to finish clears the
+    // tile's counters for the next call.
+    constexpr int CHUNK4 = NACC == 2 ? 2 : 4;          // float4 columns per chunk and accumulator
+    constexpr int CH_PER_SUB = MPAD / (4 * CHUNK4);
+    constexpr int CHUNKS = SUB * CH_PER_SUB;
+    constexpr int FIX_BATCH = 8;                       // contributors whose loads are in flight together
+    for (int pi = 0; pi < npending && *abortp == 0; ++pi) {
+      const long long tile = pending[pi];
+      const long long tile_begin = tile * args.kbt;
+      const long long tile_end = tile_begin + args.kbt;
+      const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
+      const long long c_last = (tile_end * gridDim.x - 1) / total;
+      const int nc = static_cast<int>(c_last - c_first + 1);
+      const int j = static_cast<int>(blockIdx.x - c_first);
+      if (ep_tid == 0) {
+        const volatile int* cnt = args.counters + tile;
+        const long long t0 = clock64();
+        while (*cnt != args.kbt) {
+          if (*abortp != 0 || clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            abort_flag = 1;
+            atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+            break;
+          }
+          __nanosleep(64);
+        }
+        __threadfence();
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abortp != 0) break;
+      auto row_bias = [&](const T* bias, long long wrow) {
+        return (bias && wrow < args.rows) ? static_cast<float>(bias[wrow]) : 0.f;
+      };
+      const int p_begin = j * CHUNKS / nc, p_end = (j + 1) * CHUNKS / nc;
+#pragma unroll 1
+      for (int p = p_begin; p < p_end; ++p) {
+        const int t = p / CH_PER_SUB, ch = p - t * CH_PER_SUB;
+        const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
+        float sum[NACC][4 * CHUNK4];
+#pragma unroll
+        for (int a = 0; a < NACC; ++a)
+#pragma unroll
+          for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
+#pragma unroll 1
+        for (long long cb = c_first; cb <= c_last; cb += FIX_BATCH) {
+          float4 q[FIX_BATCH][NACC][CHUNK4];
+#pragma unroll
+          for (int jc = 0; jc < FIX_BATCH; ++jc) {
+            const long long c = cb + jc;
+            if (c <= c_last) {
+              const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
+              const float4* s4 = reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
+#pragma unroll
+              for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                for (int i = 0; i < CHUNK4; ++i)
+                  q[jc][a][i] = __ldcg(s4 + ((t * NACC + a) * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
+            } else {
+#pragma unroll
+              for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                for (int i = 0; i < CHUNK4; ++i) q[jc][a][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
+#pragma unroll
+          for (int jc = 0; jc < FIX_BATCH; ++jc)
+#pragma unroll
+            for (int a = 0; a < NACC; ++a)
+#pragma unroll
+              for (int i = 0; i < CHUNK4; ++i) {
+                sum[a][4 * i] += q[jc][a][i].x;
+                sum[a][4 * i + 1] += q[jc][a][i].y;
+                sum[a][4 * i + 2] += q[jc][a][i].z;
+                sum[a][4 * i + 3] += q[jc][a][i].w;
+              }
+        }
+        if (wrow < args.rows) {
+          const float b0 = row_bias(bias0, wrow);
+          const float b1 = DUAL ? row_bias(bias1, wrow) : 0.f;
+#pragma unroll
+          for (int i = 0; i < 4 * CHUNK4; ++i) {
+            const int m = ch * 4 * CHUNK4 + i;
+            if (m < args.M) {
+              float o;
+              if (DUAL) {
+                o = act_value(args.act, sum[0][i] + b0) * (sum[NACC - 1][i] + b1);
+              } else {
+                o = sum[0][i] + b0;
+              }
+              const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
+              if (!DUAL && residual) o += static_cast<float>(residual[oi]);
+              out[oi] = static_cast<T>(o);
+            }
+          }
+        }
+      }
+      // Everybody has read what it needs of this tile's slots: count this CTA as done.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ep_tid == 0) {
+        __threadfence();
+        if (atomicAdd(args.done + tile, 1) == nc - 1) {
+          args.counters[tile] = 0;  // leave the scratch ready for the next call
+          args.done[tile] = 0;
+        }
+      }
     }
   }
 
