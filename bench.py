@@ -37,7 +37,17 @@ WORKLOADS = {
     "train-fwd-bwd-bf16": dict(M=16384, K=2048, N=8192, bias=True, p=0.1, mode="fwd+bwd"),
     "prefill-fwd-bf16": dict(M=65536, K=8192, N=28672, bias=False, p=0.0, mode="fwd"),
     "prefill-fwd-bwd-bf16": dict(M=65536, K=8192, N=28672, bias=False, p=0.0, mode="fwd+bwd"),
+    # skinny-M inference through the weight-streaming kernels: HBM-bound, metric in GB/s
+    "decode-m1-bf16": dict(M=1, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
+    "decode-m8-bf16": dict(M=8, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
+    "decode-m32-bf16": dict(M=32, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
+    "decode-m64-bf16": dict(M=64, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
 }
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes (read + write) of one decode forward at M=1 (gate/up kernel 946.6 MB + down projection
+# 474.2 MB), from the ncu capture summarised in profiles/decode_stream_kernels_k8192_n28672.md.
+DECODE_M1_DRAM_TRAFFIC_BYTES = 1.4208e9
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # DRAM bytes (read + write) of one launch of the gate/up kernel at the default workload,
@@ -47,7 +57,22 @@ K1_DRAM_TRAFFIC_BYTES = 1.265e9
 
 def flops_per_step(w) -> float:
     mkn = w["M"] * w["K"] * w["N"]
-    return (6.0 if w["mode"] == "fwd" else 18.0) * mkn
+    return (6.0 if w["mode"] in ("fwd", "decode") else 18.0) * mkn
+
+
+def decode_bytes_per_step(w) -> float:
+    """Algorithmic bytes of one decode forward: the three bf16 weight matrices once, x in, y out."""
+    return 2.0 * (3.0 * w["K"] * w["N"] + 2.0 * w["M"] * w["K"])
+
+
+def measured_hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured copy bandwidth (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (MEASURED_PEAKS.json absent)"
 
 
 def measured_peaks():
@@ -136,7 +161,7 @@ def cpu_baseline(w, budget_s: float = 12.0):
     fl = flops_per_step(w) * ms / w["M"]
 
     def run():
-        if w["mode"] == "fwd":
+        if w["mode"] in ("fwd", "decode"):
             orc.forward(x, wg, bg, wu, bu, wd, bd)
         else:
             orc.forward(x, wg, bg, wu, bu, wd, bd)
@@ -150,6 +175,14 @@ def cpu_baseline(w, budget_s: float = 12.0):
         run()
         times.append(time.perf_counter() - t0)
     t = statistics.median(times)
+    if w["mode"] == "decode":
+        # the whole batch fits the sample; fp32 weights, so the CPU streams twice the bf16 bytes the metric counts
+        return {
+            "value": decode_bytes_per_step(w) / t / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"all {ms} token rows, full K and N, fp32 torch CPU, median of {len(times)} runs "
+                      f"({t * 1e3:.0f} ms each); bytes counted as for the bf16 path",
+        }, t, ms
     return {
         "value": fl / t / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
         "sample": f"{ms} of {w['M']} token rows, full K and N, fp32 torch CPU, median of {len(times)} runs "
@@ -162,9 +195,11 @@ def run_reference(args, w, name):
     if rank != 0:
         return
     base, t, ms = cpu_baseline(w, budget_s=max(5.0, min(60.0, 0.5 * (args.steps + args.warmup))))
+    decode = w["mode"] == "decode"
     line = {
-        "impl": "reference", "metric": f"gated_mlp_{w['mode'].replace('+', '_')}_tflops", "value": base["value"],
-        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "impl": "reference",
+        "metric": "gated_mlp_decode_hbm_gbs" if decode else f"gated_mlp_{w['mode'].replace('+', '_')}_tflops",
+        "value": base["value"], "unit": base["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": t * 1e3 * w["M"] / ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "M": w["M"], "K": w["K"], "N": w["N"], "bias": w["bias"],
@@ -172,9 +207,130 @@ def run_reference(args, w, name):
                    "note": "CPU restatement of the reference's torch-eager path (the reference is Python and "
                            "is not present on this machine); ms_per_step extrapolated linearly from the row sample"},
         "cpu_baseline": base,
-        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": base["value"], "unit": base["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- decode ----
+def run_decode(args, w, name):
+    """M <= 64 tokens through the module's decode path; the metric is algorithmic GB/s of the weight stream.
+
+    Two weight sets alternate between steps, so nothing a step reads was left in L2 by the step before
+    (one set is 1.4 GB against 126 MB of L2 anyway). With N > 1 every rank decodes its own batch on
+    replicated weights (replicas, no collective)."""
+    import __graft_entry__ as entry
+
+    pkg = entry.load_package()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if dist_on:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    M, K, N = w["M"], w["K"], w["N"]
+    dt = torch.bfloat16
+    wgen = torch.Generator(device=dev).manual_seed(7)
+    sets = []
+    for _ in range(2):
+        mlp = pkg.FusedGatedMLP(K, N, bias=w["bias"]).to(dev).to(dt).eval()
+        with torch.no_grad():
+            for p_ in mlp.parameters():
+                p_.copy_((torch.randn(p_.shape, device=dev, generator=wgen) * 0.02).to(dt))
+        sets.append(mlp)
+    x = torch.randn((M, K), device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(1234 + rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist_on:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for i in range(max(args.warmup, 3) * 2):
+            sets[i & 1](x)
+        assert sets[0]._decode_scratch is not None, "the decode path was not taken"
+        barrier()
+        with ClockSampler(local) as clocks:
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(args.steps):
+                sets[i & 1](x)
+            t1.record()
+            barrier()
+    elapsed_ms = t0.elapsed_time(t1)
+
+    # end to end: x from pinned host memory, y back to pinned host memory, every step
+    x_host = torch.empty((M, K), dtype=dt).pin_memory()
+    x_host.copy_(x.cpu())
+    y_host = torch.empty((M, K), dtype=dt).pin_memory()
+    flip = [0]
+
+    def api_step(x_dev):
+        flip[0] ^= 1
+        with torch.no_grad():
+            return sets[flip[0]](x_dev)
+
+    pipe = pkg.host_pipeline.HostPipeline(api_step, dev, depth=3)
+    e2e_steps = max(3, min(args.steps, 200))
+    for _ in range(4):
+        pipe.submit(y_host, x_host)
+    pipe.drain()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record(pipe.s_in)
+    for _ in range(e2e_steps):
+        pipe.submit(y_host, x_host)
+    s1.record(pipe.s_out)
+    pipe.drain()
+    barrier()
+    e2e_ms = s0.elapsed_time(s1)
+    status = pkg._lib.status_read(dev)
+    if dist_on:
+        t = torch.tensor([elapsed_ms, e2e_ms, float(status)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms, status = t[0].item(), t[1].item(), int(t[2].item())
+    assert status == 0, f"a kernel recorded a device-side timeout (code {status})"
+
+    if rank == 0:
+        nbytes = decode_bytes_per_step(w)
+        ms_step = elapsed_ms / args.steps
+        value = world * nbytes / (ms_step * 1e-3) / 1e9
+        peak, peak_src = measured_hbm_peak()
+        line = {
+            "metric": "gated_mlp_decode_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "M_per_gpu": M, "K": K, "N": N, "bias": w["bias"], "pass": "decode forward",
+                       "parallelism": f"independent replicas x{world}, no collective",
+                       "l2": "two weight sets alternate between steps; one set (1.4 GB) exceeds the 126 MB L2"},
+            "frac_of_nominal_hbm_peak": value / world / NOMINAL_HBM_GBS,
+            "frac_of_measured_hbm_peak": value / world / peak,
+            "e2e": {"value": world * nbytes / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks.summary(),
+            "roofline": {
+                "kernel": "decode_stream_kernel<MPAD, gate+up> then <MPAD, down>, chained by programmatic dependent "
+                          "launch (timed together: timing them apart would break the chain)",
+                "bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
+                "peak_source": peak_src, "frac_of_nominal": value / world / NOMINAL_HBM_GBS,
+                "traffic": DECODE_M1_DRAM_TRAFFIC_BYTES if M == 1 else None,
+                "ms_per_launch": ms_step, "algorithmic_bytes_per_launch": nbytes,
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base, _, _ = cpu_baseline(w)
+            line["cpu_baseline"] = base
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 # ------------------------------------------------------------------- GPU ----
@@ -409,6 +565,8 @@ def main():
         return run_sweep(args)
     if args.impl == "reference":
         run_reference(args, w, args.workload)
+    elif w["mode"] == "decode":
+        run_decode(args, w, args.workload)
     else:
         run_gpu(args, w, args.workload)
 

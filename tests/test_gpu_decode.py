@@ -15,6 +15,8 @@ pytestmark = pytest.mark.gpu
     (1024, 3584, True),     # the 8-way tensor-parallel shard width of a 28672 intermediate
     (2048, 7168, False),    # many split tiles in both kernels
     (4096, 128, True),      # one gate/up tile split over 64 CTAs: the fix-up sums 64 partial tiles
+    (256, 18944, False),    # 148 gate/up row tiles: one whole tile per CTA on a 148-SM part, nothing split
+    (256, 24576, True),     # 192 row tiles: every CTA owns a whole tile, the other 44 are split over all CTAs
 ])
 def test_decode_matches_oracle(pkg, cuda_dev, M, K, N, bias):
     case = orc.make_case(M, K, N, bias, torch.bfloat16, seed=M + K, w_std=0.5 * K ** -0.5)

@@ -398,7 +398,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
     constexpr int CHUNK4 = NACC == 2 ? 2 : 4;          // float4 columns per chunk and accumulator
     constexpr int CH_PER_SUB = MPAD / (4 * CHUNK4);
     constexpr int CHUNKS = SUB * CH_PER_SUB;
-    constexpr int FIX_BATCH = 8;                       // contributors whose loads are in flight together
+    constexpr int FIX_STAGE_CAP = 64;                  // 16-byte pieces a thread stages at a time (128 KB in all)
     for (int pi = 0; pi < npending && *abortp == 0; ++pi) {
       const long long tile = pending[pi];
       const long long tile_begin = tile * args.kbt;
@@ -426,66 +426,100 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         return (bias && wrow < args.rows) ? static_cast<float>(bias[wrow]) : 0.f;
       };
       const int p_begin = j * CHUNKS / nc, p_end = (j + 1) * CHUNKS / nc;
-#pragma unroll 1
-      for (int p = p_begin; p < p_end; ++p) {
-        const int t = p / CH_PER_SUB, ch = p - t * CH_PER_SUB;
-        const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
-        float sum[NACC][4 * CHUNK4];
+      // The loads of a share are independent, and their latency is the kernel's tail, so
+      // they are issued all at once: cp.async copies them into the operand ring, which is
+      // idle by now (every MMA of this CTA has completed), each thread into a column of
+      // its own, and the sums are then taken from shared memory in CTA order.
+      auto slot_of = [&](long long c) -> const float4* {
+        const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
+        return reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
+      };
+      auto stage_addr = [&](int k) { return smem_base + static_cast<uint32_t>(k * 128 + ep_tid) * 16u; };
+      auto issue_items = [&](int k, const float4* s4, int t, int ch) {  // ITEM4 copies for one (chunk, contributor)
 #pragma unroll
         for (int a = 0; a < NACC; ++a)
 #pragma unroll
-          for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
-#pragma unroll 1
-        for (long long cb = c_first; cb <= c_last; cb += FIX_BATCH) {
-          float4 q[FIX_BATCH][NACC][CHUNK4];
+          for (int i = 0; i < CHUNK4; ++i)
+            cp_async_16(stage_addr(k + a * CHUNK4 + i),
+                        s4 + ((t * NACC + a) * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
+      };
+      auto add_items = [&](int k, float (&sum)[NACC][4 * CHUNK4]) {
 #pragma unroll
-          for (int jc = 0; jc < FIX_BATCH; ++jc) {
-            const long long c = cb + jc;
-            if (c <= c_last) {
-              const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
-              const float4* s4 = reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
+        for (int a = 0; a < NACC; ++a)
 #pragma unroll
-              for (int a = 0; a < NACC; ++a)
-#pragma unroll
-                for (int i = 0; i < CHUNK4; ++i)
-                  q[jc][a][i] = __ldcg(s4 + ((t * NACC + a) * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
-            } else {
-#pragma unroll
-              for (int a = 0; a < NACC; ++a)
-#pragma unroll
-                for (int i = 0; i < CHUNK4; ++i) q[jc][a][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+          for (int i = 0; i < CHUNK4; ++i) {
+            const float4 q = ld_shared_f4(stage_addr(k + a * CHUNK4 + i));
+            sum[a][4 * i] += q.x;
+            sum[a][4 * i + 1] += q.y;
+            sum[a][4 * i + 2] += q.z;
+            sum[a][4 * i + 3] += q.w;
           }
+      };
+      auto emit_chunk = [&](int pch, const float (&sum)[NACC][4 * CHUNK4]) {
+        const int t = pch / CH_PER_SUB, ch = pch - t * CH_PER_SUB;
+        const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
+        if (wrow >= args.rows) return;
+        const float b0 = row_bias(bias0, wrow);
+        const float b1 = DUAL ? row_bias(bias1, wrow) : 0.f;
 #pragma unroll
-          for (int jc = 0; jc < FIX_BATCH; ++jc)
+        for (int i = 0; i < 4 * CHUNK4; ++i) {
+          const int m = ch * 4 * CHUNK4 + i;
+          if (m < args.M) {
+            float o;
+            if (DUAL) {
+              o = act_value(args.act, sum[0][i] + b0) * (sum[NACC - 1][i] + b1);
+            } else {
+              o = sum[0][i] + b0;
+            }
+            const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
+            if (!DUAL && residual) o += static_cast<float>(residual[oi]);
+            out[oi] = static_cast<T>(o);
+          }
+        }
+      };
+      constexpr int ITEM4 = NACC * CHUNK4;  // 16-byte pieces per (chunk, contributor) and thread
+      int pch = p_begin;
+      while (pch < p_end) {
+        if (nc * ITEM4 <= FIX_STAGE_CAP) {
+          // several chunks, all their contributors, in one round trip
+          int nch = FIX_STAGE_CAP / (nc * ITEM4);
+          if (nch > p_end - pch) nch = p_end - pch;
+          int k = 0;
+          for (int q = 0; q < nch; ++q) {
+            const int t = (pch + q) / CH_PER_SUB, ch = (pch + q) - t * CH_PER_SUB;
+            for (long long c = c_first; c <= c_last; ++c, k += ITEM4) issue_items(k, slot_of(c), t, ch);
+          }
+          cp_async_wait_all();
+          k = 0;
+          for (int q = 0; q < nch; ++q) {
+            float sum[NACC][4 * CHUNK4];
 #pragma unroll
             for (int a = 0; a < NACC; ++a)
 #pragma unroll
-              for (int i = 0; i < CHUNK4; ++i) {
-                sum[a][4 * i] += q[jc][a][i].x;
-                sum[a][4 * i + 1] += q[jc][a][i].y;
-                sum[a][4 * i + 2] += q[jc][a][i].z;
-                sum[a][4 * i + 3] += q[jc][a][i].w;
-              }
-        }
-        if (wrow < args.rows) {
-          const float b0 = row_bias(bias0, wrow);
-          const float b1 = DUAL ? row_bias(bias1, wrow) : 0.f;
-#pragma unroll
-          for (int i = 0; i < 4 * CHUNK4; ++i) {
-            const int m = ch * 4 * CHUNK4 + i;
-            if (m < args.M) {
-              float o;
-              if (DUAL) {
-                o = act_value(args.act, sum[0][i] + b0) * (sum[NACC - 1][i] + b1);
-              } else {
-                o = sum[0][i] + b0;
-              }
-              const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
-              if (!DUAL && residual) o += static_cast<float>(residual[oi]);
-              out[oi] = static_cast<T>(o);
-            }
+              for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
+            for (int ci = 0; ci < nc; ++ci, k += ITEM4) add_items(k, sum);
+            emit_chunk(pch + q, sum);
           }
+          pch += nch;
+        } else {
+          // one chunk, its many contributors in batches
+          const int t = pch / CH_PER_SUB, ch = pch - t * CH_PER_SUB;
+          float sum[NACC][4 * CHUNK4];
+#pragma unroll
+          for (int a = 0; a < NACC; ++a)
+#pragma unroll
+            for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
+          constexpr int CB = FIX_STAGE_CAP / ITEM4;
+          for (long long cb = c_first; cb <= c_last; cb += CB) {
+            const long long ce = cb + CB - 1 < c_last ? cb + CB - 1 : c_last;
+            int k = 0;
+            for (long long c = cb; c <= ce; ++c, k += ITEM4) issue_items(k, slot_of(c), t, ch);
+            cp_async_wait_all();
+            k = 0;
+            for (long long c = cb; c <= ce; ++c, k += ITEM4) add_items(k, sum);
+          }
+          emit_chunk(pch, sum);
+          pch += 1;
         }
       }
       // Everybody has read what it needs of this tile's slots: count this CTA as done.
