@@ -141,6 +141,9 @@ def main():
         assert all(torch.equal(e, every[0]) for e in every), "ranks disagree on the summed output"
         md._peer.close()
         comm.close()
+        with torch.no_grad():
+            y_back = md(cased.x.to(dev))      # a closed peer group: the module is back on the NCCL sum
+        assert torch.equal(y_back, y_nccl)
 
         # ---------------- token sharding: no collective, mask rows offset
         Mt = 256 * world

@@ -64,6 +64,7 @@ def _peer_host_logic(P, rank):
     comm.close()
     assert fake.closed == [0x10000000 * (other + 1)] and fake.freed == [0x7000 + rank]
     comm.close()                                              # idempotent
+    assert comm.closed and not comm.supports(part)            # callers fall back to NCCL after close()
     with pytest.raises(RuntimeError):
         comm.all_reduce(part)
 

@@ -220,9 +220,14 @@ class PeerAllReduce:
         dist.barrier(group=group)
         self.calls = 0
 
+    @property
+    def closed(self) -> bool:
+        return self.regions is None
+
     def supports(self, t: Tensor) -> bool:
         n = t.numel()
-        return t.dtype == self.dtype and t.is_contiguous() and 0 < n <= self.max_elems and n % 8 == 0
+        return (not self.closed and t.dtype == self.dtype and t.is_contiguous()
+                and 0 < n <= self.max_elems and n % 8 == 0)
 
     def all_reduce(self, partial: Tensor, out: Optional[Tensor] = None, dependent: bool = False) -> Tensor:
         """Sum of `partial` over the ranks, enqueued on the current stream; returns `out` (allocated if None,
@@ -231,7 +236,7 @@ class PeerAllReduce:
         `dependent=True` launches the reduction as a programmatic dependent of the
         preceding kernel on the stream, which must be the one that wrote `partial`.
         """
-        if self.regions is None:
+        if self.closed:
             raise RuntimeError("this PeerAllReduce has been closed")
         if not self.supports(partial):
             raise ValueError(
