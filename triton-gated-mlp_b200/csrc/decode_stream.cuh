@@ -10,12 +10,18 @@
 // reduction block) units in row-tile-major order. CTA c of G takes the
 // contiguous unit range [c*U/G, (c+1)*U/G): every CTA streams the same number of
 // weight bytes (to within one unit) whatever the tile count is. A row tile whose
-// reduction is split across CTAs is finished by whichever contributor arrives
-// last: each contributor stores its fp32 partial tile to its own scratch slot,
-// bumps the tile's counter, and the one that completes the count sums all slots in
-// CTA order (so the result does not depend on arrival order), applies the
-// epilogue, and resets the counter. There is no spin-wait anywhere in this
-// scheme.
+// reduction is split across CTAs is finished by its owner, the contributor that holds
+// the tile's first reduction blocks: every other contributor stores its fp32 partial
+// tile to its scratch slot and adds its block count to the tile's counter; the owner,
+// for which the tile is the last thing it works on, waits (bounded) until the others'
+// blocks are all counted, adds their partials to its own accumulators in CTA order (so
+// the result does not depend on arrival order), applies the epilogue and clears the
+// counter. With two contributors per tile, the usual case, the other part was
+// published a whole kernel earlier and the owner never actually waits. Only owners
+// wait, and only after they have published everything they owe, so no CTA waits for one
+// that is itself waiting; the grid is at most one CTA per SM, so a contributor that has
+// not started yet is only waiting for an SM that some other kernel still holds, and the
+// wait gives up (status word, no output for that tile) after WAIT_LIMIT_CYCLES.
 //
 //   DUAL = true   H^T[n, m]  = silu(Wg[n,:].x[m,:] + bg[n]) * (Wu[n,:].x[m,:] + bu[n])
 //                 two accumulators (gate, up) per tile, written as H[m, n]
@@ -38,7 +44,6 @@ struct DecodeArgs {
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
   int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry and on exit
-  int* done;          // [row tiles] contributors that have finished their share of the sum; zero likewise
   int act;            // gate activation (ACT_*), DUAL only
   int dependent;      // 1: launched with programmatic stream serialization behind the kernel
                       //    that produces the activations (and last used slots / counters)
@@ -53,21 +58,14 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 constexpr int DECODE_THREADS = 192;
-// One CTA per SM. What the tails of these kernels cost (the time from a CTA's last MMA
-// to its exit: publish partial tiles, wait for the other contributors, sum a share) was
-// measured by removing all of it: 211 us at every M for K=8192, N=28672 against 222 us
-// (M=8) and 245 us (M=64) with it. Tried against that gap and measured no better: two
-// CTAs per SM with half the ring each (all CTAs reach their tails together, so there is
-// no sibling stream to hide a tail behind); whole row tiles owned by CTAs with only the
-// remainder split and summed early (15 us slower); the gate/up kernel prefetching the
-// down projection's first weight boxes into L2 during its tail (no change).
-
-// Weight sub-tiles (128 rows each) per work unit; they share the unit's activation
-// tile. One is what ships. Two (gate/up) and four (down projection) sub-tiles at
-// MPAD = 64 were measured on the K=8192, N=28672 problem: they cut the activation
-// bytes an SM takes in per weight byte from 8/32 and 8/16 to 8/64, but at 72 KB a
-// stage only three stages fit, every row tile then has two to nine contributors with
-// four times the partial-tile volume, and the forward took 264 us against 247 us.
+// One CTA per SM. What the handling of split row tiles costs was measured with one-off
+// builds at K=8192, N=28672: with no split-tile work at all a forward takes 211 / 214 /
+// 219 us at M = 8 / 32 / 64, against 226 / 231 / 249 us when every contributor publishes
+// its part, waits for the others and sums a share of both its split tiles at the end of
+// the kernel. Tried against that gap and measured no better: two CTAs per SM with half
+// the ring each; whole row tiles owned by CTAs with only the remainder split and summed
+// early (15 us slower); the gate/up kernel prefetching the down projection's first
+// weight boxes into L2 during its tail (no change).
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_subtiles() {
   return 1;
@@ -298,8 +296,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
     int seg = 0;
     bool ok = true;
     long long u = u_begin;
-    long long pending[2];  // row tiles this CTA holds a partial of: at most its first and its last
-    int npending = 0;
     while (u < u_end) {
       const long long tile = u / args.kbt;
       const long long tile_begin = tile * args.kbt;
@@ -344,11 +340,38 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       auto row_bias = [&](const T* bias, long long wrow) {
         return (bias && wrow < args.rows) ? static_cast<float>(bias[wrow]) : 0.f;
       };
-      // Slot layout: float4 (sub-tile t, accumulator a, i, row) at index
-      // ((t * NACC + a) * MPAD/4 + i) * 128 + row, so that the 32 lanes of a warp (32
-      // consecutive rows) touch 512 contiguous bytes per access.
-      const int which = (u == u_begin) ? 0 : 1;
-      float4* const slot4 = reinterpret_cast<float4*>(args.slots + (2LL * blockIdx.x + which) * SLOT_FLOATS);
+      // A split row tile is finished by its OWNER, the contributor that holds the tile's
+      // first reduction blocks: for that CTA the tile is the last thing it works on, while
+      // for the contributor that holds the tile's last blocks it is the first, published
+      // a whole kernel earlier. So the owner keeps its own part in registers, finds the
+      // other parts (all of them, when a tile has two contributors) already counted,
+      // fetches them in one round trip and adds them in CTA order, which makes the result
+      // independent of arrival order. Everybody else stores its part, counts it and moves
+      // on (or exits): nobody but an owner ever waits, and an owner has published
+      // everything it owes before it does.
+      const bool owner = !complete && (u == tile_begin);
+      float4* const slot4 = reinterpret_cast<float4*>(args.slots + 2LL * blockIdx.x * SLOT_FLOATS);
+      const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
+      const long long c_last = (tile_end * gridDim.x - 1) / total;
+      if (owner) {
+        // the other contributors' reduction blocks must all be counted
+        if (ep_tid == 0) {
+          const int need = args.kbt - static_cast<int>(seg_end - u);
+          const volatile int* cnt = args.counters + tile;
+          const long long t0 = clock64();
+          while (*cnt != need) {
+            if (*abortp != 0 || clock64() - t0 > WAIT_LIMIT_CYCLES) {
+              abort_flag = 1;
+              atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+              break;
+            }
+            __nanosleep(64);
+          }
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abortp != 0) break;
+      }
 
 #pragma unroll 1
       for (int t = 0; t < SUB; ++t) {
@@ -364,11 +387,49 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
             for (int i = 0; i < 16; ++i) v[a][c * 16 + i] = __uint_as_float(r[i]);
           }
         }
-        if (complete) {
+        if (owner) {
+          // The other parts, as many contributors per round trip as the operand ring holds:
+          // cp.async copies them into the ring, which is idle (this is the CTA's last
+          // segment and its MMAs have completed), each thread into a column of its own.
+          constexpr int ITEM4 = NACC * (MPAD / 4);  // 16-byte pieces per contributor and thread
+          constexpr int RING_CAP = static_cast<int>(STAGES * STAGE_BYTES / (128 * 16));
+          constexpr int FIX_CONTRIB = RING_CAP / ITEM4;  // contributors fetched per round trip
+          static_assert(ITEM4 <= RING_CAP, "the ring must hold one contributor's part");
+          auto stage_addr = [&](int k) { return smem_base + static_cast<uint32_t>(k * 128 + ep_tid) * 16u; };
+          for (long long cb = c_first + 1; cb <= c_last; cb += FIX_CONTRIB) {
+            const long long ce = cb + FIX_CONTRIB - 1 < c_last ? cb + FIX_CONTRIB - 1 : c_last;
+            int k = 0;
+            for (long long c = cb; c <= ce; ++c) {
+              const float4* s4 = reinterpret_cast<const float4*>(args.slots + 2LL * c * SLOT_FLOATS);
+#pragma unroll
+              for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                for (int i = 0; i < MPAD / 4; ++i, ++k)
+                  cp_async_16(stage_addr(k), s4 + ((t * NACC + a) * (MPAD / 4) + i) * 128 + r_in_tile);
+            }
+            cp_async_wait_all();
+            k = 0;
+            for (long long c = cb; c <= ce; ++c) {
+#pragma unroll
+              for (int a = 0; a < NACC; ++a)
+#pragma unroll
+                for (int i = 0; i < MPAD / 4; ++i, ++k) {
+                  const float4 q = ld_shared_f4(stage_addr(k));
+                  v[a][4 * i] += q.x;
+                  v[a][4 * i + 1] += q.y;
+                  v[a][4 * i + 2] += q.z;
+                  v[a][4 * i + 3] += q.w;
+                }
+            }
+          }
+        }
+        if (complete || owner) {
           const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
           emit(wrow, row_bias(bias0, wrow), DUAL ? row_bias(bias1, wrow) : 0.f, 0, v[0], v[NACC - 1], MPAD);
         } else {
-          // this CTA's partial sub-tile goes to its own slot
+          // this CTA's part of the sub-tile goes to its slot. Slot layout: float4 (sub-tile t,
+          // accumulator a, i, row) at index ((t * NACC + a) * MPAD/4 + i) * 128 + row, so that
+          // the 32 lanes of a warp (32 consecutive rows) touch 512 contiguous bytes per access.
 #pragma unroll
           for (int a = 0; a < NACC; ++a)
 #pragma unroll
@@ -382,163 +443,16 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
 
-      if (!complete) {
-        // Publish this CTA's share of the row tile and move on; the sum over the
-        // contributors is taken up after the last segment (below).
+      if (owner) {
+        if (ep_tid == 0) args.counters[tile] = 0;  // leave the scratch ready for the next call
+      } else if (!complete) {
+        // count this CTA's reduction blocks once its part is visible
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         if (ep_tid == 0) atomicAdd(args.counters + tile, static_cast<int>(seg_end - u));
-        pending[npending++] = tile;
       }
       u = seg_end;
       ++seg;
-    }
-
-    // ---- split row tiles: every contributor sums an equal share of the tile ----
-    // All of this CTA's partials are published by now, so nobody waits for a CTA
-    // that is itself waiting. Contributor j of c (in CTA order) takes chunks
-    // [j * P / c, (j + 1) * P / c) of the tile's P chunks (a chunk = 128 rows x 8 or
-    // 16 tokens of one sub-tile), waits until every contributor's partial has been
-    // counted (they all finish at about the same time: the unit ranges are equal),
-    // adds the slots in CTA order, which makes the result independent of arrival
-    // order, and applies the epilogue. The last contributor to finish clears the
-    // tile's counters for the next call.
-    constexpr int CHUNK4 = NACC == 2 ? 2 : 4;          // float4 columns per chunk and accumulator
-    constexpr int CH_PER_SUB = MPAD / (4 * CHUNK4);
-    constexpr int CHUNKS = SUB * CH_PER_SUB;
-    constexpr int FIX_STAGE_CAP = 64;                  // 16-byte pieces a thread stages at a time (128 KB in all)
-    for (int pi = 0; pi < npending && *abortp == 0; ++pi) {
-      const long long tile = pending[pi];
-      const long long tile_begin = tile * args.kbt;
-      const long long tile_end = tile_begin + args.kbt;
-      const long long c_first = ((tile_begin + 1) * gridDim.x - 1) / total;
-      const long long c_last = (tile_end * gridDim.x - 1) / total;
-      const int nc = static_cast<int>(c_last - c_first + 1);
-      const int j = static_cast<int>(blockIdx.x - c_first);
-      if (ep_tid == 0) {
-        const volatile int* cnt = args.counters + tile;
-        const long long t0 = clock64();
-        while (*cnt != args.kbt) {
-          if (*abortp != 0 || clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            abort_flag = 1;
-            atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
-            break;
-          }
-          __nanosleep(64);
-        }
-        __threadfence();
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abortp != 0) break;
-      auto row_bias = [&](const T* bias, long long wrow) {
-        return (bias && wrow < args.rows) ? static_cast<float>(bias[wrow]) : 0.f;
-      };
-      const int p_begin = j * CHUNKS / nc, p_end = (j + 1) * CHUNKS / nc;
-      // The loads of a share are independent, and their latency is the kernel's tail, so
-      // they are issued all at once: cp.async copies them into the operand ring, which is
-      // idle by now (every MMA of this CTA has completed), each thread into a column of
-      // its own, and the sums are then taken from shared memory in CTA order.
-      auto slot_of = [&](long long c) -> const float4* {
-        const int w = unit_start(c, total, gridDim.x) >= tile_begin ? 0 : 1;
-        return reinterpret_cast<const float4*>(args.slots + (2LL * c + w) * SLOT_FLOATS);
-      };
-      auto stage_addr = [&](int k) { return smem_base + static_cast<uint32_t>(k * 128 + ep_tid) * 16u; };
-      auto issue_items = [&](int k, const float4* s4, int t, int ch) {  // ITEM4 copies for one (chunk, contributor)
-#pragma unroll
-        for (int a = 0; a < NACC; ++a)
-#pragma unroll
-          for (int i = 0; i < CHUNK4; ++i)
-            cp_async_16(stage_addr(k + a * CHUNK4 + i),
-                        s4 + ((t * NACC + a) * (MPAD / 4) + ch * CHUNK4 + i) * 128 + r_in_tile);
-      };
-      auto add_items = [&](int k, float (&sum)[NACC][4 * CHUNK4]) {
-#pragma unroll
-        for (int a = 0; a < NACC; ++a)
-#pragma unroll
-          for (int i = 0; i < CHUNK4; ++i) {
-            const float4 q = ld_shared_f4(stage_addr(k + a * CHUNK4 + i));
-            sum[a][4 * i] += q.x;
-            sum[a][4 * i + 1] += q.y;
-            sum[a][4 * i + 2] += q.z;
-            sum[a][4 * i + 3] += q.w;
-          }
-      };
-      auto emit_chunk = [&](int pch, const float (&sum)[NACC][4 * CHUNK4]) {
-        const int t = pch / CH_PER_SUB, ch = pch - t * CH_PER_SUB;
-        const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
-        if (wrow >= args.rows) return;
-        const float b0 = row_bias(bias0, wrow);
-        const float b1 = DUAL ? row_bias(bias1, wrow) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 4 * CHUNK4; ++i) {
-          const int m = ch * 4 * CHUNK4 + i;
-          if (m < args.M) {
-            float o;
-            if (DUAL) {
-              o = act_value(args.act, sum[0][i] + b0) * (sum[NACC - 1][i] + b1);
-            } else {
-              o = sum[0][i] + b0;
-            }
-            const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
-            if (!DUAL && residual) o += static_cast<float>(residual[oi]);
-            out[oi] = static_cast<T>(o);
-          }
-        }
-      };
-      constexpr int ITEM4 = NACC * CHUNK4;  // 16-byte pieces per (chunk, contributor) and thread
-      int pch = p_begin;
-      while (pch < p_end) {
-        if (nc * ITEM4 <= FIX_STAGE_CAP) {
-          // several chunks, all their contributors, in one round trip
-          int nch = FIX_STAGE_CAP / (nc * ITEM4);
-          if (nch > p_end - pch) nch = p_end - pch;
-          int k = 0;
-          for (int q = 0; q < nch; ++q) {
-            const int t = (pch + q) / CH_PER_SUB, ch = (pch + q) - t * CH_PER_SUB;
-            for (long long c = c_first; c <= c_last; ++c, k += ITEM4) issue_items(k, slot_of(c), t, ch);
-          }
-          cp_async_wait_all();
-          k = 0;
-          for (int q = 0; q < nch; ++q) {
-            float sum[NACC][4 * CHUNK4];
-#pragma unroll
-            for (int a = 0; a < NACC; ++a)
-#pragma unroll
-              for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
-            for (int ci = 0; ci < nc; ++ci, k += ITEM4) add_items(k, sum);
-            emit_chunk(pch + q, sum);
-          }
-          pch += nch;
-        } else {
-          // one chunk, its many contributors in batches
-          const int t = pch / CH_PER_SUB, ch = pch - t * CH_PER_SUB;
-          float sum[NACC][4 * CHUNK4];
-#pragma unroll
-          for (int a = 0; a < NACC; ++a)
-#pragma unroll
-            for (int i = 0; i < 4 * CHUNK4; ++i) sum[a][i] = 0.f;
-          constexpr int CB = FIX_STAGE_CAP / ITEM4;
-          for (long long cb = c_first; cb <= c_last; cb += CB) {
-            const long long ce = cb + CB - 1 < c_last ? cb + CB - 1 : c_last;
-            int k = 0;
-            for (long long c = cb; c <= ce; ++c, k += ITEM4) issue_items(k, slot_of(c), t, ch);
-            cp_async_wait_all();
-            k = 0;
-            for (long long c = cb; c <= ce; ++c, k += ITEM4) add_items(k, sum);
-          }
-          emit_chunk(pch, sum);
-          pch += 1;
-        }
-      }
-      // Everybody has read what it needs of this tile's slots: count this CTA as done.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ep_tid == 0) {
-        __threadfence();
-        if (atomicAdd(args.done + tile, 1) == nc - 1) {
-          args.counters[tile] = 0;  // leave the scratch ready for the next call
-          args.done[tile] = 0;
-        }
-      }
     }
   }
 

@@ -598,7 +598,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct DecodeLayout {
   int mpad;
-  size_t counters1_off, counters2_off, done1_off, done2_off, slots_off, total;
+  size_t counters1_off, counters2_off, slots_off, total;
 };
 static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
   DecodeLayout l;
@@ -606,9 +606,7 @@ static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
   const size_t t1 = static_cast<size_t>((p->N + 127) / 128), t2 = static_cast<size_t>((p->K + 127) / 128);
   l.counters1_off = 0;
   l.counters2_off = align_up(t1 * sizeof(int), 256);
-  l.done1_off = l.counters2_off + align_up(t2 * sizeof(int), 256);
-  l.done2_off = l.done1_off + align_up(t1 * sizeof(int), 256);
-  l.slots_off = l.done2_off + align_up(t2 * sizeof(int), 256);
+  l.slots_off = l.counters2_off + align_up(t2 * sizeof(int), 256);
   // one slot holds a CTA's partial row tile: all sub-tiles and accumulators of the larger kernel
   const size_t accs = l.mpad == 16
                           ? std::max<size_t>(2 * decode_subtiles<16, true>(), decode_subtiles<16, false>())
@@ -623,8 +621,8 @@ template <int MPAD, bool DUAL, typename T>
 static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
                            const void* w0, const void* w1, const void* act, int64_t act_ld,
                            const void* bias0, const void* bias1, const void* residual, void* out,
-                           int64_t ld_out, float* slots, int* counters, int* done, bool dependent,
-                           int gate_act, cudaStream_t stream) {
+                           int64_t ld_out, float* slots, int* counters, bool dependent, int gate_act,
+                           cudaStream_t stream) {
   CUtensorMap mW0, mW1, mAct;
   int rc;
   constexpr int BOX_ROWS = decode_box_rows<MPAD, DUAL>();
@@ -650,7 +648,6 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   a.ld_out = ld_out;
   a.slots = slots;
   a.counters = counters;
-  a.done = done;
   a.dependent = dependent ? 1 : 0;
   a.act = gate_act;
   const long long total = ((rows + TILE_ROWS - 1) / TILE_ROWS) * static_cast<long long>(a.kbt);
@@ -729,15 +726,13 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   // activations or touch h, y or the scratch (which a preceding decode call may still use).
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
                            b_gate, b_up, static_cast<const void*>(nullptr), h, p->N, slots,
-                           reinterpret_cast<int*>(sc + l.counters1_off),
-                           reinterpret_cast<int*>(sc + l.done1_off), true, p->act, st);
+                           reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
                               static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
                               static_cast<const void*>(nullptr), residual, y, p->K, slots,
-                              reinterpret_cast<int*>(sc + l.counters2_off),
-                              reinterpret_cast<int*>(sc + l.done2_off), true, p->act, st);
+                              reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
 }
 
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,
