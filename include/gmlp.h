@@ -222,15 +222,14 @@ int gmlp_set_sm_limit(int sms);
  * is kept on the device, so a call carries no per-call host state. src must be
  * complete on `stream` before the call. `dependent` != 0 launches the kernel as a
  * programmatic dependent of the preceding kernel on the stream (which must be the
- * one that wrote src). One kernel, no allocation, no host synchronisation: below
- * 256 KB (and always with fewer than four ranks) every partial is pushed to every
- * peer; from 256 KB on (when n divides by 8 * world) each rank reduces one slice and
- * hands the result round. The
- * wait for the peers is bounded (about a second); on expiry dst is left unwritten
- * and gmlp_status_read returns 4. Calls that share regions must not overlap on a
+ * one that wrote src). One kernel, no allocation, no host synchronisation: every
+ * partial is pushed to every peer, except from 1 MB on with eight ranks (and n a
+ * multiple of 8 * world), where each rank reduces one slice and hands the result
+ * round. The wait for the peers is bounded (about a second); on expiry dst is left
+ * unwritten and gmlp_status_read returns 4. Calls that share regions must not overlap on a
  * GPU (one stream per group). */
 /* Tuning / test hook: the size in bytes from which gmlp_peer_allreduce takes the
- * two-shot form. 0 = the built-in rule above, > 0 = from that many bytes at any group
+ * two-shot form. 0 = the built-in rule below, > 0 = from that many bytes at any group
  * size, < 0 = never. Every rank must use the same setting. Returns the previous one. */
 long long gmlp_set_peer_two_shot_bytes(long long bytes);
 size_t gmlp_peer_region_bytes(int64_t max_elems, int32_t world);

@@ -48,7 +48,7 @@ def main():
 
         # ---------------- the same step with the down projection and dx computed in chunks of 128 rows,
         # each chunk's all-reduce overlapping the next chunk's GEMM
-        m.tp_chunk_rows = 128
+        m.tp_chunk_rows = m.tp_chunk_rows_fwd = 128
         m.zero_grad(set_to_none=True)
         m.set_philox(seed, offset)
         x2 = case.x.to(dev).requires_grad_(True)
@@ -139,6 +139,9 @@ def main():
         every = [torch.empty_like(yp) for _ in range(world)]
         dist.all_gather(every, yp)
         assert all(torch.equal(e, every[0]) for e in every), "ranks disagree on the summed output"
+        md.peer_max_bytes = 0                 # above the cap the module goes back to the NCCL sum
+        with torch.no_grad():
+            assert torch.equal(md(cased.x.to(dev)), y_nccl)
         md._peer.close()
         comm.close()
         with torch.no_grad():

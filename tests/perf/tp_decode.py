@@ -64,6 +64,7 @@ def main():
                 t_nccl = timed(lambda: m(x), dev)
                 t_ar_nccl = timed(lambda: dist.all_reduce(y), dev)
                 comm = m.enable_peer_allreduce(64)
+                m.peer_max_bytes = 1 << 30   # time the peer sum at every M, also above the module's default cap
                 t_peer = timed(lambda: m(x), dev)
                 hook(-1)   # every partial to every peer
                 t_ar_one = timed(lambda: comm.all_reduce(y, out=y), dev)

@@ -1,6 +1,6 @@
 """Tensor-parallel prefill / training step (K=8192, N=28672 split over the ranks, bf16, M rows replicated):
 time per forward and per forward+backward with one all-reduce after the whole GEMM against the chunked form
-(module.tp_chunk_rows) whose all-reduces overlap the next chunk's GEMM.
+(module.tp_chunk_rows_fwd, module.tp_chunk_rows) whose all-reduces overlap the next chunk's GEMM.
 Usage: python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
        --master-port 29651 tests/perf/tp_prefill.py [M]"""
 import os
@@ -60,15 +60,16 @@ def main():
             x.grad = None
 
         rows = []
-        for chunk, sms in ((0, 16), (4096, 16), (4096, 32), (2048, 16)):
-            m.tp_chunk_rows, m.tp_comm_sms = chunk, sms
-            rows.append((chunk, sms, timed(fwd, 10, dev), timed(fwd_bwd, 5, dev)))
+        # (forward chunk rows, backward chunk rows, SMs left to the collective)
+        for cf, cb, sms in ((0, 0, 16), (0, 4096, 16), (4096, 4096, 16), (0, 2048, 16), (0, 4096, 32)):
+            m.tp_chunk_rows_fwd, m.tp_chunk_rows, m.tp_comm_sms = cf, cb, sms
+            rows.append((f"{cf}/{cb}", sms, timed(fwd, 10, dev), timed(fwd_bwd, 5, dev)))
         assert pkg._lib.status_read(dev) == 0
         if rank == 0:
             for chunk, sms, tf, tb in rows:
                 pf = 6.0 * M * K * N / tf / 1e12          # whole-job PFLOP/s (N is the un-sharded size)
                 pb = 18.0 * M * K * N / tb / 1e12
-                print(f"tp{world} M={M} chunk_rows={chunk} comm_sms={sms}: fwd {tf:.3f} ms ({pf:.2f} PFLOP/s), "
+                print(f"tp{world} M={M} chunk_rows(fwd/bwd)={chunk} comm_sms={sms}: fwd {tf:.3f} ms ({pf:.2f} PFLOP/s), "
                       f"fwd+bwd {tb:.3f} ms ({pb:.2f} PFLOP/s)", flush=True)
     finally:
         dist.destroy_process_group()

@@ -949,12 +949,13 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
   a.dependent = dependent ? 1 : 0;
   a.status = dev->status_ptr;
   // Kernel and grid depend on n and world alone, so that every rank makes the same
-  // choice and block b means the same slice everywhere. From 256 KB on and with four
-  // or more ranks, the two-shot form (each rank reduces one slice and hands it round)
-  // moves world/2 times less data over NVLink than pushing every partial to every
-  // peer; with two ranks it moves the same and only adds a second flag exchange.
+  // choice and block b means the same slice everywhere. The two-shot form (each rank
+  // reduces one slice and hands it round) moves world/2 times less data over NVLink but
+  // needs a second flag exchange. Measured at K=8192 (sum alone, one-shot / two-shot):
+  // 8 ranks 512 KB 18.8 / 21.9 us, 1 MB 24.5 / 22.7 us; 4 ranks 1 MB 16.3 / 19.6 us;
+  // 2 ranks 1 MB 11.0 / 17.1 us. So it is taken from 1 MB on with eight ranks only.
   const bool big = g_two_shot_bytes > 0 ? n * 2 >= g_two_shot_bytes
-                                        : (g_two_shot_bytes == 0 && world >= 4 && n * 2 >= PEER_TWO_SHOT_MIN_BYTES);
+                                        : (g_two_shot_bytes == 0 && world >= 8 && n * 2 >= PEER_TWO_SHOT_MIN_BYTES);
   const bool two_shot = big && (n % (8ll * world)) == 0;
   const long long vecs = two_shot ? n / 8 / world : n / 8;
   long long blocks = (vecs + PEER_THREADS - 1) / PEER_THREADS;

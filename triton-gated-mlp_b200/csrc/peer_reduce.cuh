@@ -42,7 +42,7 @@ constexpr int PEER_MAX_BLOCKS = 64;
 constexpr int PEER_THREADS = 512;
 constexpr int PEER_SLOT_ALIGN = 256;
 constexpr int GMLP_DEV_TIMEOUT_PEER = 4;
-constexpr long long PEER_TWO_SHOT_MIN_BYTES = 256 * 1024;
+constexpr long long PEER_TWO_SHOT_MIN_BYTES = 1024 * 1024;
 // About one second at the boost clock: the peers' kernels are launched by their own
 // hosts, so the skew between ranks is host scheduling noise, not device time.
 constexpr long long PEER_WAIT_LIMIT_CYCLES = 2000000000LL;
