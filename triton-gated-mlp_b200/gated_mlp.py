@@ -155,7 +155,7 @@ class FusedGatedMLP(nn.Module):
                      pass. > 0: that GEMM runs in chunks of this many token rows and
                      each chunk's all-reduce overlaps the next chunk's GEMM, the last
                      one the weight-gradient GEMMs (8 ranks, M=16384, K=8192, N=28672:
-                     fwd+bwd 8.56 -> 8.10 ms with 4096-row chunks in both passes).
+                     fwd+bwd 8.6-8.7 -> 8.10 ms with 4096-row chunks).
       tp_chunk_rows_fwd  the same for the down projection of the forward pass, where
                      nothing follows the last chunk to hide its all-reduce behind (the
                      same measurement: forward 3.04 -> 3.12 ms, so it is off by default).
