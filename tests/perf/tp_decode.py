@@ -2,7 +2,7 @@
 the partial outputs summed by NCCL and by the one-shot peer-memory kernel, and the two sums alone
 (all from CUDA graphs, so that the device time is measured and not the host's launch rate).
 Usage: python -m torch.distributed.run --nnodes=1 --nproc-per-node G --master-addr 127.0.0.1 \
-       --master-port 29650 tests/perf/tp_decode.py"""
+       --master-port 29650 tests/perf/tp_decode.py [nodep]"""
 import os
 import sys
 from pathlib import Path
@@ -65,6 +65,9 @@ def main():
                 t_ar_nccl = timed(lambda: dist.all_reduce(y), dev)
                 comm = m.enable_peer_allreduce(64)
                 m.peer_max_bytes = 1 << 30   # time the peer sum at every M, also above the module's default cap
+                if "nodep" in sys.argv:      # the peer sum as an ordinary launch, not a programmatic dependent
+                    plain = comm.all_reduce
+                    comm.all_reduce = lambda t, out=None, dependent=False: plain(t, out=out, dependent=False)
                 t_peer = timed(lambda: m(x), dev)
                 hook(-1)   # every partial to every peer
                 t_ar_one = timed(lambda: comm.all_reduce(y, out=y), dev)

@@ -207,9 +207,9 @@ class FusedGatedMLP(nn.Module):
         self.tp_chunk_rows_fwd = 0
         self.tp_comm_sms = 16
         # Largest partial output (bytes) the decode path sums through peer memory; above it NCCL
-        # is used. Measured at K=8192, 4 and 8 ranks: a win up to 512 KB (8 ranks, M=8: 67 -> 51 us
-        # per step), a loss at 1 MB (M=64: 90 -> 94 us).
-        self.peer_max_bytes = 512 * 1024
+        # is used. Measured at K=8192 over 8 ranks, step with NCCL sum -> with peer sum:
+        # M=1 64.5 -> 47.9 us, M=8 67.4 -> 50.4, M=32 (512 KB) 74.8 -> 62.9, M=64 (1 MB) 88.8 -> 86.1.
+        self.peer_max_bytes = 1024 * 1024
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -236,9 +236,11 @@ class FusedGatedMLP(nn.Module):
         if tp_group is not None:
             if (self._peer is not None and self._peer.supports(y)
                     and y.numel() * y.element_size() <= self.peer_max_bytes):
-                # the partial outputs are summed through the peers' memory, in place, chained to
-                # the down-projection kernel as a programmatic dependent
-                self._peer.all_reduce(y, out=y, dependent=True)
+                # The partial outputs are summed through the peers' memory, in place. As an
+                # ordinary launch: as a programmatic dependent of the down projection the sum was
+                # no faster at 16-512 KB and 8 us slower at 1 MB (8 ranks), its blocks then sit on
+                # SMs the down projection's last CTAs still use.
+                self._peer.all_reduce(y, out=y, dependent=False)
             else:
                 parallel.all_reduce_sum(y, tp_group)
         return y
