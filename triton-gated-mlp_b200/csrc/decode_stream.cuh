@@ -97,6 +97,16 @@ __device__ __forceinline__ long long unit_start(long long c, long long total, lo
   return (c * total) / g;
 }
 
+// out[m * ld] = act(gate[m] + b0) * (up[m] + b1) for the tokens m < M of one weight row,
+// with the activation a compile-time constant.
+template <int ACT, int COUNT, typename T>
+__device__ __forceinline__ void store_gated(T* po, long long ld, int M, const float* gate, const float* up,
+                                            float b0, float b1) {
+#pragma unroll
+  for (int m = 0; m < COUNT; ++m)
+    if (m < M) po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] + b0) * (up[m] + b1));
+}
+
 template <int MPAD, bool DUAL, typename T>
 __global__ void __launch_bounds__(DECODE_THREADS, 1)
 decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
@@ -317,23 +327,34 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * ACC_COLS + lane_addr;
 
-      // One output chunk: tokens [m0, m0 + count) of weight row `wrow`.
-      auto emit = [&](long long wrow, float b0, float b1, int m0, const float* first, const float* second,
-                      int count) {
+      // All MPAD tokens of weight row `wrow`. The activation is chosen OUTSIDE the unrolled
+      // token loop: with the switch inside, each of the 64 copies of the loop body carried
+      // every activation's code, the taken path was 64 islands in 150 KB of instructions run
+      // once per tile, and instruction fetch alone cost 21 us per forward at M = 64.
+      auto emit = [&](long long wrow, float b0, float b1, const float* first, const float* second) {
         if (wrow >= args.rows) return;
+        T* const po = out + wrow;
+        if (DUAL) {
+          switch (args.act) {
+            case ACT_SILU: store_gated<ACT_SILU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_NONE: store_gated<ACT_NONE, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_RELU: store_gated<ACT_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_GELU: store_gated<ACT_GELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_SIGMOID:
+              store_gated<ACT_SIGMOID, MPAD>(po, args.ld_out, args.M, first, second, b0, b1);
+              break;
+            case ACT_TANH: store_gated<ACT_TANH, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            default: store_gated<ACT_LEAKY_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+          }
+        } else {
+          const T* const pr = residual ? residual + wrow : nullptr;
 #pragma unroll
-        for (int i = 0; i < count; ++i) {
-          const int m = m0 + i;
-          if (m < args.M) {
-            float o;
-            if (DUAL) {
-              o = act_value(args.act, first[i] + b0) * (second[i] + b1);
-            } else {
-              o = first[i] + b0;
+          for (int m = 0; m < MPAD; ++m) {
+            if (m < args.M) {
+              float o = first[m] + b0;
+              if (pr) o += static_cast<float>(pr[static_cast<long long>(m) * args.ld_out]);
+              po[static_cast<long long>(m) * args.ld_out] = static_cast<T>(o);
             }
-            const long long oi = static_cast<long long>(m) * args.ld_out + wrow;
-            if (!DUAL && residual) o += static_cast<float>(residual[oi]);
-            out[oi] = static_cast<T>(o);
           }
         }
       };
@@ -425,7 +446,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         }
         if (complete || owner) {
           const long long wrow = tile * TILE_ROWS + t * 128 + r_in_tile;
-          emit(wrow, row_bias(bias0, wrow), DUAL ? row_bias(bias1, wrow) : 0.f, 0, v[0], v[NACC - 1], MPAD);
+          emit(wrow, row_bias(bias0, wrow), DUAL ? row_bias(bias1, wrow) : 0.f, v[0], v[NACC - 1]);
         } else {
           // this CTA's part of the sub-tile goes to its slot. Slot layout: float4 (sub-tile t,
           // accumulator a, i, row) at index ((t * NACC + a) * MPAD/4 + i) * 128 + row, so that
