@@ -208,7 +208,7 @@ class FusedGatedMLP(nn.Module):
         self.tp_comm_sms = 16
         # Largest partial output (bytes) the decode path sums through peer memory; above it NCCL
         # is used. Measured at K=8192 over 8 ranks, step with NCCL sum -> with peer sum:
-        # M=1 64.5 -> 47.9 us, M=8 67.4 -> 50.4, M=32 (512 KB) 74.8 -> 62.9, M=64 (1 MB) 88.8 -> 86.1.
+        # M=1 64.2 -> 46.5 us, M=8 66.4 -> 50.1, M=32 (512 KB) 70.1 -> 58.2, M=64 (1 MB) 75.7 -> 72.0.
         self.peer_max_bytes = 1024 * 1024
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
