@@ -352,7 +352,11 @@ __device__ __forceinline__ void read_row(const BlockView& bv, uint32_t buf, uint
 // lanes and its part of the tile's columns: lane i owns output row row0 + i and walks
 // the columns in units of 16. `taddr` addresses (lane quarter, first accumulator column
 // of the tile); `stage` is the warp's pair of staging blocks.
-template <int BN, int EPI, typename T>
+// ACTC: the gate activation as a compile-time constant, or -1 to read it from the
+// arguments. The unrolled epilogues hold 64 copies of the activation per tile pass; with
+// the seven-way switch in each copy the taken path is 64 islands in some 150 KB of
+// instructions, so the usual activation (SiLU) gets a body of its own.
+template <int BN, int EPI, typename T, int ACTC>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row0,
                                               int lane, int batch, int n0, int part,
                                               const BlockView& bv, uint32_t stage, const T* bias0,
@@ -450,7 +454,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
             qu[j] = pack8<T>(u);
           }
 #pragma unroll
-          for (int i = 0; i < 8; ++i) h[i] = act_value(args.act, g[i]) * u[i];
+          for (int i = 0; i < 8; ++i) h[i] = act_value(ACTC >= 0 ? ACTC : args.act, g[i]) * u[i];
           if (drop_on) {
             float f[8];
             dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
@@ -511,7 +515,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           float f, df;
-          act_value_grad(args.act, g[i], f, df);
+          act_value_grad(ACTC >= 0 ? ACTC : args.act, g[i], f, df);
           du[i] = dh[i] * f;
           dg[i] = dh[i] * u[i] * df;
         }
@@ -559,8 +563,12 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, in
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + acc * BN + lane_addr;
     const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
-    epilogue_tile<BN, EPI, T>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
-                              bias0, bias1, drop_on);
+    if (EPI != EPI_STORE && args.act == ACT_SILU)
+      epilogue_tile<BN, EPI, T, ACT_SILU>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
+                                bias0, bias1, drop_on);
+    else
+      epilogue_tile<BN, EPI, T, -1>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
+                                bias0, bias1, drop_on);
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
     // semantics; no fence is placed here on purpose, since a fence would also wait for
