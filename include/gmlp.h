@@ -74,8 +74,17 @@ typedef struct gmlp_problem_t {
   int64_t col0_global;  /* global index of local intermediate column 0 (TP sharding) */
   int64_t N_global;     /* un-sharded intermediate size; 0 means N */
   int32_t act;          /* gmlp_act_t of the gate (0 = SiLU) */
-  int32_t reserved;     /* must be 0 */
+  uint32_t tuning;      /* per-call GEMM tuning, GMLP_TUNE_* fields ORed together; 0 = the defaults */
 } gmlp_problem_t;
+
+/* Fields of gmlp_problem_t.tuning. A field left 0 takes the process-wide default
+ * (the built-in rule unless a gmlp_set_* call changed it). Because the values travel
+ * with the call, two modules, host threads or devices never change each other's grids.
+ * No counterpart in the reference, which fixes these through its autotuner
+ * (src/triton_gated_mlp/ops/fwd.py:48-62). */
+#define GMLP_TUNE_PAIR_MODE(m) ((uint32_t)(m) & 3u)               /* 1 single-CTA kernel, 2 CTA pair */
+#define GMLP_TUNE_RASTER_GROUP(g) (((uint32_t)(g) & 0xFFFu) << 2)  /* row tiles per raster group */
+#define GMLP_TUNE_SM_LIMIT(n) (((uint32_t)(n) & 0xFFFu) << 14)     /* SMs a GEMM grid may occupy */
 
 /* H[M,N] = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)), act = p->act (SiLU by default).
  * Replaces mlp_hidden_states_fwd (src/triton_gated_mlp/ops/fwd.py:198-279, kernel
@@ -141,7 +150,11 @@ int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int6
  *     GMLP_ERR_SCRATCH and a message; use gmlp_colsum for them.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress) with that device current; make that first call before
- *     starting any stream capture.
+ *     starting any stream capture. The first libgmlp call of any kind on a device is
+ *     also when the CUDA runtime loads the library's device image, this array
+ *     included: a host that is about to hand all remaining device memory to its own
+ *     pool must make one libgmlp call on every device BEFORE it does so, or the image
+ *     finds no room.
  *   - All calls on a device share the one array. It keeps whatever the last call left
  *     there, which is harmless (the first pass overwrites every value the second pass
  *     reads), but two calls that overlap on the GPU (different streams) race on it:
@@ -158,8 +171,16 @@ int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* sr
  * already wastes the tensor pipe. dropout_p must be 0.
  * `scratch`: gmlp_decode_scratch_bytes(p) bytes, 16-byte aligned. Its leading
  * counter area (the first 64 KiB is more than enough) must be ZERO before the first
- * call; every call leaves it zero again, so one memset at allocation suffices.
- * Calls that share a scratch buffer must not overlap on the GPU. */
+ * call; every call leaves it zero again, so one memset at allocation suffices, with
+ * one exception: after gmlp_status_read has returned a non-zero word (a kernel gave
+ * up a wait) the counter area must be cleared again before the scratch is reused.
+ * Calls that share a scratch buffer must not overlap on the GPU.
+ * Both kernels start as programmatic dependents of whatever precedes them on
+ * `stream` and begin streaming WEIGHTS before that predecessor has finished (they
+ * wait for it only before touching x, h, y or the scratch). The kernel immediately
+ * before the call on the stream must therefore not write w_gate, w_up or w_down:
+ * after an optimiser step, a dequantisation or a weight merge into those buffers,
+ * put any other kernel (or an event wait) between it and the call. */
 size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p);
 int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, const void* w_down,

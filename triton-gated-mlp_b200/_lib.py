@@ -39,7 +39,7 @@ class Problem(C.Structure):
         ("dtype", C.c_int32), ("dropout_p", C.c_float),
         ("seed", C.c_uint64), ("offset", C.c_uint64),
         ("row0_global", C.c_int64), ("col0_global", C.c_int64), ("N_global", C.c_int64),
-        ("act", C.c_int32), ("reserved", C.c_int32),
+        ("act", C.c_int32), ("tuning", C.c_uint32),
     ]
 
 
@@ -137,16 +137,37 @@ def require_cuda(*tensors: torch.Tensor | None) -> torch.device:
     return dev
 
 
+_scratch_epoch = 0
+
+
+def scratch_epoch() -> int:
+    """Counts the non-zero status words read so far. Scratch that kernels keep zeroed between
+    calls (the decode counters) may be dirty after a kernel gave up a wait; holders of such
+    scratch allocate afresh when the epoch has moved."""
+    return _scratch_epoch
+
+
 def status_read(device: torch.device | None = None) -> int:
     """Synchronise `device` and return (and clear) its kernel status word."""
+    global _scratch_epoch
     v = C.c_int(0)
     with torch.cuda.device(device):
         check(load().gmlp_status_read(C.byref(v)))
+    if v.value != 0:
+        _scratch_epoch += 1
     return v.value
 
 
+def tune_word(pair_mode: int = 0, raster_group: int = 0, sm_limit: int = 0) -> int:
+    """gmlp_problem_t.tuning for one call (the GMLP_TUNE_* fields of include/gmlp.h); 0 fields = defaults."""
+    if not (0 <= pair_mode <= 2 and 0 <= raster_group <= 4095 and 0 <= sm_limit <= 4095):
+        raise ValueError("pair_mode in 0..2, raster_group and sm_limit in 0..4095")
+    return (pair_mode & 3) | ((raster_group & 0xFFF) << 2) | ((sm_limit & 0xFFF) << 14)
+
+
 def set_cta_pair_mode(mode: int) -> int:
-    """0 = per problem, 1 = single-CTA kernel only, 2 = CTA-pair kernel only; returns the previous mode."""
+    """Process-wide default: 0 = per problem, 1 = single-CTA kernel only, 2 = CTA-pair kernel only; returns the
+    previous mode. A call that carries its own tune_word() is not affected."""
     return load().gmlp_set_cta_pair_mode(int(mode))
 
 

@@ -43,7 +43,8 @@ struct DecodeArgs {
   const void* residual;  // optional [M, rows] added to the output (down projection only)
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
-  int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry and on exit
+  int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry, and on exit
+                      // unless the kernel gave up a wait (status word != 0): then the host clears them
   int act;            // gate activation (ACT_*), DUAL only
   int dependent;      // 1: launched with programmatic stream serialization behind the kernel
                       //    that produces the activations (and last used slots / counters)
@@ -58,14 +59,8 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 constexpr int DECODE_THREADS = 192;
-// One CTA per SM. What the handling of split row tiles costs was measured with one-off
-// builds at K=8192, N=28672: with no split-tile work at all a forward takes 211 / 214 /
-// 219 us at M = 8 / 32 / 64, against 226 / 231 / 249 us when every contributor publishes
-// its part, waits for the others and sums a share of both its split tiles at the end of
-// the kernel. Tried against that gap and measured no better: two CTAs per SM with half
-// the ring each; whole row tiles owned by CTAs with only the remainder split and summed
-// early (15 us slower); the gate/up kernel prefetching the down projection's first
-// weight boxes into L2 during its tail (no change).
+// One CTA per SM, one weight sub-tile per unit (two CTAs per SM with half the ring each,
+// and larger units with whole row tiles owned by CTAs, were both slower).
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_subtiles() {
   return 1;
@@ -75,8 +70,7 @@ __host__ __device__ constexpr int decode_stage_bytes() {
   return (DUAL ? 2 : 1) * decode_subtiles<MPAD, DUAL>() * 16384 + MPAD * 128;
 }
 // As many stages as fit in shared memory: bytes in flight per SM are what hides the
-// DRAM latency (with 8 stages of 16 KB the down-projection kernel streamed at 5.6 TB/s
-// where the gate/up kernel, with 160 KB in flight, reached 6.4 TB/s).
+// DRAM latency.
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_stages() {
   constexpr int fit = (232448 - 1024 - 512) / decode_stage_bytes<MPAD, DUAL>();
@@ -320,17 +314,18 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
       }
       // The four epilogue warps meet at named barriers further down; they must all
-      // take the same way out, so they agree on the outcome of the wait first. Every
+      // take the same way out, so they VOTE on the outcome of the wait: the barrier
+      // returns one answer to all 128 threads even if the abort flag (set at any time
+      // by the producer or the MMA thread) flips between two warps' reads of it. Every
       // warp reaches this barrier because its wait above is bounded.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*abortp != 0) break;
+      if (named_bar_or(1, 128, *abortp != 0)) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * ACC_COLS + lane_addr;
 
       // All MPAD tokens of weight row `wrow`. The activation is chosen OUTSIDE the unrolled
-      // token loop: with the switch inside, each of the 64 copies of the loop body carried
-      // every activation's code, the taken path was 64 islands in 150 KB of instructions run
-      // once per tile, and instruction fetch alone cost 21 us per forward at M = 64.
+      // token loop: with the switch inside, each of the 64 copies of the loop body carries
+      // every activation's code and the taken path is 64 islands in 150 KB of instructions
+      // run once per tile, which costs instruction fetch time at every tile.
       auto emit = [&](long long wrow, float b0, float b1, const float* first, const float* second) {
         if (wrow >= args.rows) return;
         T* const po = out + wrow;
@@ -390,8 +385,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
           }
           __threadfence();
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abortp != 0) break;
+        if (named_bar_or(1, 128, *abortp != 0)) break;
       }
 
 #pragma unroll 1

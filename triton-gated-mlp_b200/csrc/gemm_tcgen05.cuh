@@ -3,9 +3,11 @@
 //   warp 0 (one lane)  TMA producer: fills a STAGES-deep shared-memory ring
 //   warp 1 (one lane)  MMA issuer: tcgen05.mma into one of two TMEM accumulators
 //   warps 2..17        epilogue: tcgen05.ld the finished accumulator, apply the
-//                      fused elementwise work, store to global memory
+//                      fused elementwise work, hand the result to TMA stores
+//   warp 18            watcher: waits for "accumulator full" and wakes the epilogue
+//                      warps, which sleep at a named barrier meanwhile
 // The two TMEM accumulators let the epilogue of tile i overlap the main loop of
-// tile i+1. No cluster launch and no TMA multicast is used.
+// tile i+1. No TMA multicast is used.
 //
 // Logical problem: C[M, N] = sum_k A[m, k] * B[n, k], 16-bit inputs, fp32
 // accumulation. Each operand can be stored K-major (reduction index contiguous)
@@ -57,23 +59,43 @@ struct GemmArgs {
 constexpr int BM = 128;        // rows per tile = TMEM lanes
 constexpr int BK = 64;         // reduction elements per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 16;     // reduction elements per tcgen05.mma (16-bit inputs)
-constexpr int GEMM_THREADS = 576;  // producer warp, MMA warp, 16 epilogue warps
+
+// Epilogue warps, and who wakes them. The sixteen epilogue warps have nothing to do for
+// most of a tile's main loop. Polling the "accumulator full" mbarrier from each of them
+// issues instructions the whole time, which on a power-capped part costs clock; so they
+// sleep at a named barrier (no issue slots) and ONE watcher warp polls the mbarrier and
+// arrives on the named barrier for them. The watcher also decides, once per tile and
+// for all epilogue warps alike, whether the tile is processed or the kernel is being
+// abandoned (epi_go), so the warps can never take different ways out.
+constexpr int EPI_WARPS = 16;
+constexpr int WATCHER_WARP = 2 + EPI_WARPS;
+constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);        // 608
+constexpr uint32_t EPI_BAR_THREADS = 32 * (EPI_WARPS + 1);  // epilogue warps + watcher
+constexpr uint32_t EPI_BAR_ID0 = 1;                       // named barriers 1, 2: one per accumulator
 
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
   return (2 * bn <= 32) ? 32u : (2 * bn <= 64) ? 64u : (2 * bn <= 128) ? 128u
          : (2 * bn <= 256) ? 256u : 512u;
 }
 
-// Epilogue warps and their staging buffers (see "Epilogue I/O" below).
-constexpr int EPI_WARPS = 16;
-constexpr int EPI_PARTS = EPI_WARPS / 4;                  // column parts of a tile
-constexpr int BLK_BYTES = 32 * 32;                        // one warp's [32 rows x 16 columns] 16-bit block
-constexpr int STAGING_BYTES = EPI_WARPS * 2 * BLK_BYTES;  // two blocks per warp: 32 KB
-
-// Operand ring + the epilogue warps' staging blocks + alignment slack.
-template <int BN, int STAGES>
+// Epilogue staging (see "Epilogue I/O" below).
+constexpr int EPI_PARTS = EPI_WARPS / 4;  // column parts of a tile
+constexpr int BLK_BYTES = 32 * 32;        // dH epilogue: one warp's [32 rows x 16 columns] 16-bit block
+constexpr int STORE_STAGE_BYTES = 4096;   // store / gate-up epilogues: 4 KB per warp
+template <int EPI>
+__host__ __device__ constexpr int staging_bytes() {
+  return EPI == EPI_DHIDDEN ? EPI_WARPS * 2 * BLK_BYTES : EPI_WARPS * STORE_STAGE_BYTES;
+}
+// Ring depth: as many stages as fit beside the staging area in the 227 KB a CTA may use.
+constexpr int SMEM_LIMIT = 232448;
+template <int B_ROWS, int EPI>
+__host__ __device__ constexpr int gemm_stages() {
+  return (SMEM_LIMIT - 2048 - staging_bytes<EPI>()) / (BM * 128 + B_ROWS * 128);
+}
+// Operand ring (B_ROWS rows of B per stage and CTA) + staging + alignment slack.
+template <int B_ROWS, int EPI, int STAGES>
 constexpr size_t gemm_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + BN * 128) + STAGING_BYTES + 1024;
+  return static_cast<size_t>(STAGES) * (BM * 128 + B_ROWS * 128) + staging_bytes<EPI>() + 1024;
 }
 
 // ------------------------------------------------------------ small helpers --
@@ -237,23 +259,32 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
 
 // ------------------------------------------------------------ Epilogue I/O ----
 // EPI_WARPS = 16 epilogue warps, four per TMEM lane quarter: warp e (0..15) reads TMEM
-// lanes 32 * (e & 3) and column part (e >> 2) of the tile, in units of 16 columns.
+// lanes 32 * (e & 3) and column part (e >> 2) of the tile.
 //
 // After tcgen05.ld a thread owns one output ROW. Moving data between global memory and
 // that layout directly makes every 16-byte access of a warp touch 32 different cache
-// lines, half a sector each; measured on the training shape, each extra matrix written
-// that way cost a third of the whole GEMM. Routing the blocks through the TMA engine
-// instead ran into its request rate (about one row of a box per cycle, so 32-byte rows
-// waste three quarters of it and the dH kernel's epilogue alone used up the whole
-// budget its operand loads need). So the epilogue keeps to the load/store unit and
-// fixes the access pattern: every warp owns two 1 KB staging blocks ([32 rows x 16
-// columns], 32-byte rows) in shared memory and transposes through them, so that in
-// global memory two neighbouring lanes cover one row's 32 bytes and one instruction
-// moves 16 full sectors.
+// lines, so every epilogue goes through shared memory.
+//
+// Store and gate/up epilogues: each warp writes its rows into a staging block laid out
+// the way a TMA store expects it (rows of 128 or 64 bytes, swizzled in 16-byte chunks so
+// that the 32 row-owning lanes hit 32 different bank groups), and one lane hands the whole
+// [32 rows x 64 or 32 columns] block to the TMA engine: one bulk store instead of
+// st.shared / ld.shared / st.global round trips on the load/store unit, no address
+// arithmetic or bounds predicates per access (the TMA engine clips at the matrix edge).
+// Rows of 128 bytes where a warp covers 64 columns; the gate/up epilogue covers 32 hidden
+// columns per warp and uses 64-byte rows. (TMA requests are counted per row of a box:
+// the shorter the row, the more of the engine's request rate a block costs, which is why
+// no epilogue uses 32-byte rows.)
+//
+// dH epilogue: it also LOADS two [M, N] matrices and keeps to the load/store unit: every
+// warp owns two 1 KB staging blocks ([32 rows x 16 columns], 32-byte rows) and transposes
+// through them, so that in global memory two neighbouring lanes cover one row's 32 bytes.
 //   row view        lane r holds row r:            bytes [32 r, 32 r + 32)
 //   coalesced view  lane l, step t in {0, 1}:      row (l >> 1) + 16 t, 16-byte half l & 1
 // The two halves of a row swap places in rows 4..7 of every group of 8 (a 32-byte
-// swizzle), which keeps both views free of bank conflicts.
+// swizzle), which keeps both views free of bank conflicts. Every element is read and
+// then written by the same lane at the same coordinates, so dGate / dUp may be the very
+// buffers G / U were read from.
 template <typename T>
 __device__ __forceinline__ void unpack8(const uint4& q, float (&v)[8]) {
   float2 a = Pack2<T>::unpack(q.x), b = Pack2<T>::unpack(q.y), c = Pack2<T>::unpack(q.z),
@@ -284,7 +315,46 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& q) {
                : "memory");
 }
 
-// Addressing of one warp's staging blocks for one lane.
+// Offset of 16-byte chunk `c` of row `r` in a staging block with rows of ROW_BYTES
+// (128 or 64), swizzled the way the TMA engine reads it back: the chunk index is XORed
+// with bits [7, 7 + log2(ROW_BYTES / 16)) of the byte address.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t staged_chunk(int r, int c) {
+  static_assert(ROW_BYTES == 128 || ROW_BYTES == 64, "row length of a staging block");
+  const int x = ROW_BYTES == 128 ? (r & 7) : ((r >> 1) & 3);
+  return static_cast<uint32_t>(r * ROW_BYTES + ((c ^ x) << 4));
+}
+
+// SiLU on two values at once: sigma(x) = 0.5 tanh(x / 2) + 0.5 with the multiplies and
+// FMAs issued as packed fp32 pairs.
+__device__ __forceinline__ f32x2 sigmoid2(f32x2 x) {
+  const f32x2 half = f2_pack(0.5f, 0.5f);
+  float a, b;
+  f2_unpack(f2_mul(x, half), a, b);
+  return f2_fma(f2_pack(tanh_f(a), tanh_f(b)), half, half);
+}
+
+// keep/scale factors for 8 consecutive columns as in dropout_factors8, with the tests
+// done on the raw words: (w >> 16) >= t  <=>  w >= (t << 16), and for the low half the
+// same after shifting it up.
+__device__ __forceinline__ void dropout_factors8_fast(const DropoutParams& d, long long grow,
+                                                      long long gcol, float (&f)[8]) {
+  const unsigned long long e =
+      static_cast<unsigned long long>(grow) * static_cast<unsigned long long>(d.ncols_global) +
+      static_cast<unsigned long long>(gcol);
+  const Philox4 r = dropout_words(d, e >> 3);
+  const uint32_t t = d.thresh << 16;
+  f[0] = (r.x << 16) >= t ? d.scale : 0.0f;
+  f[1] = r.x >= t ? d.scale : 0.0f;
+  f[2] = (r.y << 16) >= t ? d.scale : 0.0f;
+  f[3] = r.y >= t ? d.scale : 0.0f;
+  f[4] = (r.z << 16) >= t ? d.scale : 0.0f;
+  f[5] = r.z >= t ? d.scale : 0.0f;
+  f[6] = (r.w << 16) >= t ? d.scale : 0.0f;
+  f[7] = r.w >= t ? d.scale : 0.0f;
+}
+
+// Addressing of one warp's dH staging blocks for one lane.
 struct BlockView {
   uint32_t row_lo, row_hi;   // row view: offsets of this lane's two 16-byte halves
   uint32_t co[2];            // coalesced view: offset of this lane's 16 bytes in step t
@@ -325,7 +395,8 @@ __device__ __forceinline__ void store_block(const BlockView& bv, uint32_t buf, T
   }
 }
 // First half of a block load: this lane's two 16-byte pieces in the coalesced view
-// (zero where the block leaves the matrix). Issued one unit ahead of use.
+// (zero where the block leaves the matrix). Issued one unit ahead of use. Ordinary
+// loads, not the read-only path: the block may be overwritten in place later on.
 template <typename T>
 __device__ __forceinline__ void fetch_block(const BlockView& bv, const T* in, long long ld, int row0,
                                             int col, int M, int N, uint4 (&v)[2]) {
@@ -334,7 +405,7 @@ __device__ __forceinline__ void fetch_block(const BlockView& bv, const T* in, lo
   for (int t = 0; t < 2; ++t) {
     const int r = row0 + bv.crow[t];
     v[t] = make_uint4(0u, 0u, 0u, 0u);
-    if (r < M && c < N) v[t] = __ldg(reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * ld + c));
+    if (r < M && c < N) v[t] = *reinterpret_cast<const uint4*>(in + static_cast<long long>(r) * ld + c);
   }
 }
 // Second half: through the staging block into the row view. The caller places a
@@ -348,129 +419,165 @@ __device__ __forceinline__ void read_row(const BlockView& bv, uint32_t buf, uint
   hi = ld_shared_v4(buf + bv.row_hi);
 }
 
+// The output matrices of a launch as TMA sees them (store and gate/up epilogues).
+struct OutMaps {
+  const CUtensorMap* o0;
+  const CUtensorMap* o1;
+  const CUtensorMap* o2;
+};
+
 // Epilogue of one 128-row accumulator tile, executed by one warp for its 32 TMEM
-// lanes and its part of the tile's columns: lane i owns output row row0 + i and walks
-// the columns in units of 16. `taddr` addresses (lane quarter, first accumulator column
-// of the tile); `stage` is the warp's pair of staging blocks.
+// lanes and its part of the tile's columns: lane i owns output row row0 + i. `taddr`
+// addresses (lane quarter, first accumulator column of the tile); `stage` is the warp's
+// staging area.
 // ACTC: the gate activation as a compile-time constant, or -1 to read it from the
-// arguments. The unrolled epilogues hold 64 copies of the activation per tile pass; with
-// the seven-way switch in each copy the taken path is 64 islands in some 150 KB of
+// arguments. The unrolled epilogues hold many copies of the activation per tile pass;
+// with the seven-way switch in each copy the taken path is islands in a sea of
 // instructions, so the usual activation (SiLU) gets a body of its own.
 template <int BN, int EPI, typename T, int ACTC>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t taddr, int row0,
-                                              int lane, int batch, int n0, int part,
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
+                                              int row0, int lane, int batch, int n0, int part,
                                               const BlockView& bv, uint32_t stage, const T* bias0,
                                               const T* bias1, bool drop_on) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-  constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
-  static_assert(NU >= 1, "tile too narrow for the column parts");
   const int row = row0 + lane;
   const bool row_ok = row < args.M;
-  const int u0 = part * NU;
   const int M = args.M, N = args.N;
-  int flip = 0;  // which of the two staging blocks the next store uses
-  auto next_block = [&]() {
-    const uint32_t b = stage + flip * BLK_BYTES;
-    flip ^= 1;
-    return b;
-  };
 
-  if (EPI == EPI_STORE) {
-    T* const out = static_cast<T*>(batch ? args.out1 : args.out0);
+  if constexpr (EPI == EPI_STORE) {
+    constexpr int WCOLS = TILE_N / EPI_PARTS;  // columns per warp
+    static_assert(WCOLS == 64, "the store epilogue stages [32 x 64] blocks (128-byte rows)");
+    const int col = n0 + part * WCOLS;
+    if (col >= N || row0 >= M) return;  // warp-uniform: nothing of this block is inside the matrix
     const T* const res =
         args.in0 ? static_cast<const T*>(args.in0) + static_cast<long long>(row) * args.ld_in : nullptr;
+    // the block may still be feeding the previous tile's store
+    if (lane == 0) bulk_wait_group_read<0>();
+    __syncwarp();
 #pragma unroll
-    for (int ui = 0; ui < NU; ++ui) {
-      const int col = n0 + (u0 + ui) * 16;
-      uint32_t acc[16];
-      tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
+    for (int hh = 0; hh < 2; ++hh) {
+      uint32_t acc[32];
+      tmem_ld_32x32(taddr + part * WCOLS + hh * 32, acc);
       tmem_ld_wait();
-      if (col < N && row0 < M) {  // warp-uniform
-        uint4 q[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int gc = col + j * 8;
-          float v[8];
+      for (int j = 0; j < 4; ++j) {
+        const int gc = col + hh * 32 + j * 8;
+        float v[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
-          if (gc < N) {
-            if (bias0) {
-              float b[8];
-              load8(bias0 + gc, b);
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[j * 8 + i]);
+        if (gc < N) {
+          if (bias0) {
+            float b[8];
+            load8(bias0 + gc, b);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += b[i];
-            }
-            if (res && row_ok) {
-              float b[8];
-              load8(res + gc, b);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += b[i];
-            }
+            for (int i = 0; i < 8; ++i) v[i] += b[i];
           }
-          q[j] = pack8<T>(v);
+          if (res && row_ok) {
+            float b[8];
+            load8(res + gc, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] += b[i];
+          }
         }
-        store_block<T>(bv, next_block(), out, args.ld_out, row0, col, M, N, q[0], q[1]);
+        st_shared_v4(stage + staged_chunk<128>(lane, hh * 4 + j), pack8<T>(v));
       }
     }
-  } else if (EPI == EPI_SWIGLU) {
-    T* const out_h = static_cast<T*>(args.out0);
-    T* const out_g = static_cast<T*>(args.out1);
-    T* const out_u = static_cast<T*>(args.out2);
+    fence_proxy_async_smem();  // the staged rows become visible to the TMA engine
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(batch ? maps.o1 : maps.o0, stage, col, row0);
+      bulk_commit_group();
+    }
+  } else if constexpr (EPI == EPI_SWIGLU) {
+    constexpr int WCOLS = TILE_N / EPI_PARTS;  // hidden columns per warp
+    static_assert(WCOLS == 32, "the gate/up epilogue stages [32 x 32] blocks (64-byte rows)");
+    const int col = n0 + part * WCOLS;
+    if (col >= N || row0 >= M) return;  // warp-uniform
+    const bool save = args.out1 != nullptr;  // keep the pre-activations for the backward pass
+    const uint32_t buf_a = stage, buf_b = stage + STORE_STAGE_BYTES / 2;
     const long long grow = args.drop.row0_global + row;
+    if (lane == 0) bulk_wait_group_read<0>();
+    __syncwarp();
+    uint4 qu[4];  // U waits in registers until H has left its block
 #pragma unroll
-    for (int ui = 0; ui < NU; ++ui) {
-      const int col = n0 + (u0 + ui) * 16;
+    for (int hh = 0; hh < 2; ++hh) {
       uint32_t rg[16], ru[16];
-      tmem_ld_32x16(taddr + (u0 + ui) * 16, rg);
-      tmem_ld_32x16(taddr + TILE_N + (u0 + ui) * 16, ru);
+      tmem_ld_32x16(taddr + part * WCOLS + hh * 16, rg);
+      tmem_ld_32x16(taddr + TILE_N + part * WCOLS + hh * 16, ru);
       tmem_ld_wait();
-      if (col < N && row0 < M) {  // warp-uniform
-        uint4 qh[2], qg[2], qu[2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int gc = col + j * 8;
-          float g[8], u[8], h[8];
+      for (int j = 0; j < 2; ++j) {
+        const int gc = col + hh * 16 + j * 8;
+        float g[8], u[8], h[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            g[i] = __uint_as_float(rg[j * 8 + i]);
-            u[i] = __uint_as_float(ru[j * 8 + i]);
+        for (int i = 0; i < 8; ++i) {
+          g[i] = __uint_as_float(rg[j * 8 + i]);
+          u[i] = __uint_as_float(ru[j * 8 + i]);
+        }
+        if (gc < N) {
+          if (bias0) {
+            float b[8];
+            load8(bias0 + gc, b);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] += b[i];
           }
-          if (gc < N) {
-            if (bias0) {
-              float b[8];
-              load8(bias0 + gc, b);
+          if (bias1) {
+            float b[8];
+            load8(bias1 + gc, b);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) g[i] += b[i];
-            }
-            if (bias1) {
-              float b[8];
-              load8(bias1 + gc, b);
+            for (int i = 0; i < 8; ++i) u[i] += b[i];
+          }
+        }
+        const uint32_t off = staged_chunk<64>(lane, hh * 2 + j);
+        if (save) {
+          st_shared_v4(buf_b + off, pack8<T>(g));
+          qu[hh * 2 + j] = pack8<T>(u);
+        }
+        if (ACTC == ACT_SILU) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) u[i] += b[i];
-            }
+          for (int i = 0; i < 8; i += 2) {
+            const f32x2 g2 = f2_pack(g[i], g[i + 1]);
+            const f32x2 h2 = f2_mul(f2_mul(g2, sigmoid2(g2)), f2_pack(u[i], u[i + 1]));
+            f2_unpack(h2, h[i], h[i + 1]);
           }
-          if (out_g) {  // keep the pre-activations for the backward pass
-            qg[j] = pack8<T>(g);
-            qu[j] = pack8<T>(u);
-          }
+        } else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) h[i] = act_value(ACTC >= 0 ? ACTC : args.act, g[i]) * u[i];
-          if (drop_on) {
-            float f[8];
-            dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+        }
+        if (drop_on) {
+          float f[8];
+          dropout_factors8_fast(args.drop, grow, args.drop.col0_global + gc, f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) h[i] *= f[i];
-          }
-          qh[j] = pack8<T>(h);
+          for (int i = 0; i < 8; ++i) h[i] *= f[i];
         }
-        store_block<T>(bv, next_block(), out_h, args.ld_out, row0, col, M, N, qh[0], qh[1]);
-        if (out_g) {
-          store_block<T>(bv, next_block(), out_g, args.ld_out, row0, col, M, N, qg[0], qg[1]);
-          store_block<T>(bv, next_block(), out_u, args.ld_out, row0, col, M, N, qu[0], qu[1]);
-        }
+        st_shared_v4(buf_a + off, pack8<T>(h));
+      }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(maps.o0, buf_a, col, row0);
+      bulk_commit_group();
+      if (save) {
+        tma_store_2d(maps.o1, buf_b, col, row0);
+        bulk_commit_group();
+        bulk_wait_group_read<1>();  // H has been read out of its block
+      }
+    }
+    if (save) {
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) st_shared_v4(buf_a + staged_chunk<64>(lane, c), qu[c]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(maps.o2, buf_a, col, row0);
+        bulk_commit_group();
       }
     }
   } else {  // EPI_DHIDDEN
+    constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
+    const int u0 = part * NU;
     T* const out_g = static_cast<T*>(args.out0);
     T* const out_u = static_cast<T*>(args.out1);
     const T* const in_g = static_cast<const T*>(args.in0);
@@ -508,16 +615,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
         unpack8<T>(uq[j], u);
         if (drop_on) {
           float f[8];
-          dropout_factors8(args.drop, grow, args.drop.col0_global + gc, f);
+          dropout_factors8_fast(args.drop, grow, args.drop.col0_global + gc, f);
 #pragma unroll
           for (int i = 0; i < 8; ++i) dh[i] *= f[i];
         }
+        if (ACTC == ACT_SILU) {
+          // s = sigma(g), f = g s, f' = s + f (1 - s); d_up = dh f, d_gate = dh u f'
+          const f32x2 one = f2_pack(1.0f, 1.0f), neg = f2_pack(-1.0f, -1.0f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float f, df;
-          act_value_grad(ACTC >= 0 ? ACTC : args.act, g[i], f, df);
-          du[i] = dh[i] * f;
-          dg[i] = dh[i] * u[i] * df;
+          for (int i = 0; i < 8; i += 2) {
+            const f32x2 g2 = f2_pack(g[i], g[i + 1]), dh2 = f2_pack(dh[i], dh[i + 1]);
+            const f32x2 s2 = sigmoid2(g2);
+            const f32x2 f2v = f2_mul(g2, s2);
+            const f32x2 df2 = f2_fma(f2v, f2_fma(s2, neg, one), s2);
+            f2_unpack(f2_mul(dh2, f2v), du[i], du[i + 1]);
+            f2_unpack(f2_mul(f2_mul(dh2, f2_pack(u[i], u[i + 1])), df2), dg[i], dg[i + 1]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float f, df;
+            act_value_grad(ACTC >= 0 ? ACTC : args.act, g[i], f, df);
+            du[i] = dh[i] * f;
+            dg[i] = dh[i] * u[i] * df;
+          }
         }
         qg[j] = pack8<T>(dg);
         qu[j] = pack8<T>(du);
@@ -530,20 +651,45 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, uint32_t tad
   }
 }
 
+// The watcher role (warp 18, all lanes): for every tile of this CTA, wait until the MMA
+// issuer's commit has marked the accumulator full, publish the verdict and release the
+// epilogue warps from their named barrier. It arrives on the barrier whatever the
+// outcome, so the epilogue warps always wake up, read the same verdict and leave together.
+__device__ __forceinline__ void watcher_role(const GemmArgs& args, int lane, int first_tile,
+                                             int tile_stride, int total_tiles, uint32_t tfull0,
+                                             volatile int* epi_go, int* abort_flag) {
+  volatile int* abortp = abort_flag;
+  int local = 0;
+  for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
+    const int acc = local & 1;
+    const bool ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane);
+    tc_fence_after_sync();
+    if (lane == 0) {
+      epi_go[acc] = ok ? 1 : 0;
+      if (!ok) {
+        *abort_flag = 1;
+        atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
+      }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    named_bar_arrive(EPI_BAR_ID0 + acc, EPI_BAR_THREADS);
+    if (!ok) break;
+  }
+}
+
 // The epilogue role of one warp for all tiles of its CTA (or CTA pair).
 //   TILE_M     rows per tile: 128, or 256 for a CTA pair (row_off = cluster rank * 128)
-//   tfull0 / tempty0   shared::cta addresses of tfull[0] / tempty[0] ([1] is 8 bytes on)
+//   tempty0    shared::cta address of tempty[0] ([1] is 8 bytes on)
 //   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
-//   epi_smem   this CTA's epilogue staging area (two blocks per epilogue warp)
+//   epi_smem   this CTA's epilogue staging area
 template <int BN, int EPI, typename T, int TILE_M, bool REMOTE>
-__device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, int lane,
-                                              int first_tile, int tile_stride, int total_tiles,
-                                              int m_tiles, int n_tiles, int row_off,
-                                              uint32_t tmem_base, uint32_t tfull0,
-                                              uint32_t tempty0, uint32_t epi_smem,
-                                              int* abort_flag) {
+__device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMaps& maps, int warp,
+                                              int lane, int first_tile, int tile_stride,
+                                              int total_tiles, int m_tiles, int n_tiles, int row_off,
+                                              uint32_t tmem_base, uint32_t tempty0, uint32_t epi_smem,
+                                              volatile int* epi_go) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-  volatile int* abortp = abort_flag;
   const int ew = warp - 2;       // epilogue warp index 0..15
   const int quarter = warp & 3;  // TMEM lanes this warp may read
   const int col_part = ew >> 2;
@@ -552,23 +698,23 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, in
   const T* const bias1 = static_cast<const T*>(args.bias1);
   const bool drop_on = args.drop.thresh != 0u;
   const BlockView bv(lane);
-  const uint32_t stage = epi_smem + ew * (2 * BLK_BYTES);
-  bool ok = true;
+  const uint32_t stage = epi_smem + ew * (EPI == EPI_DHIDDEN ? 2 * BLK_BYTES : STORE_STAGE_BYTES);
   int local = 0;
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
     const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
     const int acc = local & 1;
-    ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane);
-    if (!ok) break;
+    __syncwarp();
+    named_bar_sync(EPI_BAR_ID0 + acc, EPI_BAR_THREADS);  // asleep until the watcher arrives
+    if (epi_go[acc] == 0) break;                         // the same verdict for all sixteen warps
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + acc * BN + lane_addr;
     const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
     if (EPI != EPI_STORE && args.act == ACT_SILU)
-      epilogue_tile<BN, EPI, T, ACT_SILU>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
-                                bias0, bias1, drop_on);
+      epilogue_tile<BN, EPI, T, ACT_SILU>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
+                                          stage, bias0, bias1, drop_on);
     else
-      epilogue_tile<BN, EPI, T, -1>(args, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv, stage,
-                                bias0, bias1, drop_on);
+      epilogue_tile<BN, EPI, T, -1>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
+                                    stage, bias0, bias1, drop_on);
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
     // semantics; no fence is placed here on purpose, since a fence would also wait for
@@ -579,10 +725,8 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, int warp, in
       else mbar_arrive(tempty0 + 8u * acc);
     }
   }
-  if (!ok && lane == 0) {
-    *abort_flag = 1;
-    atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_EPILOGUE);
-  }
+  // Shared memory must outlive the TMA stores that still read it.
+  if (EPI != EPI_DHIDDEN && lane == 0) bulk_wait_group_read<0>();
 }
 
 // ------------------------------------------------------------------ kernel --
@@ -591,7 +735,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
                     const __grid_constant__ CUtensorMap tmA1,
                     const __grid_constant__ CUtensorMap tmB0,
-                    const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmB1,
+                    const __grid_constant__ CUtensorMap tmO0,
+                    const __grid_constant__ CUtensorMap tmO1,
+                    const __grid_constant__ CUtensorMap tmO2, const GemmArgs args) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N range for M = 128");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 64 == 0, "MN-major B arrives in 64-column boxes");
@@ -610,6 +757,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  __shared__ volatile int epi_go[2];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -628,6 +776,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    epi_go[0] = epi_go[1] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -745,11 +894,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
         atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_MMA);
       }
     }
+  } else if (warp == WATCHER_WARP) {
+    watcher_role(args, lane, blockIdx.x, gridDim.x, total_tiles, tfull_bar(0), epi_go, &abort_flag);
   } else {
     // ------------------------------------------------------------ epilogue --
-    epilogue_role<BN, EPI, T, BM, false>(args, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
-                                         n_tiles, 0, tmem_base, tfull_bar(0), tempty_bar(0),
-                                         smem_base + STAGES * STAGE_BYTES, &abort_flag);
+    const OutMaps maps{&tmO0, &tmO1, &tmO2};
+    epilogue_role<BN, EPI, T, BM, false>(args, maps, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
+                                         n_tiles, 0, tmem_base, tempty_bar(0),
+                                         smem_base + STAGES * STAGE_BYTES, epi_go);
   }
 
   tc_fence_before_sync();
@@ -777,17 +929,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 //   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
 //              both copies at once.
 //   tempty[a]  lives in the leader, 32 arrivals: the 16 epilogue warps of each CTA.
-template <int BN, int STAGES>
-constexpr size_t gemm_pair_smem_bytes() {
-  return static_cast<size_t>(STAGES) * (BM * 128 + (BN / 2) * 128) + STAGING_BYTES + 1024;
-}
-
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
                          const __grid_constant__ CUtensorMap tmA1,
                          const __grid_constant__ CUtensorMap tmB0,
-                         const __grid_constant__ CUtensorMap tmB1, const GemmArgs args) {
+                         const __grid_constant__ CUtensorMap tmB1,
+                         const __grid_constant__ CUtensorMap tmO0,
+                         const __grid_constant__ CUtensorMap tmO1,
+                         const __grid_constant__ CUtensorMap tmO2, const GemmArgs args) {
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tcgen05 N range for M = 256");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
@@ -805,6 +955,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
+  __shared__ volatile int epi_go[2];
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_u32(bars);
@@ -826,6 +977,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
+    epi_go[0] = epi_go[1] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -945,11 +1097,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
         atomicCAS(args.status, 0, GMLP_DEV_TIMEOUT_MMA);
       }
     }
+  } else if (warp == WATCHER_WARP) {
+    watcher_role(args, lane, pair, num_pairs, total_tiles, tfull_bar(0), epi_go, &abort_flag);
   } else {
     // ------------------------------------------------------------ epilogue --
-    epilogue_role<BN, EPI, T, PAIR_M, true>(args, warp, lane, pair, num_pairs, total_tiles, m_tiles,
-                                            n_tiles, static_cast<int>(rank) * BM, tmem_base, tfull_bar(0),
-                                            tempty_bar(0), smem_base + STAGES * STAGE_BYTES, &abort_flag);
+    const OutMaps maps{&tmO0, &tmO1, &tmO2};
+    epilogue_role<BN, EPI, T, PAIR_M, true>(args, maps, warp, lane, pair, num_pairs, total_tiles, m_tiles,
+                                            n_tiles, static_cast<int>(rank) * BM, tmem_base, tempty_bar(0),
+                                            smem_base + STAGES * STAGE_BYTES, epi_go);
   }
 
   // Neither CTA may exit (or free TMEM) while its peer can still read its shared

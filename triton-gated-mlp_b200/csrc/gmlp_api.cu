@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -31,7 +32,7 @@ static int fail(int code, const char* fmt, ...) {
 __device__ int g_dev_status;
 
 struct DeviceInfo {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   int sm_count = 0;
   int cc_major = 0;
   int* status_ptr = nullptr;
@@ -55,9 +56,13 @@ static int device_info(const DeviceInfo** out) {
   // right device selected but no driver context, which tensor-map encoding needs.
   e = cudaSetDevice(dev);
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "cudaSetDevice: %s", cudaGetErrorString(e));
-  std::lock_guard<std::mutex> lk(g_mu);
   DeviceInfo& d = g_dev[dev];
-  if (!d.ready) {
+  if (d.ready.load(std::memory_order_acquire)) {
+    *out = &d;
+    return GMLP_OK;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!d.ready.load(std::memory_order_relaxed)) {
     cudaDeviceProp prop;
     e = cudaGetDeviceProperties(&prop, dev);
     if (e != cudaSuccess)
@@ -80,26 +85,71 @@ static int device_info(const DeviceInfo** out) {
         return fail(GMLP_ERR_LAUNCH, "cuTensorMapEncodeTiled entry point not available");
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    d.ready = true;
+    d.ready.store(true, std::memory_order_release);
   }
   *out = &d;
   return GMLP_OK;
 }
 
 // ------------------------------------------------------------- tensor maps --
-// 2-D row-major matrix [outer, inner] of 16-bit elements, 128-byte swizzle,
-// out-of-bounds elements read as zero.
+// Encoded maps are kept in a small per-thread cache keyed by everything that goes
+// into the encoding: a training loop presents the same (pointer, shape) pairs step
+// after step (weights always, activations whenever the allocator hands the same
+// blocks back), and cuTensorMapEncodeTiled is a driver call of about a microsecond.
+// A map holds no reference to the memory it describes, so a stale entry whose key
+// matches again is exactly the map a fresh encoding would give. Per thread: no lock,
+// and calls from different host threads never share an entry.
+struct MapKey {
+  const void* base;
+  int64_t inner, outer, pitch;
+  uint32_t box_inner, box_outer;
+  int32_t dtype, swizzle;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch &&
+           box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype &&
+           swizzle == o.swizzle;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int MAP_CACHE_SLOTS = 256;
+static thread_local MapSlot g_map_cache[MAP_CACHE_SLOTS];
+
+static uint32_t map_hash(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.inner) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.outer) * 0x165667B19E3779F9ull;
+  h ^= (static_cast<uint64_t>(k.box_inner) << 40) ^ (static_cast<uint64_t>(k.box_outer) << 24) ^
+       (static_cast<uint64_t>(k.swizzle) << 8) ^ static_cast<uint64_t>(k.dtype) ^
+       static_cast<uint64_t>(k.pitch) * 0x27D4EB2F165667C5ull;
+  return static_cast<uint32_t>(h >> 40) % MAP_CACHE_SLOTS;
+}
+
+// 2-D row-major matrix [outer, inner] of 16-bit elements, swizzled rows of
+// `swizzle_bytes` (32 / 64 / 128), out-of-bounds elements read as zero and are not
+// written by stores.
 static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
-                      int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype) {
+                      int64_t pitch_elems, uint32_t box_inner, uint32_t box_outer, int dtype,
+                      int swizzle_bytes = 128) {
+  const MapKey key{base, inner, outer, pitch_elems, box_inner, box_outer, dtype, swizzle_bytes};
+  MapSlot& slot = g_map_cache[map_hash(key)];
+  if (slot.used && slot.key == key) {
+    *m = slot.map;
+    return GMLP_OK;
+  }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt =
       dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapSwizzle sw = swizzle_bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
+                                : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                      : CU_TENSOR_MAP_SWIZZLE_128B;
   const CUresult r = g_encode(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
@@ -107,6 +157,9 @@ static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t o
                 "cuTensorMapEncodeTiled failed (%d) for base=%p inner=%lld outer=%lld pitch=%lld",
                 static_cast<int>(r), base, static_cast<long long>(inner),
                 static_cast<long long>(outer), static_cast<long long>(pitch_elems));
+  slot.key = key;
+  slot.map = *m;
+  slot.used = true;
   return GMLP_OK;
 }
 
@@ -145,29 +198,66 @@ struct Epilogue {
   DropoutParams drop = {};
 };
 
-// 0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA-pair kernel.
-static int g_pair_mode = 0;
-// Row tiles per raster group; 0 = the built-in default.
-static int g_group_m = 0;
-// CTAs the persistent GEMM grids may occupy; 0 = every SM. Lowered by a caller that
-// runs a collective's kernels beside the GEMMs and has to leave them SMs to land on.
-static int g_sm_limit = 0;
-static int64_t gemm_cta_budget(int sm_count) {
-  int64_t b = (g_sm_limit > 0 && g_sm_limit < sm_count) ? g_sm_limit : sm_count;
+// Process-wide DEFAULTS of the three tuning knobs (set by gmlp_set_*). A call that
+// carries its own values in gmlp_problem_t.tuning does not read them, so two modules
+// (or two host threads, or a backward pass beside a forward pass) never change each
+// other's grids through these.
+//   pair mode   0 = choose per problem, 1 = always the single-CTA kernel, 2 = always the CTA pair
+//   group_m     row tiles per raster group; 0 = built-in rule
+//   sm_limit    CTAs a persistent GEMM grid may occupy; 0 = every SM
+static std::atomic<int> g_pair_mode{0};
+static std::atomic<int> g_group_m{0};
+static std::atomic<int> g_sm_limit{0};
+
+struct Tuning {
+  int pair_mode, group_m, sm_limit;
+};
+// Field layout of the per-call word: see GMLP_TUNE_* in gmlp.h.
+static Tuning resolve_tuning(uint32_t word) {
+  Tuning t;
+  t.pair_mode = static_cast<int>(word & 3u);
+  t.group_m = static_cast<int>((word >> 2) & 0xFFFu);
+  t.sm_limit = static_cast<int>((word >> 14) & 0xFFFu);
+  if (t.pair_mode == 0 || t.pair_mode == 3) t.pair_mode = g_pair_mode.load(std::memory_order_relaxed);
+  if (t.group_m == 0) t.group_m = g_group_m.load(std::memory_order_relaxed);
+  if (t.sm_limit == 0) t.sm_limit = g_sm_limit.load(std::memory_order_relaxed);
+  return t;
+}
+static int64_t gemm_cta_budget(int sm_count, int sm_limit) {
+  int64_t b = (sm_limit > 0 && sm_limit < sm_count) ? sm_limit : sm_count;
   return b < 2 ? 2 : b;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of
+// before every launch.
+template <typename K>
+static int ensure_smem_attr(K kfn, size_t smem, std::atomic<uint64_t>& done) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const uint64_t bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return GMLP_OK;
+  const cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+  if (e != cudaSuccess)
+    return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  done.fetch_or(bit, std::memory_order_release);
+  return GMLP_OK;
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
 static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
                          const Operand& a0, const Operand* a1, const Operand& b0,
                          const Operand* b1, int64_t k1, int batches, const Epilogue& ep,
-                         cudaStream_t stream) {
+                         uint32_t tuning_word, cudaStream_t stream) {
+  const Tuning tune = resolve_tuning(tuning_word);
   // The CTA-pair kernel works on 256-row tiles; with a single row tile there is
   // nothing for the second CTA to do.
-  const bool pair = g_pair_mode == 2 || (g_pair_mode == 0 && M > BM);
-  // Shared memory: the operand ring plus 32 KB of staging blocks for the epilogue warps.
-  constexpr int STAGES = 4;
-  constexpr int PAIR_STAGES = 6;
+  const bool pair = tune.pair_mode == 2 || (tune.pair_mode == 0 && M > BM);
+  // Shared memory: the operand ring, as deep as fits beside the epilogue's staging area.
+  constexpr int B_ROWS_SINGLE = BN, B_ROWS_PAIR = BN / 2;  // rows of B a CTA stages per block
+  constexpr int STAGES = gemm_stages<B_ROWS_SINGLE, EPI>();
+  constexpr int PAIR_STAGES = gemm_stages<B_ROWS_PAIR, EPI>();
+  static_assert(STAGES >= 3 && PAIR_STAGES >= 4, "operand ring too shallow");
   const uint32_t b_rows = pair ? BN / 2 : ((EPI == EPI_SWIGLU) ? BN / 2 : BN);
   CUtensorMap mA0, mA1, mB0, mB1;
   int rc;
@@ -185,6 +275,24 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   }
   if (!ep.out0 || !aligned16(ep.out0) || (ep.ld_out % 8) != 0)
     return fail(GMLP_ERR_ALIGN, "output base / pitch not 16-byte aligned");
+  // Output matrices as the epilogue's TMA stores see them: [32 rows x 64 columns] blocks
+  // (128-byte rows) for the plain store, [32 x 32] (64-byte rows) for the gate/up kernel.
+  // The dH epilogue stores through the load/store unit and takes no maps.
+  CUtensorMap mO0 = mA0, mO1 = mA0, mO2 = mA0;
+  if (EPI == EPI_STORE) {
+    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 64, 32, dtype, 128))) return rc;
+    if (batches == 2) {
+      if (!ep.out1 || !aligned16(ep.out1))
+        return fail(GMLP_ERR_ALIGN, "second output base not 16-byte aligned");
+      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 64, 32, dtype, 128))) return rc;
+    }
+  } else if (EPI == EPI_SWIGLU) {
+    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
+    if (ep.out1) {
+      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
+      if ((rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
+    }
+  }
   GemmArgs args;
   memset(&args, 0, sizeof(args));
   args.M = static_cast<int>(M);
@@ -214,32 +322,27 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   if (tiles <= 0 || tiles > 0x7fffffffLL) return fail(GMLP_ERR_SHAPE, "tile count out of range");
   // Raster groups: a group of row tiles sweeps all column tiles, so the tiles in
   // flight at any time (one per SM or SM pair) share a small set of A and B tiles
-  // in L2. 4096 rows per group: on this power-capped part the group size shows up
-  // as clock (DRAM and L2 traffic cost power): in a seconds-long run at M=32768,
-  // K=8192, N=28672 the gate/up kernel held 1057 MHz with 16 row tiles per group
-  // against 1027 MHz with 8 and 922 MHz with 1.
-  args.group_m = g_group_m > 0 ? g_group_m : (pair ? 16 : 32);
+  // in L2, and the group's rows of A stay resident while B streams past once per group.
+  args.group_m = tune.group_m > 0 ? tune.group_m : (pair ? 16 : 32);
   cudaError_t e;
   if (pair) {
-    const int64_t max_pairs = gemm_cta_budget(dev->sm_count) / 2;
+    const int64_t max_pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-    constexpr size_t smem = gemm_pair_smem_bytes<BN, PAIR_STAGES>();
+    constexpr size_t smem = gemm_smem_bytes<B_ROWS_PAIR, EPI, PAIR_STAGES>();
+    static_assert(smem + 512 <= SMEM_LIMIT, "pair kernel exceeds the shared memory of an SM");
     auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES>;
-    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
-    if (e != cudaSuccess)
-      return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+    static std::atomic<uint64_t> attr_done{0};
+    if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, args);
   } else {
-    const int64_t budget = gemm_cta_budget(dev->sm_count);
+    const int64_t budget = gemm_cta_budget(dev->sm_count, tune.sm_limit);
     const int grid = static_cast<int>(tiles < budget ? tiles : budget);
-    constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
+    constexpr size_t smem = gemm_smem_bytes<B_ROWS_SINGLE, EPI, STAGES>();
+    static_assert(smem + 512 <= SMEM_LIMIT, "kernel exceeds the shared memory of an SM");
     auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
-    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem));
-    if (e != cudaSuccess)
-      return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, args);
+    static std::atomic<uint64_t> attr_done{0};
+    if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
+    kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, args);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
@@ -249,12 +352,12 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
 template <int BN, bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, const Operand& a0,
                        const Operand* a1, const Operand& b0, const Operand* b1, int64_t k1,
-                       int batches, const Epilogue& ep, cudaStream_t stream) {
+                       int batches, const Epilogue& ep, uint32_t tuning_word, cudaStream_t stream) {
   if (dtype == GMLP_BF16)
     return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1, k1,
-                                                             batches, ep, stream);
+                                                             batches, ep, tuning_word, stream);
   return launch_gemm_t<BN, A_MN, B_MN, EPI, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
-                                                    ep, stream);
+                                                    ep, tuning_word, stream);
 }
 
 static int check_problem(const gmlp_problem_t* p) {
@@ -317,23 +420,23 @@ using namespace gmlp;
 
 extern "C" {
 
-int gmlp_version(void) { return 101; }
+int gmlp_version(void) { return 200; }
 
 int gmlp_set_cta_pair_mode(int mode) {
-  const int prev = g_pair_mode;
-  if (mode >= 0 && mode <= 2) g_pair_mode = mode;
+  const int prev = g_pair_mode.load();
+  if (mode >= 0 && mode <= 2) g_pair_mode.store(mode);
   return prev;
 }
 
 int gmlp_set_sm_limit(int sms) {
-  const int prev = g_sm_limit;
-  if (sms >= 0 && sms <= 4096) g_sm_limit = sms;
+  const int prev = g_sm_limit.load();
+  if (sms >= 0 && sms <= 4095) g_sm_limit.store(sms);
   return prev;
 }
 
 int gmlp_set_raster_group(int row_tiles) {
-  const int prev = g_group_m;
-  if (row_tiles >= 0 && row_tiles <= 4096) g_group_m = row_tiles;
+  const int prev = g_group_m.load();
+  if (row_tiles >= 0 && row_tiles <= 4095) g_group_m.store(row_tiles);
   return prev;
 }
 
@@ -384,7 +487,7 @@ int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   ep.drop = make_dropout(p);
   ep.act = p->act;
   return launch_gemm<256, false, false, EPI_SWIGLU>(dev, p->dtype, p->M, p->N, a, nullptr, bg, &bu,
-                                                    0, 1, ep, static_cast<cudaStream_t>(stream));
+                                                    0, 1, ep, p->tuning, static_cast<cudaStream_t>(stream));
 }
 
 int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
@@ -405,7 +508,7 @@ int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
   ep.ld_out = p->K;
   ep.ld_in = p->K;
   return launch_gemm<256, false, false, EPI_STORE>(dev, p->dtype, p->M, p->K, a, nullptr, b,
-                                                   nullptr, 0, 1, ep,
+                                                   nullptr, 0, 1, ep, p->tuning,
                                                    static_cast<cudaStream_t>(stream));
 }
 
@@ -429,7 +532,7 @@ int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down
   ep.drop = make_dropout(p);
   ep.act = p->act;
   return launch_gemm<256, false, true, EPI_DHIDDEN>(dev, p->dtype, p->M, p->N, a, nullptr, b,
-                                                    nullptr, 0, 1, ep,
+                                                    nullptr, 0, 1, ep, p->tuning,
                                                     static_cast<cudaStream_t>(stream));
 }
 
@@ -450,7 +553,8 @@ int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
   ep.out0 = dx;
   ep.ld_out = p->K;
   return launch_gemm<256, false, true, EPI_STORE>(dev, p->dtype, p->M, p->K, a0, &a1, b0, &b1,
-                                                  p->N, 1, ep, static_cast<cudaStream_t>(stream));
+                                                  p->N, 1, ep, p->tuning,
+                                                  static_cast<cudaStream_t>(stream));
 }
 
 int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
@@ -470,7 +574,7 @@ int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void*
   ep.out1 = dw_up;
   ep.ld_out = p->K;
   return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr, 0,
-                                                 2, ep, static_cast<cudaStream_t>(stream));
+                                                 2, ep, p->tuning, static_cast<cudaStream_t>(stream));
 }
 
 int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
@@ -487,7 +591,7 @@ int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, voi
   ep.out0 = dw_down;
   ep.ld_out = p->N;
   return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->K, p->N, a, nullptr, b, nullptr,
-                                                 0, 1, ep, static_cast<cudaStream_t>(stream));
+                                                 0, 1, ep, p->tuning, static_cast<cudaStream_t>(stream));
 }
 
 int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const void* u,
@@ -538,42 +642,40 @@ int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream) {
   return GMLP_OK;
 }
 
+// Row blocks of the column-sum kernels. The target is a fixed number of thread blocks
+// (a few per SM on any sm_100 part) rather than a multiple of the device's SM count, so
+// that the scratch size is a function of the shape alone and can be computed without a
+// device (gmlp_colsum_scratch_bytes takes none).
+constexpr int64_t COLSUM_TARGET_BLOCKS = 592;
 static int colsum_row_blocks(int64_t rows, int64_t cols) {
   const int64_t col_blocks = (cols + COLSUM_COLS - 1) / COLSUM_COLS;
-  int64_t rb = (148 * 4 + col_blocks - 1) / col_blocks;  // about four blocks per SM
-  const int64_t max_rb = (rows + 63) / 64;               // at least 64 rows per block
+  int64_t rb = (COLSUM_TARGET_BLOCKS + col_blocks - 1) / col_blocks;
+  const int64_t max_rb = (rows + 63) / 64;  // at least 64 rows per block
   if (rb > max_rb) rb = max_rb;
   if (rb < 1) rb = 1;
   return static_cast<int>(rb);
 }
 
-size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols) {
-  if (rows <= 0 || cols <= 0) return 0;
-  return static_cast<size_t>(colsum_row_blocks(rows, cols)) * static_cast<size_t>(cols) *
-         sizeof(float);
-}
-
-int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
-                void* scratch, size_t scratch_bytes, void* dst, void* stream) {
+static int colsum_check(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                        const void* dst) {
   if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
     return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
   if (rows <= 0 || cols <= 0 || (cols % 8) != 0 || (ld % 8) != 0 || ld < cols)
     return fail(GMLP_ERR_SHAPE, "colsum needs rows > 0, cols and ld multiples of 8, ld >= cols");
-  if (!src || !dst || !scratch) return fail(GMLP_ERR_ARG, "NULL pointer argument");
-  if (!aligned16(src) || !aligned16(scratch))
-    return fail(GMLP_ERR_ALIGN, "src / scratch must be 16-byte aligned");
-  if (scratch_bytes < gmlp_colsum_scratch_bytes(rows, cols))
-    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes,
-                gmlp_colsum_scratch_bytes(rows, cols));
-  const DeviceInfo* dev;
-  int rc;
-  if ((rc = device_info(&dev))) return rc;
+  if (!src || !dst) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(src)) return fail(GMLP_ERR_ALIGN, "src must be 16-byte aligned");
+  return GMLP_OK;
+}
+
+// Both passes of a column sum with the fp32 partial sums in `part` (device memory of at
+// least gmlp_colsum_scratch_bytes(rows, cols) bytes, wherever it comes from). Pass 1
+// writes every partial sum that pass 2 reads, so `part` needs no clearing.
+static int colsum_launch(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                         float* part, void* dst, cudaStream_t st) {
   const int rb = colsum_row_blocks(rows, cols);
   const long long rows_per_block = (rows + rb - 1) / rb;
   const dim3 grid(static_cast<unsigned>((cols + COLSUM_COLS - 1) / COLSUM_COLS),
                   static_cast<unsigned>(rb));
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  float* part = static_cast<float*>(scratch);
   const unsigned fin_blocks = static_cast<unsigned>((cols + 255) / 256);
   if (dtype == GMLP_BF16) {
     colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
@@ -589,6 +691,27 @@ int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int6
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
   return GMLP_OK;
+}
+
+size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<size_t>(colsum_row_blocks(rows, cols)) * static_cast<size_t>(cols) *
+         sizeof(float);
+}
+
+int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
+                void* scratch, size_t scratch_bytes, void* dst, void* stream) {
+  int rc;
+  if ((rc = colsum_check(rows, cols, dtype, src, ld, dst))) return rc;
+  if (!scratch) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(scratch)) return fail(GMLP_ERR_ALIGN, "scratch must be 16-byte aligned");
+  if (scratch_bytes < gmlp_colsum_scratch_bytes(rows, cols))
+    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes,
+                gmlp_colsum_scratch_bytes(rows, cols));
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  return colsum_launch(rows, cols, dtype, src, ld, static_cast<float*>(scratch), dst,
+                       static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
@@ -757,15 +880,15 @@ int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!a_mn && !b_mn)
     return launch_gemm<256, false, false, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0,
-                                                     1, ep, st);
+                                                     1, ep, 0u, st);
   if (!a_mn && b_mn)
     return launch_gemm<256, false, true, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
-                                                    ep, st);
+                                                    ep, 0u, st);
   if (a_mn && b_mn)
     return launch_gemm<256, true, true, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
-                                                   ep, st);
+                                                   ep, 0u, st);
   return launch_gemm<256, true, false, EPI_STORE>(dev, dtype, M, N, a, nullptr, b, nullptr, 0, 1,
-                                                  ep, st);
+                                                  ep, 0u, st);
 }
 
 }  // extern "C"
@@ -783,12 +906,8 @@ static std::mutex g_colsum_static_mu;
 
 extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* src,
                                   int64_t ld, void* dst, void* stream) {
-  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
-    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
-  if (rows <= 0 || cols <= 0 || (cols % 8) != 0 || (ld % 8) != 0 || ld < cols)
-    return fail(GMLP_ERR_SHAPE, "colsum needs rows > 0, cols and ld multiples of 8, ld >= cols");
-  if (!src || !dst) return fail(GMLP_ERR_ARG, "NULL pointer argument");
-  if (!aligned16(src)) return fail(GMLP_ERR_ALIGN, "src must be 16-byte aligned");
+  int rc;
+  if ((rc = colsum_check(rows, cols, dtype, src, ld, dst))) return rc;
   const size_t need = gmlp_colsum_scratch_bytes(rows, cols);
   if (need > COLSUM_STATIC_BYTES)
     return fail(GMLP_ERR_SCRATCH,
@@ -797,7 +916,6 @@ extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, con
                 static_cast<long long>(rows), static_cast<long long>(cols), need,
                 static_cast<size_t>(COLSUM_STATIC_BYTES));
   const DeviceInfo* dev;
-  int rc;
   if ((rc = device_info(&dev))) return rc;
   int ordinal = 0;
   cudaError_t e = cudaGetDevice(&ordinal);
@@ -817,28 +935,9 @@ extern "C" int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, con
     }
     part = g_colsum_static_ptr[ordinal];
   }
-  // Pass 1 writes every partial sum that pass 2 reads, so nothing left in the array
-  // by an earlier call is ever read and nothing has to be cleared.
-  const int rb = colsum_row_blocks(rows, cols);
-  const long long rows_per_block = (rows + rb - 1) / rb;
-  const dim3 grid(static_cast<unsigned>((cols + COLSUM_COLS - 1) / COLSUM_COLS),
-                  static_cast<unsigned>(rb));
-  const unsigned fin_blocks = static_cast<unsigned>((cols + 255) / 256);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == GMLP_BF16) {
-    colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows_per_block, part);
-    colsum_final_kernel<__nv_bfloat16><<<fin_blocks, 256, 0, st>>>(
-        part, cols, rb, static_cast<__nv_bfloat16*>(dst));
-  } else {
-    colsum_partial_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), rows,
-                                                        cols, ld, rows_per_block, part);
-    colsum_final_kernel<__half><<<fin_blocks, 256, 0, st>>>(part, cols, rb,
-                                                            static_cast<__half*>(dst));
-  }
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
-  return GMLP_OK;
+  // Nothing left in the array by an earlier call is ever read (see colsum_launch), so
+  // nothing has to be cleared.
+  return colsum_launch(rows, cols, dtype, src, ld, part, dst, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------- peer memory + all-reduce --
@@ -951,9 +1050,8 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
   // Kernel and grid depend on n and world alone, so that every rank makes the same
   // choice and block b means the same slice everywhere. The two-shot form (each rank
   // reduces one slice and hands it round) moves world/2 times less data over NVLink but
-  // needs a second flag exchange. Measured at K=8192 (sum alone, one-shot / two-shot):
-  // 8 ranks 512 KB 18.8 / 21.9 us, 1 MB 24.5 / 22.7 us; 4 ranks 1 MB 16.3 / 19.6 us;
-  // 2 ranks 1 MB 11.0 / 17.1 us. So it is taken from 1 MB on with eight ranks only.
+  // needs a second flag exchange, which pays only for the largest messages on the
+  // largest groups: it is taken from PEER_TWO_SHOT_MIN_BYTES on with eight ranks.
   const bool big = g_two_shot_bytes > 0 ? n * 2 >= g_two_shot_bytes
                                         : (g_two_shot_bytes == 0 && world >= 8 && n * 2 >= PEER_TWO_SHOT_MIN_BYTES);
   const bool two_shot = big && (n % (8ll * world)) == 0;

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the gated-MLP kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no cluster multicast anywhere), tcgen05
+// mbarrier, TMA loads and stores (cp.async.bulk.tensor, no cluster multicast anywhere), tcgen05
 // MMA / TMEM allocation / TMEM loads, and the shared-memory matrix descriptors.
 //
 // Every wait in this file is bounded: a wait that does not complete within
@@ -120,6 +120,79 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
+}
+
+// 2-D tiled store, this CTA's shared memory -> global, as part of the calling thread's
+// current bulk async-group. Elements outside the tensor are not written. x is the
+// innermost coordinate; x * element size must be a multiple of 16 bytes and neither
+// coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Blocks until at most N of the calling thread's bulk groups still READ their
+// shared-memory source (the global writes may still be in flight).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------- named CTA barriers ----
+// Barrier 0 is __syncthreads(). A warp parked at bar.sync costs no issue slots, unlike
+// one that polls an mbarrier. `threads` counts whole warps (a multiple of 32).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Barrier plus vote: true for every participant if `pred` is true for any of them. All
+// participants get the same answer, so they can all take the same branch on it.
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %3, 0;\n"
+      "bar.red.or.pred q, %1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(r)
+      : "r"(id), "r"(threads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ------------------------------------------------------ packed fp32 pairs ----
+// sm_100 executes add / mul / fma on two fp32 values held in one 64-bit register at
+// the issue cost of one instruction.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
 }
 
 // ----------------------------------------------------------------- tcgen05 --

@@ -37,16 +37,21 @@ _ACT_MODULES = {
 
 
 class _SmLimit:
-    """Callable that keeps `comm_sms` SMs free of persistent GEMM CTAs (True) or gives them back (False)."""
+    """While switched on, GEMM launches that pass `limit.tuning` leave `comm_sms` SMs free of
+    persistent CTAs for a collective's kernels. The limit travels with each call
+    (gmlp_problem_t.tuning); nothing process-wide is touched, so other modules, devices and
+    host threads keep their full grids."""
 
     def __init__(self, device: torch.device, comm_sms: int):
         self.sms = max(2, torch.cuda.get_device_properties(device).multi_processor_count - max(0, int(comm_sms)))
         self.on = False
 
     def __call__(self, on: bool) -> None:
-        if on != self.on:
-            _lib.set_sm_limit(self.sms if on else 0)
-            self.on = on
+        self.on = bool(on)
+
+    @property
+    def tuning(self) -> int:
+        return _lib.tune_word(sm_limit=self.sms) if self.on else 0
 
 
 class FusedGatedMLPFunction(Function):
@@ -60,7 +65,8 @@ class FusedGatedMLPFunction(Function):
     def forward(ctx, x: Tensor, W_gate: Tensor, b_gate: Optional[Tensor], W_up: Tensor,
                 b_up: Optional[Tensor], W_down: Tensor, b_down: Optional[Tensor],
                 drop: Dropout, shard: Shard, tp_group, act: str = "silu",
-                residual: Optional[Tensor] = None, tp_chunk_rows=(0, 0), tp_comm_sms: int = 16) -> Tensor:
+                residual: Optional[Tensor] = None, tp_chunk_rows=(0, 0), tp_comm_sms: int = 16,
+                inplace_backward: bool = True) -> Tensor:
         tp_chunk_fwd, tp_chunk_bwd = tp_chunk_rows
         need_bwd = any(ctx.needs_input_grad)
         if need_bwd:
@@ -77,13 +83,10 @@ class FusedGatedMLPFunction(Function):
             # (NCCL, on its own stream) runs beside chunk i+1's GEMM.
             y = torch.empty((x.shape[0], W_down.shape[0]), dtype=x.dtype, device=x.device)
             limit = _SmLimit(x.device, tp_comm_sms)
-            try:
-                works = parallel.overlapped_all_reduce(
-                    y, lambda r0, r1: kernels.down_fwd(h[r0:r1], W_down, bias, None if res is None else res[r0:r1],
-                                                       out=y[r0:r1]),
-                    tp_group, tp_chunk_fwd, limit)
-            finally:
-                limit(False)
+            works = parallel.overlapped_all_reduce(
+                y, lambda r0, r1: kernels.down_fwd(h[r0:r1], W_down, bias, None if res is None else res[r0:r1],
+                                                   out=y[r0:r1], tuning=limit.tuning),
+                tp_group, tp_chunk_fwd, limit)
             parallel.wait_all(works)
         else:
             y = kernels.down_fwd(h, W_down, bias, res)
@@ -94,6 +97,7 @@ class FusedGatedMLPFunction(Function):
             ctx.drop, ctx.shard, ctx.tp_group, ctx.act = drop, shard, tp_group, act
             ctx.tp_chunk_rows, ctx.tp_comm_sms = tp_chunk_bwd, tp_comm_sms
             ctx.has_bias = (b_gate is not None, b_up is not None, b_down is not None)
+            ctx.inplace_backward, ctx.consumed = bool(inplace_backward), False
         return y
 
     @staticmethod
@@ -102,44 +106,54 @@ class FusedGatedMLPFunction(Function):
         need = ctx.needs_input_grad
         dy = dy.contiguous()
         dx = dW_gate = db_gate = dW_up = db_up = dW_down = db_down = None
-        limit, works = None, []
-        try:
-            need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
-            if need_hidden:
-                d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act)
-                if need[0]:
-                    if ctx.tp_group is not None and ctx.tp_chunk_rows > 0:
-                        # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
-                        dx = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
-                        limit = _SmLimit(x.device, ctx.tp_comm_sms)
-                        works = parallel.overlapped_all_reduce(
-                            dx, lambda r0, r1: kernels.bwd_dx(d_gate[r0:r1], d_up[r0:r1], W_gate, W_up, out=dx[r0:r1]),
-                            ctx.tp_group, ctx.tp_chunk_rows, limit)
-                        limit(True)
-                    else:
-                        dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
-                        if ctx.tp_group is not None:
-                            parallel.all_reduce_sum(dx, ctx.tp_group)
-                if need[1] or need[3]:
-                    dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
-                if need[2] and ctx.has_bias[0]:
-                    db_gate = kernels.colsum(d_gate)
-                if need[4] and ctx.has_bias[1]:
-                    db_up = kernels.colsum(d_up)
-            if need[5]:
-                dW_down = kernels.bwd_dw_down(dy, h)
-            if need[6] and ctx.has_bias[2]:
-                db_down = kernels.colsum(dy)
-        finally:
-            if limit is not None:
-                limit(False)
+        limit = _SmLimit(x.device, ctx.tp_comm_sms)
+        works = []
+        need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
+        if need_hidden:
+            if ctx.consumed:
+                raise RuntimeError(
+                    "FusedGatedMLP: this graph's saved gate/up pre-activations were overwritten by an earlier "
+                    "backward pass (inplace_backward=True writes d_gate / d_up over them). Set "
+                    "module.inplace_backward = False to run backward more than once over one forward.")
+            # d_gate / d_up land in the buffers G / U were saved in: two [M, N] allocations fewer.
+            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act,
+                                               inplace=ctx.inplace_backward)
+            ctx.consumed = ctx.inplace_backward
+            if need[0]:
+                if ctx.tp_group is not None and ctx.tp_chunk_rows > 0:
+                    # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
+                    dx = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+                    works = parallel.overlapped_all_reduce(
+                        dx, lambda r0, r1: kernels.bwd_dx(d_gate[r0:r1], d_up[r0:r1], W_gate, W_up, out=dx[r0:r1],
+                                                          tuning=limit.tuning),
+                        ctx.tp_group, ctx.tp_chunk_rows, limit)
+                    limit(True)
+                else:
+                    dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
+                    if ctx.tp_group is not None:
+                        parallel.all_reduce_sum(dx, ctx.tp_group)
+            if need[1] or need[3]:
+                dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x, tuning=limit.tuning)
+            if need[2] and ctx.has_bias[0]:
+                db_gate = kernels.colsum(d_gate)
+            if need[4] and ctx.has_bias[1]:
+                db_up = kernels.colsum(d_up)
+        if need[5]:
+            dW_down = kernels.bwd_dw_down(dy, h, tuning=limit.tuning)
+        if need[6] and ctx.has_bias[2]:
+            db_down = kernels.colsum(dy)
         parallel.wait_all(works)
         d_res = dy if (len(need) > 11 and need[11]) else None  # y = ... + residual
-        return dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res, None, None
+        return (dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res, None, None,
+                None)
 
 
 class FusedGatedMLP(nn.Module):
     """Gated MLP block; see the module docstring.
+
+    The kernels compute in bfloat16 or float16 with fp32 accumulation: cast the module
+    with .to(torch.bfloat16) or .to(torch.float16) (and move it to a CUDA device) before
+    the first forward; an fp32 module raises NotImplementedError, a CPU tensor GmlpError.
 
     Extra keyword-only arguments (all default to the single-GPU reference behaviour):
       parallel_mode  "none" | "token" | "tp". "token": this rank holds a slice of
@@ -150,17 +164,26 @@ class FusedGatedMLP(nn.Module):
                      down-projection partial sums are all-reduced over
                      `process_group`.
       process_group  torch.distributed group for "tp".
-    Attributes for "tp" at prefill / training sizes (set after construction):
-      tp_chunk_rows  0 (default): one all-reduce after the whole dx GEMM of the backward
-                     pass. > 0: that GEMM runs in chunks of this many token rows and
-                     each chunk's all-reduce overlaps the next chunk's GEMM, the last
-                     one the weight-gradient GEMMs (8 ranks, M=16384, K=8192, N=28672:
-                     fwd+bwd 8.6-8.7 -> 8.10 ms with 4096-row chunks).
+    Attributes (set after construction):
+      inplace_backward  True (default): the backward pass writes d_gate / d_up over the saved
+                     gate / up pre-activations instead of allocating two more [M, N]
+                     buffers. A second backward over the same forward (retain_graph=True)
+                     then raises; set False for that use.
+      tp_chunk_rows  "tp" at prefill / training sizes. 0 (default): one all-reduce after
+                     the whole dx GEMM of the backward pass. > 0: that GEMM runs in chunks
+                     of this many token rows and each chunk's all-reduce overlaps the next
+                     chunk's GEMM, the last one the weight-gradient GEMMs.
       tp_chunk_rows_fwd  the same for the down projection of the forward pass, where
-                     nothing follows the last chunk to hide its all-reduce behind (the
-                     same measurement: forward 3.04 -> 3.12 ms, so it is off by default).
+                     nothing follows the last chunk to hide its all-reduce behind (off by
+                     default).
       tp_comm_sms    SMs the persistent GEMM grids leave to the collective's kernels
                      while one is in flight (default 16).
+      peer_max_bytes largest partial output the "tp" decode path sums through peer memory
+                     (after enable_peer_allreduce()); larger ones go through NCCL.
+      check_status_every  0 (default): never read the device status word on the decode
+                     path. N > 0: every N-th "tp" decode call synchronises, reads it and
+                     raises if a peer wait ran out (the output of that call is then this
+                     rank's partial sum only).
       philox_seed    dropout seed; `philox_offset` advances by one per training
                      forward call.
     """
@@ -203,13 +226,13 @@ class FusedGatedMLP(nn.Module):
         self.philox_offset = 0
         self._decode_scratch = None
         self._peer = None
+        self.inplace_backward = True
         self.tp_chunk_rows = 0
         self.tp_chunk_rows_fwd = 0
         self.tp_comm_sms = 16
-        # Largest partial output (bytes) the decode path sums through peer memory; above it NCCL
-        # is used. Measured at K=8192 over 8 ranks, step with NCCL sum -> with peer sum:
-        # M=1 64.2 -> 46.5 us, M=8 66.4 -> 50.1, M=32 (512 KB) 70.1 -> 58.2, M=64 (1 MB) 75.7 -> 72.0.
         self.peer_max_bytes = 1024 * 1024
+        self.check_status_every = 0
+        self._decode_calls = 0
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -224,7 +247,9 @@ class FusedGatedMLP(nn.Module):
 
     def _decode_forward(self, x: Tensor, tp_group, residual: Optional[Tensor]) -> Tensor:
         """Inference with at most 64 tokens: the weight-streaming kernels (HBM-bound)."""
-        key = (x.device, x.dtype)
+        # A kernel that gave up a wait may have left counters in the scratch non-zero: a
+        # non-zero status read (anywhere in the process) starts a new scratch epoch.
+        key = (x.device, x.dtype, _lib.scratch_epoch())
         if self._decode_scratch is None or self._decode_scratch[0] != key:
             self._decode_scratch = (key, kernels.decode_scratch(
                 x.shape[0], self.hidden_size, self.intermediate_size, x.dtype, x.device))
@@ -236,11 +261,17 @@ class FusedGatedMLP(nn.Module):
         if tp_group is not None:
             if (self._peer is not None and self._peer.supports(y)
                     and y.numel() * y.element_size() <= self.peer_max_bytes):
-                # The partial outputs are summed through the peers' memory, in place. As an
-                # ordinary launch: as a programmatic dependent of the down projection the sum was
-                # no faster at 16-512 KB and 8 us slower at 1 MB (8 ranks), its blocks then sit on
-                # SMs the down projection's last CTAs still use.
+                # The partial outputs are summed through the peers' memory, in place, as an
+                # ordinary launch (as a programmatic dependent its blocks would occupy SMs that
+                # the down projection's last CTAs still need).
                 self._peer.all_reduce(y, out=y, dependent=False)
+                self._decode_calls += 1
+                if self.check_status_every > 0 and self._decode_calls % self.check_status_every == 0:
+                    code = _lib.status_read(x.device)
+                    if code != 0:
+                        raise _lib.GmlpError(
+                            f"device status {code}: a bounded wait ran out during tensor-parallel decode "
+                            "(4 = a peer's partial output never arrived); the last output is not the full sum")
             else:
                 parallel.all_reduce_sum(y, tp_group)
         return y
@@ -284,6 +315,6 @@ class FusedGatedMLP(nn.Module):
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
             self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group, self.act_fn, residual,
             (int(self.tp_chunk_rows_fwd), int(self.tp_chunk_rows)) if tp_group is not None else (0, 0),
-            int(self.tp_comm_sms),
+            int(self.tp_comm_sms), bool(self.inplace_backward),
         )
         return y.view(shapes) if len(shapes) > 2 else y

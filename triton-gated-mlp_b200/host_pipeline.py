@@ -9,10 +9,37 @@ device->host), so a stream of batches runs at the pace of the slowest of the thr
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional
 
 import torch
 from torch import Tensor
+
+
+def bind_host_thread_near(device_index: int) -> Optional[List[int]]:
+    """Restrict the calling process to the CPU cores the driver reports as closest to GPU
+    `device_index` (NVML's CPU affinity for the device: the cores of the NUMA node its PCIe
+    root hangs off), so that pinned buffers allocated afterwards land in that node's memory
+    and the copy threads run beside it. With several ranks on one host this keeps each
+    rank's host traffic on its own socket. Only the process's own affinity is changed; no
+    setting of the GPU. Returns the cores chosen, or None when NVML or the affinity call is
+    unavailable or reports nothing useful (the process then stays as it was)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(int(device_index))
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (ncpu + 63) // 64)
+        cores = [64 * i + b for i, wd in enumerate(words) for b in range(64) if (int(wd) >> b) & 1]
+        allowed = os.sched_getaffinity(0)
+        cores = sorted(c for c in cores if c in allowed)
+        if not cores or len(cores) == len(allowed):
+            return None
+        os.sched_setaffinity(0, cores)
+        return cores
+    except Exception:
+        return None
 
 
 class HostPipeline:
@@ -35,8 +62,19 @@ class HostPipeline:
         i = self._n % self.depth
         slot = self._slots[i]
         if slot is None or [t.shape for t in slot["dev_in"]] != [t.shape for t in host_inputs]:
+            # The device inputs belong to the copy stream: allocate them there, and when a
+            # slot is replaced (batch shape changed) let that stream wait for the run that
+            # may still read the old buffers before their memory can be handed out again.
+            with torch.cuda.stream(self.s_in):
+                if slot is not None and slot["used"]:
+                    self.s_in.wait_event(slot["run_done"])
+                    for t in slot["dev_in"]:
+                        t.record_stream(self.s_run)
+                dev_in = [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_inputs]
+            for t in dev_in:
+                t.record_stream(self.s_run)
             slot = {
-                "dev_in": [torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in host_inputs],
+                "dev_in": dev_in,
                 "in_done": torch.cuda.Event(), "run_done": torch.cuda.Event(), "out_done": torch.cuda.Event(),
                 "used": False,
             }

@@ -45,11 +45,13 @@ def act_code(act: str) -> int:
     return ACT_CODES[act]
 
 
-def _problem(M: int, K: int, N: int, dt: torch.dtype, drop: Dropout, shard: Shard, act: str = "silu") -> Problem:
+def _problem(M: int, K: int, N: int, dt: torch.dtype, drop: Dropout, shard: Shard, act: str = "silu",
+             tuning: int = 0) -> Problem:
     return Problem(
         M=M, K=K, N=N, dtype=dtype_code(dt), dropout_p=float(drop.p),
         seed=int(drop.seed) & 0xFFFFFFFFFFFFFFFF, offset=int(drop.offset) & 0xFFFFFFFFFFFFFFFF,
-        row0_global=shard.row0, col0_global=shard.col0, N_global=shard.n_global, act=act_code(act), reserved=0,
+        row0_global=shard.row0, col0_global=shard.col0, N_global=shard.n_global, act=act_code(act),
+        tuning=int(tuning),
     )
 
 
@@ -71,9 +73,10 @@ def _same_dtype(*ts: Tensor | None) -> torch.dtype:
 
 
 def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
-               drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False, act: str = "silu"):
+               drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False, act: str = "silu",
+               tuning: int = 0):
     """H = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)); with save=True also
-    returns the biased pre-activations (G, U)."""
+    returns the biased pre-activations (G, U). `tuning`: _lib.tune_word() for this launch."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up)
     dt = _same_dtype(x, w_gate, b_gate, w_up, b_up)
     x, w_gate, w_up, b_gate, b_up = _c(x), _c(w_gate), _c(w_up), _c(b_gate), _c(b_up)
@@ -83,7 +86,7 @@ def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     g = torch.empty((M, N), dtype=dt, device=dev) if save else None
     u = torch.empty((M, N), dtype=dt, device=dev) if save else None
     if M > 0:
-        prob = _problem(M, K, N, dt, drop, shard, act)
+        prob = _problem(M, K, N, dt, drop, shard, act, tuning)
         with torch.cuda.device(dev):
             check(load().gmlp_hidden_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up),
                                          ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
@@ -99,7 +102,7 @@ def _out_buffer(out: Tensor | None, shape, dt: torch.dtype, dev: torch.device) -
 
 
 def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor | None = None,
-             out: Tensor | None = None) -> Tensor:
+             out: Tensor | None = None, tuning: int = 0) -> Tensor:
     """y = h W_down^T (+ b_down) (+ residual), written into `out` when given."""
     dev = require_cuda(h, w_down, b_down, residual)
     dt = _same_dtype(h, w_down, b_down, residual)
@@ -108,7 +111,7 @@ def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor 
     K = w_down.shape[0]
     y = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
-        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
         with torch.cuda.device(dev):
             check(load().gmlp_down_fwd(C.byref(prob), ptr(h), ptr(w_down), ptr(b_down), ptr(residual),
                                        ptr(y), stream_of(h)))
@@ -116,17 +119,22 @@ def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor 
 
 
 def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT,
-                shard: Shard = NO_SHARD, act: str = "silu"):
-    """(d_gate, d_up) from dy through W_down and the SiLU/multiply derivative."""
+                shard: Shard = NO_SHARD, act: str = "silu", inplace: bool = False, tuning: int = 0):
+    """(d_gate, d_up) from dy through W_down and the activation/multiply derivative.
+
+    inplace=True writes d_gate over g and d_up over u (both must be contiguous) and returns
+    those tensors: two [M, N] buffers fewer, and the pre-activations are gone afterwards."""
     dev = require_cuda(dy, w_down, g, u)
     dt = _same_dtype(dy, w_down, g, u)
+    if inplace and not (g.is_contiguous() and u.is_contiguous()):
+        raise ValueError("inplace=True needs contiguous g and u")
     dy, w_down, g, u = _c(dy), _c(w_down), _c(g), _c(u)
     M, K = dy.shape
     N = w_down.shape[1]
-    d_gate = torch.empty((M, N), dtype=dt, device=dev)
-    d_up = torch.empty((M, N), dtype=dt, device=dev)
+    d_gate = g if inplace else torch.empty((M, N), dtype=dt, device=dev)
+    d_up = u if inplace else torch.empty((M, N), dtype=dt, device=dev)
     if M > 0:
-        prob = _problem(M, K, N, dt, drop, shard, act)
+        prob = _problem(M, K, N, dt, drop, shard, act, tuning)
         with torch.cuda.device(dev):
             check(load().gmlp_bwd_dhidden(C.byref(prob), ptr(dy), ptr(w_down), ptr(g), ptr(u),
                                           ptr(d_gate), ptr(d_up), stream_of(dy)))
@@ -150,7 +158,8 @@ def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard
     return d_gate, d_up
 
 
-def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tensor | None = None) -> Tensor:
+def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tensor | None = None,
+           tuning: int = 0) -> Tensor:
     """dx = d_gate W_gate + d_up W_up, written into `out` when given."""
     dev = require_cuda(d_gate, d_up, w_gate, w_up)
     dt = _same_dtype(d_gate, d_up, w_gate, w_up)
@@ -159,14 +168,14 @@ def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tens
     K = w_gate.shape[1]
     dx = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
-        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+        prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
         with torch.cuda.device(dev):
             check(load().gmlp_bwd_dx(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(w_gate), ptr(w_up),
                                      ptr(dx), stream_of(d_gate)))
     return dx
 
 
-def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor):
+def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor, tuning: int = 0):
     """(dW_gate, dW_up) = (d_gate^T x, d_up^T x)."""
     dev = require_cuda(d_gate, d_up, x)
     dt = _same_dtype(d_gate, d_up, x)
@@ -177,14 +186,14 @@ def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor):
         return (torch.zeros((N, K), dtype=dt, device=dev), torch.zeros((N, K), dtype=dt, device=dev))
     dw_gate = torch.empty((N, K), dtype=dt, device=dev)
     dw_up = torch.empty((N, K), dtype=dt, device=dev)
-    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
     with torch.cuda.device(dev):
         check(load().gmlp_bwd_dw_gate_up(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(x), ptr(dw_gate),
                                          ptr(dw_up), stream_of(x)))
     return dw_gate, dw_up
 
 
-def bwd_dw_down(dy: Tensor, h: Tensor) -> Tensor:
+def bwd_dw_down(dy: Tensor, h: Tensor, tuning: int = 0) -> Tensor:
     """dW_down = dy^T h."""
     dev = require_cuda(dy, h)
     dt = _same_dtype(dy, h)
@@ -194,7 +203,7 @@ def bwd_dw_down(dy: Tensor, h: Tensor) -> Tensor:
     if M == 0:
         return torch.zeros((K, N), dtype=dt, device=dev)
     dw = torch.empty((K, N), dtype=dt, device=dev)
-    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
     with torch.cuda.device(dev):
         check(load().gmlp_bwd_dw_down(C.byref(prob), ptr(dy), ptr(h), ptr(dw), stream_of(dy)))
     return dw
