@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(pkg):
 
 def test_version_and_error_string_need_no_gpu(pkg):
     lib = pkg._lib.load()
-    assert lib.gmlp_version() >= 100
+    assert lib.gmlp_version() >= 200   # 200: gmlp_problem_t.reserved became the per-call tuning word
     assert isinstance(lib.gmlp_last_error(), bytes)
 
 
@@ -39,7 +39,7 @@ def test_argument_checks_run_before_any_device_call(pkg):
     L = pkg._lib
     lib = L.load()
     ok = dict(M=4, K=64, N=64, dtype=0, dropout_p=0.0, seed=0, offset=0, row0_global=0, col0_global=0, N_global=0,
-              act=0, reserved=0)
+              act=0, tuning=0)
 
     def rc(**kw):
         p = L.Problem(**{**ok, **kw})

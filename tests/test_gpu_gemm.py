@@ -94,3 +94,41 @@ def test_output_slices_and_sm_limit(pkg, cuda_dev):
         K_.bwd_dx(dg, du, wg, wu, out=out[:128])          # wrong shape
     with pytest.raises(ValueError):
         K_.down_fwd(h, wd, bd, out=torch.empty((M, K), dtype=torch.float16, device=cuda_dev))
+
+
+def test_per_call_tuning_from_two_threads(pkg, cuda_dev):
+    """Two host threads launch GEMMs on two streams at once, one with a per-call tuning word (32 SMs, single-CTA
+    kernel, raster group 2), the other with the defaults. Both get the bits of an undisturbed call, and the
+    process-wide defaults never move: a module that limits its own grids does not change anybody else's."""
+    import threading
+
+    K_, L = pkg.ops.kernels, pkg._lib
+    lib = L.load()
+    g = torch.Generator(device="cpu").manual_seed(9)
+    M, K, N = 1024, 512, 768
+    h = (torch.randn((M, N), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    wd = (torch.randn((K, N), generator=g) * 0.1).to(torch.bfloat16).to(cuda_dev)
+    want = K_.down_fwd(h, wd, None)
+    torch.cuda.synchronize()
+    word = L.tune_word(pair_mode=1, raster_group=2, sm_limit=32)
+    before = (lib.gmlp_set_cta_pair_mode(-1), lib.gmlp_set_raster_group(-1), lib.gmlp_set_sm_limit(-1))
+    results, errors = {}, []
+
+    def work(name, tuning):
+        try:
+            with torch.cuda.stream(torch.cuda.Stream(cuda_dev)):
+                outs = [K_.down_fwd(h, wd, None, tuning=tuning) for _ in range(20)]
+                torch.cuda.current_stream(cuda_dev).synchronize()
+            results[name] = outs
+        except Exception as e:  # surfaced in the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=("tuned", word)), threading.Thread(target=work, args=("plain", 0))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for outs in results.values():
+        assert all(torch.equal(o, want) for o in outs)
+    assert (lib.gmlp_set_cta_pair_mode(-1), lib.gmlp_set_raster_group(-1), lib.gmlp_set_sm_limit(-1)) == before

@@ -135,3 +135,35 @@ def test_fused_residual(pkg, cuda_dev, M):
     assert torch.equal(r.grad, case.dy.to(cuda_dev))
     with pytest.raises(ValueError):
         m(x, residual=r[:, :128])
+
+
+def test_inplace_backward_reuses_saved_buffers_and_guards_a_second_pass(pkg, cuda_dev):
+    """By default d_gate / d_up are written over the saved gate / up pre-activations: same gradients as the
+    out-of-place form, less peak memory, and a second backward over the same forward (which would read
+    overwritten activations) raises instead of returning wrong numbers. With inplace_backward=False the
+    graph can be walked twice."""
+    case = orc.make_case(512, 256, 1024, True, torch.bfloat16, seed=21, w_std=0.03, dy_std=0.05)
+    dy = case.dy.to(cuda_dev)
+
+    def grads(inplace, twice=False):
+        m = build_module(pkg, case, torch.bfloat16, cuda_dev)
+        m.inplace_backward = inplace
+        x = case.x.to(cuda_dev).requires_grad_(True)
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats(cuda_dev)
+        base = torch.cuda.memory_allocated(cuda_dev)
+        y = m(x)
+        y.backward(dy, retain_graph=twice)
+        peak = torch.cuda.max_memory_allocated(cuda_dev) - base
+        out = {"dx": x.grad.clone(), **{n: q.grad.clone() for n, q in m.named_parameters()}}
+        if twice:
+            y.backward(dy)
+        return out, peak
+
+    a, peak_in = grads(True)
+    b, peak_out = grads(False)
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    assert peak_out - peak_in >= 2 * 512 * 1024 * 2 * 0.9      # two [M, N] 16-bit buffers fewer
+    grads(False, twice=True)                                     # allowed
+    with pytest.raises(RuntimeError, match="inplace_backward"):
+        grads(True, twice=True)

@@ -92,3 +92,35 @@ def test_module_shard_descriptor(pkg):
     t = pkg.FusedGatedMLP(64, 128, parallel_mode="token")
     t.token_row0 = 4096
     assert (t._shard().row0, t._shard().col0) == (4096, 0)
+
+
+def test_tuning_travels_with_the_call_not_with_the_process(pkg):
+    """GEMM tuning is a field of each call's problem descriptor. Switching one module's SM limit on must not
+    move the process-wide defaults that every other module, device and host thread reads."""
+    L = pkg._lib
+    lib = L.load()
+    assert L.tune_word() == 0
+    w = L.tune_word(pair_mode=2, raster_group=16, sm_limit=132)
+    assert (w & 3, (w >> 2) & 0xFFF, (w >> 14) & 0xFFF) == (2, 16, 132)
+    with pytest.raises(ValueError):
+        L.tune_word(sm_limit=5000)
+    from triton_gated_mlp_b200.gated_mlp import _SmLimit
+
+    before = (lib.gmlp_set_cta_pair_mode(-1), lib.gmlp_set_raster_group(-1), lib.gmlp_set_sm_limit(-1))  # queries
+    lim = _SmLimit(torch.device("cpu"), 16, sm_count=148)
+    assert lim.tuning == 0
+    lim(True)
+    assert lim.tuning == L.tune_word(sm_limit=132)
+    assert (lib.gmlp_set_cta_pair_mode(-1), lib.gmlp_set_raster_group(-1), lib.gmlp_set_sm_limit(-1)) == before
+    lim(False)
+    assert lim.tuning == 0
+    # the descriptor carries the word
+    p = pkg.ops.kernels._problem(4, 64, 64, torch.bfloat16, pkg.ops.kernels.NO_DROPOUT, pkg.ops.kernels.NO_SHARD,
+                                 tuning=w)
+    assert p.tuning == w
+
+
+def test_status_read_moves_the_scratch_epoch_only_on_failure(pkg):
+    L = pkg._lib
+    e0 = L.scratch_epoch()
+    assert isinstance(e0, int) and L.scratch_epoch() == e0

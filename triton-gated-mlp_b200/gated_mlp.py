@@ -42,8 +42,10 @@ class _SmLimit:
     (gmlp_problem_t.tuning); nothing process-wide is touched, so other modules, devices and
     host threads keep their full grids."""
 
-    def __init__(self, device: torch.device, comm_sms: int):
-        self.sms = max(2, torch.cuda.get_device_properties(device).multi_processor_count - max(0, int(comm_sms)))
+    def __init__(self, device: torch.device, comm_sms: int, sm_count: Optional[int] = None):
+        if sm_count is None:
+            sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+        self.sms = max(2, int(sm_count) - max(0, int(comm_sms)))
         self.on = False
 
     def __call__(self, on: bool) -> None:
