@@ -578,6 +578,7 @@ def tp_section(pkg, dev, rank, world, dist):
     x64 = torch.randn((64, K), device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(42))
     want = None
     if rank == 0:
+        torch.set_num_threads(max(1, min(16, os.cpu_count() or 1)))   # torchrun pins OMP_NUM_THREADS to 1
         want = orc.forward(x64.float().cpu(), wg.float().cpu(), None, wu.float().cpu(), None, wd.float().cpu(), None)
     del wg, wu, wd
     decode = []
@@ -752,7 +753,7 @@ def run_gpu(args, w, name):
         y.backward(dy)
         return xx.grad
 
-    launches_per_step = 2 if not train else (2 + 4 + (3 if w["bias"] else 0) * 2)
+    launches_per_step = 2 if not train else 6   # bias gradients come out of the weight-gradient kernels
 
     def barrier():
         torch.cuda.synchronize()

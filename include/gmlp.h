@@ -105,9 +105,33 @@ int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
  * dH' = dH * mask / (1-p), in one kernel. Replaces the dH half of down_proj's
  * autograd (implicit at src/triton_gated_mlp/gated_mlp.py:236) fused with
  * _compute_quantities_for_bwd (src/triton_gated_mlp/ops/bwd.py:82-211), reading
- * the saved pre-activations instead of recomputing them. */
+ * the saved pre-activations instead of recomputing them. d_gate may be g and d_up may
+ * be u (in place: every element is read before the same thread overwrites it). */
 int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down,
                      const void* g, const void* u, void* d_gate, void* d_up, void* stream);
+
+/* The whole forward pass in one call: gmlp_hidden_fwd then gmlp_down_fwd on `stream`
+ * (FusedGatedMLP.forward, src/triton_gated_mlp/gated_mlp.py:222-237: the fused hidden
+ * state followed by self.down_proj). Arguments as for the two calls. */
+int gmlp_mlp_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate, const void* b_gate,
+                 const void* w_up, const void* b_up, const void* w_down, const void* b_down,
+                 const void* residual, void* h, void* g_save, void* u_save, void* y, void* stream);
+
+/* The whole backward pass in one call (FusedGatedMLPFunction.backward,
+ * src/triton_gated_mlp/gated_mlp.py:186-200, plus the down projection's and the biases'
+ * gradients that the reference leaves to autograd): gmlp_bwd_dhidden, gmlp_bwd_dx,
+ * gmlp_bwd_dw_gate_up_bias, gmlp_bwd_dw_down_bias, in that order on `stream`.
+ * Output pointers that are NULL are skipped: dx; dw_gate and dw_up (both or neither);
+ * dw_down; db_gate / db_up (only together with dw_gate, dw_up) and db_down (only with
+ * dw_down). d_gate / d_up are work buffers [M,N], required when dx or dw_gate is asked
+ * for; they may be the buffers g / u themselves (every element is read before it is
+ * overwritten). `scratch` as for gmlp_bwd_dw_gate_up_bias; may be NULL when no bias
+ * gradient is asked for. */
+int gmlp_mlp_bwd(const gmlp_problem_t* p, const void* dy, const void* x, const void* w_gate,
+                 const void* w_up, const void* w_down, const void* g, const void* u, const void* h,
+                 void* d_gate, void* d_up, void* dx, void* dw_gate, void* dw_up, void* dw_down,
+                 void* db_gate, void* db_up, void* db_down, void* scratch, size_t scratch_bytes,
+                 void* stream);
 
 /* The elementwise half of the above for a caller that already holds dH[M,N]
  * (the op-level contract of mlp_hidden_states_bwd, ops/bwd.py:466-602). */
@@ -128,11 +152,33 @@ int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void*
 int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
                      void* stream);
 
+/* The two weight-gradient GEMMs above with the bias gradients fused in:
+ * db_gate[N] = sum over tokens of d_gate, db_up[N] likewise, db_down[K] = sum over
+ * tokens of dy. The reference returns None for the gate / up bias gradients
+ * (src/triton_gated_mlp/gated_mlp.py:200) and leaves db_down to autograd of :236;
+ * EagerGatedMLP's autograd defines the values. The sums are the row sums of the GEMM's
+ * own A operand (d^T), taken beside the main loop by an otherwise idle warp of every
+ * CTA from tiles fetched a second time through L2: no extra launch and no second pass
+ * over d_gate / d_up / dy in HBM. Any of the db pointers may be NULL (with all NULL
+ * the call is the plain GEMM and takes no scratch). fp32 accumulation, partial sums
+ * added in a fixed order: results are bitwise repeatable.
+ * `scratch`: gmlp_bias_grad_scratch_bytes(p) bytes, 16-byte aligned, serves both calls;
+ * its first 64 KiB (arrival counters) must be ZERO before the first call and every
+ * call leaves them zero, unless gmlp_status_read has since returned a non-zero word:
+ * then clear them again. Calls that share a scratch buffer must not overlap on the GPU. */
+size_t gmlp_bias_grad_scratch_bytes(const gmlp_problem_t* p);
+int gmlp_bwd_dw_gate_up_bias(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                             const void* x, void* dw_gate, void* dw_up, void* db_gate, void* db_up,
+                             void* scratch, size_t scratch_bytes, void* stream);
+int gmlp_bwd_dw_down_bias(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                          void* db_down, void* scratch, size_t scratch_bytes, void* stream);
+
 /* dst[cols] = sum over rows of src[rows, cols] (fp32 accumulation): the bias
  * gradients db_gate, db_up (from d_gate, d_up) and db_down (from dy), which the
  * reference leaves to autograd of nn.Linear / returns as None
- * (src/triton_gated_mlp/gated_mlp.py:200). `scratch` holds
- * gmlp_colsum_scratch_bytes(rows, cols) bytes of fp32 partial sums. */
+ * (src/triton_gated_mlp/gated_mlp.py:200), as a stand-alone pass for a caller that
+ * does not run the weight-gradient GEMMs (which otherwise deliver them, see above).
+ * `scratch` holds gmlp_colsum_scratch_bytes(rows, cols) bytes of fp32 partial sums. */
 size_t gmlp_colsum_scratch_bytes(int64_t rows, int64_t cols);
 int gmlp_colsum(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
                 void* scratch, size_t scratch_bytes, void* dst, void* stream);

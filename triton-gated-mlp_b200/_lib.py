@@ -19,8 +19,9 @@ ACT_CODES = {"silu": 0, "swish": 0, "no_act": 1, "relu": 2, "gelu": 3, "sigmoid"
 
 # Every symbol include/gmlp.h declares; tests check that the library exports all of them.
 EXPORTS = (
-    "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
-    "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
+    "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_mlp_fwd", "gmlp_mlp_bwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
+    "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_bias_grad_scratch_bytes", "gmlp_bwd_dw_gate_up_bias",
+    "gmlp_bwd_dw_down_bias", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group", "gmlp_set_sm_limit",
     "gmlp_peer_region_bytes", "gmlp_set_peer_two_shot_bytes", "gmlp_peer_alloc", "gmlp_peer_open", "gmlp_peer_close", "gmlp_peer_free",
     "gmlp_peer_allreduce", "gmlp_status_read", "gmlp_last_error", "gmlp_version",
@@ -51,11 +52,17 @@ def _declare(lib: C.CDLL) -> None:
     pp = C.POINTER(Problem)
     lib.gmlp_hidden_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_down_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_mlp_fwd.argtypes = [pp] + [vp] * 13
+    lib.gmlp_mlp_bwd.argtypes = [pp] + [vp] * 18 + [C.c_size_t, vp]
     lib.gmlp_bwd_dhidden.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_bwd_dact.argtypes = [pp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_bwd_dx.argtypes = [pp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_bwd_dw_gate_up.argtypes = [pp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_bwd_dw_down.argtypes = [pp, vp, vp, vp, vp]
+    lib.gmlp_bias_grad_scratch_bytes.argtypes = [pp]
+    lib.gmlp_bias_grad_scratch_bytes.restype = C.c_size_t
+    lib.gmlp_bwd_dw_gate_up_bias.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
+    lib.gmlp_bwd_dw_down_bias.argtypes = [pp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_colsum_scratch_bytes.argtypes = [i64, i64]
     lib.gmlp_colsum_scratch_bytes.restype = C.c_size_t
     lib.gmlp_colsum.argtypes = [i64, i64, i32, vp, i64, vp, C.c_size_t, vp, vp]

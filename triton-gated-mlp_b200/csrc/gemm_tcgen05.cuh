@@ -54,6 +54,12 @@ struct GemmArgs {
   long long ld_out;  // row pitch (elements) of out*
   long long ld_in;   // row pitch (elements) of in*
   DropoutParams drop;
+  // Row sums of an MN-major A operand, taken on the side by the watcher warp (ASUM kernels):
+  // the bias gradients of the weight-gradient GEMMs, db[n] = sum over tokens of d[token, n],
+  // where d^T is exactly the kernel's A. Null / zero when unused.
+  void* asum_out[2];  // per batch: [M] sums, in the matrices' 16-bit type
+  float* asum_part;   // [batches][n_tiles][m_tiles * tile rows] fp32 partial sums
+  int* asum_cnt;      // [batches][m_tiles * tile rows / 128] arrivals; zero on entry and on exit
 };
 
 constexpr int BM = 128;        // rows per tile = TMEM lanes
@@ -72,6 +78,8 @@ constexpr int WATCHER_WARP = 2 + EPI_WARPS;
 constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);        // 608
 constexpr uint32_t EPI_BAR_THREADS = 32 * (EPI_WARPS + 1);  // epilogue warps + watcher
 constexpr uint32_t EPI_BAR_ID0 = 1;                       // named barriers 1, 2: one per accumulator
+constexpr uint32_t EPI_DONE_BAR = 3;                      // ASUM kernels: the epilogue warps have left the staging area
+constexpr int ASUM_BUFS = 4;                              // the watcher's private ring: 4 x 16 KB in the staging area
 
 __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
   return (2 * bn <= 32) ? 32u : (2 * bn <= 64) ? 64u : (2 * bn <= 128) ? 128u
@@ -81,10 +89,10 @@ __host__ __device__ constexpr uint32_t tmem_cols_for(int bn) {
 // Epilogue staging (see "Epilogue I/O" below).
 constexpr int EPI_PARTS = EPI_WARPS / 4;  // column parts of a tile
 constexpr int BLK_BYTES = 32 * 32;        // dH epilogue: one warp's [32 rows x 16 columns] 16-bit block
-constexpr int STORE_STAGE_BYTES = 4096;   // store / gate-up epilogues: 4 KB per warp
+constexpr int STORE_STAGE_BYTES = 4096;   // every epilogue: 4 KB of staging per warp
 template <int EPI>
 __host__ __device__ constexpr int staging_bytes() {
-  return EPI == EPI_DHIDDEN ? EPI_WARPS * 2 * BLK_BYTES : EPI_WARPS * STORE_STAGE_BYTES;
+  return EPI_WARPS * STORE_STAGE_BYTES;
 }
 // Ring depth: as many stages as fit beside the staging area in the 227 KB a CTA may use.
 constexpr int SMEM_LIMIT = 232448;
@@ -277,8 +285,11 @@ __device__ __forceinline__ TileCoord decode_tile(int tile, int m_tiles, int n_ti
 // no epilogue uses 32-byte rows.)
 //
 // dH epilogue: it also LOADS two [M, N] matrices and keeps to the load/store unit: every
-// warp owns two 1 KB staging blocks ([32 rows x 16 columns], 32-byte rows) and transposes
-// through them, so that in global memory two neighbouring lanes cover one row's 32 bytes.
+// warp owns two PAIRS of 1 KB staging blocks ([32 rows x 16 columns], 32-byte rows; one block
+// for G, one for U) and transposes through them, so that in global memory two neighbouring
+// lanes cover one row's 32 bytes. The loads are asynchronous copies (cp.async) straight into
+// a pair, issued two 16-column units ahead of use (no registers held meanwhile), so the
+// first two units of a tile are fetched while the warp sleeps through the main loop.
 //   row view        lane r holds row r:            bytes [32 r, 32 r + 32)
 //   coalesced view  lane l, step t in {0, 1}:      row (l >> 1) + 16 t, 16-byte half l & 1
 // The two halves of a row swap places in rows 4..7 of every group of 8 (a 32-byte
@@ -434,11 +445,28 @@ struct OutMaps {
 // arguments. The unrolled epilogues hold many copies of the activation per tile pass;
 // with the seven-way switch in each copy the taken path is islands in a sea of
 // instructions, so the usual activation (SiLU) gets a body of its own.
+// Asynchronous copy of this lane's two 16-byte pieces (coalesced view) of the [32 x 16] block at
+// (row0, col) of `in` into the staging block `buf`; zeros where the block leaves the matrix.
+template <typename T>
+__device__ __forceinline__ void fetch_block_async(const BlockView& bv, uint32_t buf, const T* in, long long ld,
+                                                  int row0, int col, int M, int N) {
+  const int c = col + bv.chalf * 8;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int r = row0 + bv.crow[t];
+    const bool ok = r < M && c < N;
+    cp_async_16_zfill(buf + bv.co[t], ok ? static_cast<const void*>(in + static_cast<long long>(r) * ld + c)
+                                         : static_cast<const void*>(in), ok ? 16u : 0u);
+  }
+}
+
+// DHIDDEN only: next_row0 / next_n0 locate this warp's rows and the first column of the NEXT tile
+// (next_row0 < 0: there is none); its first two units are requested at the end of this tile.
 template <int BN, int EPI, typename T, int ACTC>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
                                               int row0, int lane, int batch, int n0, int part,
                                               const BlockView& bv, uint32_t stage, const T* bias0,
-                                              const T* bias1, bool drop_on) {
+                                              const T* bias1, bool drop_on, int next_row0, int next_n0) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int row = row0 + lane;
   const bool row_ok = row < args.M;
@@ -577,28 +605,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMap
     }
   } else {  // EPI_DHIDDEN
     constexpr int NU = TILE_N / 16 / EPI_PARTS;  // 16-column units per warp
+    static_assert(NU >= 2 && NU % 2 == 0, "units alternate between the warp's two pairs of staging blocks");
     const int u0 = part * NU;
     T* const out_g = static_cast<T*>(args.out0);
     T* const out_u = static_cast<T*>(args.out1);
     const T* const in_g = static_cast<const T*>(args.in0);
     const T* const in_u = static_cast<const T*>(args.in1);
     const long long grow = args.drop.row0_global + row;
-    const uint32_t buf_g = stage, buf_u = stage + BLK_BYTES;
-    uint4 pg[2], pu[2];  // G and U of the next unit, coalesced view, in flight
-    fetch_block<T>(bv, in_g, args.ld_in, row0, n0 + u0 * 16, M, N, pg);
-    fetch_block<T>(bv, in_u, args.ld_in, row0, n0 + u0 * 16, M, N, pu);
 #pragma unroll
     for (int ui = 0; ui < NU; ++ui) {
       const int col = n0 + (u0 + ui) * 16;
+      const uint32_t buf_g = stage + (ui & 1) * (2 * BLK_BYTES), buf_u = buf_g + BLK_BYTES;
       uint32_t acc[16];
       tmem_ld_32x16(taddr + (u0 + ui) * 16, acc);
-      __syncwarp();  // the previous unit's coalesced reads of both blocks are done
-      spill_block(bv, buf_g, pg);
-      spill_block(bv, buf_u, pu);
-      if (ui + 1 < NU) {
-        fetch_block<T>(bv, in_g, args.ld_in, row0, col + 16, M, N, pg);
-        fetch_block<T>(bv, in_u, args.ld_in, row0, col + 16, M, N, pu);
-      }
+      // this unit's G and U were requested two units ago; the request after it may still be in flight
+      cp_async_wait_group<1>();
       __syncwarp();
       uint4 gq[2], uq[2];
       read_row(bv, buf_g, gq[0], gq[1]);
@@ -647,22 +668,148 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMap
       // the coalesced view.
       store_block<T>(bv, buf_g, out_g, args.ld_out, row0, col, M, N, qg[0], qg[1]);
       store_block<T>(bv, buf_u, out_u, args.ld_out, row0, col, M, N, qu[0], qu[1]);
+      __syncwarp();  // the pair has been read out: request the unit after next into it
+      if (ui + 2 < NU) {
+        fetch_block_async<T>(bv, buf_g, in_g, args.ld_in, row0, col + 32, M, N);
+        fetch_block_async<T>(bv, buf_u, in_u, args.ld_in, row0, col + 32, M, N);
+      } else if (next_row0 >= 0) {
+        const int ncol = next_n0 + (u0 + ui + 2 - NU) * 16;
+        fetch_block_async<T>(bv, buf_g, in_g, args.ld_in, next_row0, ncol, M, N);
+        fetch_block_async<T>(bv, buf_u, in_u, args.ld_in, next_row0, ncol, M, N);
+      }
+      cp_async_commit();  // one group per unit, empty when there was nothing left to request
     }
   }
+}
+
+// Row sums of this CTA's 128 rows of the MN-major A operand over the tile's SHARE of the
+// reduction blocks (block kb belongs to the column tile kb mod n_tiles of its row tile, so
+// the column tiles of one row tile divide the work between them), by the watcher warp while
+// the main loop runs: the blocks are fetched with TMA through the same tensor map the
+// producer uses into a private ring in the epilogue's staging area (idle at that time),
+// summed from shared memory, and the partial sums go to `asum_part`. The CTA that brings
+// the count of a 128-row block to n_tiles adds the partials in column-tile order (so the
+// result does not depend on arrival order) and writes the sums.
+//   seq      running number of this warp's ring loads (ring slot and mbarrier phase follow from it)
+//   returns false if a wait ran out
+template <typename T>
+__device__ __forceinline__ bool asum_tile(const GemmArgs& args, const CUtensorMap* map, const TileCoord& tc,
+                                          int lane, int n_tiles, int mn0, int mn_pad, uint32_t ring,
+                                          uint32_t bar0, uint32_t& seq, volatile int* abortp) {
+  constexpr uint32_t BUF_BYTES = 2 * BK * 128;  // two [64 reduction rows x 64 columns] boxes
+  const int count = tc.n_tile < args.kb0 ? (args.kb0 - tc.n_tile + n_tiles - 1) / n_tiles : 0;
+  auto issue = [&](int i) {  // lane 0
+    const uint32_t slot = (seq + i) % ASUM_BUFS;
+    const uint32_t dst = ring + slot * BUF_BYTES, bar = bar0 + 8u * slot;
+    const int k0 = (tc.n_tile + i * n_tiles) * BK;
+    fence_proxy_async_smem();
+    mbar_expect_tx(bar, BUF_BYTES);
+    tma_load_2d(dst, map, bar, mn0, k0);
+    tma_load_2d(dst + BK * 128, map, bar, mn0 + 64, k0);
+  };
+  if (lane == 0)
+    for (int i = 0; i < count && i < ASUM_BUFS; ++i) issue(i);
+  const int j = lane & 7, rg = lane >> 3;  // 16-byte chunk (8 columns) and row group of this lane
+  float acc[2][8];
+#pragma unroll
+  for (int b = 0; b < 2; ++b)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[b][c] = 0.f;
+  bool ok = true;
+  for (int i = 0; i < count; ++i) {
+    const uint32_t slot = (seq + i) % ASUM_BUFS, phase = ((seq + i) / ASUM_BUFS) & 1u;
+    ok = mbar_wait_warp(bar0 + 8u * slot, phase, abortp, lane);
+    if (!ok) break;
+    const uint32_t buf = ring + slot * BUF_BYTES;
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+#pragma unroll 4
+      for (int r = rg; r < BK; r += 4) {
+        float v[8];
+        unpack8<T>(ld_shared_v4(buf + b * (BK * 128) + staged_chunk<128>(r, j)), v);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[b][c] += v[c];
+      }
+    }
+    __syncwarp();  // every lane has read the slot before it is refilled
+    if (lane == 0 && i + ASUM_BUFS < count) issue(i + ASUM_BUFS);
+  }
+  seq += static_cast<uint32_t>(count);
+  if (!ok) return false;
+  // lanes with the same chunk hold different rows: fold them onto lanes 0..7
+#pragma unroll
+  for (int b = 0; b < 2; ++b)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      acc[b][c] += __shfl_xor_sync(0xffffffffu, acc[b][c], 8);
+      acc[b][c] += __shfl_xor_sync(0xffffffffu, acc[b][c], 16);
+    }
+  float* const part = args.asum_part + (static_cast<long long>(tc.batch) * n_tiles + tc.n_tile) * mn_pad + mn0;
+  if (lane < 8) {
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      float4* q = reinterpret_cast<float4*>(part + 64 * b + 8 * j);
+      q[0] = make_float4(acc[b][0], acc[b][1], acc[b][2], acc[b][3]);
+      q[1] = make_float4(acc[b][4], acc[b][5], acc[b][6], acc[b][7]);
+    }
+  }
+  __threadfence();
+  __syncwarp();
+  int last = 0;
+  int* const cnt = args.asum_cnt + static_cast<long long>(tc.batch) * (mn_pad / 128) + mn0 / 128;
+  if (lane == 0) {
+    last = atomicAdd(cnt, 1) == n_tiles - 1 ? 1 : 0;
+    if (last) *cnt = 0;  // nobody else touches this counter again in this launch
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (last) {
+    __threadfence();
+    T* const out = static_cast<T*>(args.asum_out[tc.batch]);
+    const float* const p0 = args.asum_part + static_cast<long long>(tc.batch) * n_tiles * mn_pad + mn0;
+    // 128 columns, 4 per lane
+    const int c = lane * 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < n_tiles; ++t) {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(p0 + static_cast<long long>(t) * mn_pad + c));
+      s.x += q.x; s.y += q.y; s.z += q.z; s.w += q.w;
+    }
+    if (mn0 + c < args.M) {  // M is a multiple of 8: the four columns are inside or outside together
+      uint2 o;
+      o.x = Pack2<T>::pack(s.x, s.y);
+      o.y = Pack2<T>::pack(s.z, s.w);
+      *reinterpret_cast<uint2*>(out + mn0 + c) = o;
+    }
+  }
+  return true;
 }
 
 // The watcher role (warp 18, all lanes): for every tile of this CTA, wait until the MMA
 // issuer's commit has marked the accumulator full, publish the verdict and release the
 // epilogue warps from their named barrier. It arrives on the barrier whatever the
 // outcome, so the epilogue warps always wake up, read the same verdict and leave together.
-__device__ __forceinline__ void watcher_role(const GemmArgs& args, int lane, int first_tile,
-                                             int tile_stride, int total_tiles, uint32_t tfull0,
-                                             volatile int* epi_go, int* abort_flag) {
+// ASUM: before that wait it takes the tile's share of the A operand's row sums (asum_tile),
+// using the staging area between the previous tile's epilogue and this tile's.
+template <typename T, int TILE_M, bool ASUM>
+__device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtensorMap* mapA0,
+                                             const CUtensorMap* mapA1, int lane, int first_tile,
+                                             int tile_stride, int total_tiles, int m_tiles, int n_tiles,
+                                             int row_off, uint32_t tfull0, uint32_t asum_bar0,
+                                             uint32_t epi_smem, volatile int* epi_go, int* abort_flag) {
   volatile int* abortp = abort_flag;
   int local = 0;
+  uint32_t seq = 0;
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
     const int acc = local & 1;
-    const bool ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane);
+    bool ok = true;
+    if (ASUM) {
+      const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+      const int mn0 = tc.m_tile * TILE_M + row_off;
+      if (local > 0) named_bar_sync(EPI_DONE_BAR, EPI_BAR_THREADS);  // the staging area is free
+      if (args.asum_out[tc.batch] != nullptr && mn0 < args.M)
+        ok = asum_tile<T>(args, tc.batch ? mapA1 : mapA0, tc, lane, n_tiles, mn0, m_tiles * TILE_M, epi_smem,
+                          asum_bar0, seq, abortp);
+    }
+    ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane) && ok;
     tc_fence_after_sync();
     if (lane == 0) {
       epi_go[acc] = ok ? 1 : 0;
@@ -683,7 +830,7 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, int lane, int
 //   tempty0    shared::cta address of tempty[0] ([1] is 8 bytes on)
 //   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
 //   epi_smem   this CTA's epilogue staging area
-template <int BN, int EPI, typename T, int TILE_M, bool REMOTE>
+template <int BN, int EPI, typename T, int TILE_M, bool REMOTE, bool ASUM>
 __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMaps& maps, int warp,
                                               int lane, int first_tile, int tile_stride,
                                               int total_tiles, int m_tiles, int n_tiles, int row_off,
@@ -698,10 +845,32 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMap
   const T* const bias1 = static_cast<const T*>(args.bias1);
   const bool drop_on = args.drop.thresh != 0u;
   const BlockView bv(lane);
-  const uint32_t stage = epi_smem + ew * (EPI == EPI_DHIDDEN ? 2 * BLK_BYTES : STORE_STAGE_BYTES);
+  const uint32_t stage = epi_smem + ew * STORE_STAGE_BYTES;
+  if (EPI == EPI_DHIDDEN) {
+    // the first tile's first two units; every later request is made from inside epilogue_tile
+    if (first_tile < total_tiles) {
+      const TileCoord t0 = decode_tile(first_tile, m_tiles, n_tiles, args.group_m);
+      const int r0 = t0.m_tile * TILE_M + row_off + quarter * 32;
+      const int c0 = t0.n_tile * TILE_N + col_part * (TILE_N / EPI_PARTS);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t buf = stage + q * (2 * BLK_BYTES);
+        fetch_block_async<T>(bv, buf, static_cast<const T*>(args.in0), args.ld_in, r0, c0 + 16 * q, args.M, args.N);
+        fetch_block_async<T>(bv, buf + BLK_BYTES, static_cast<const T*>(args.in1), args.ld_in, r0, c0 + 16 * q,
+                             args.M, args.N);
+        cp_async_commit();
+      }
+    }
+  }
   int local = 0;
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
     const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
+    int next_row0 = -1, next_n0 = 0;
+    if (EPI == EPI_DHIDDEN && tile + tile_stride < total_tiles) {
+      const TileCoord nx = decode_tile(tile + tile_stride, m_tiles, n_tiles, args.group_m);
+      next_row0 = nx.m_tile * TILE_M + row_off + quarter * 32;
+      next_n0 = nx.n_tile * TILE_N;
+    }
     const int acc = local & 1;
     __syncwarp();
     named_bar_sync(EPI_BAR_ID0 + acc, EPI_BAR_THREADS);  // asleep until the watcher arrives
@@ -711,10 +880,10 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMap
     const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
     if (EPI != EPI_STORE && args.act == ACT_SILU)
       epilogue_tile<BN, EPI, T, ACT_SILU>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
-                                          stage, bias0, bias1, drop_on);
+                                          stage, bias0, bias1, drop_on, next_row0, next_n0);
     else
       epilogue_tile<BN, EPI, T, -1>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
-                                    stage, bias0, bias1, drop_on);
+                                    stage, bias0, bias1, drop_on, next_row0, next_n0);
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
     // semantics; no fence is placed here on purpose, since a fence would also wait for
@@ -724,13 +893,22 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMap
       if (REMOTE) mbar_arrive_cluster(mapa_shared(tempty0 + 8u * acc, 0));
       else mbar_arrive(tempty0 + 8u * acc);
     }
+    if (ASUM && tile + tile_stride < total_tiles) {
+      // The watcher borrows the staging area until the next tile's epilogue: tell it once
+      // this warp's stores have been read out of it.
+      if (lane == 0) bulk_wait_group_read<0>();
+      __syncwarp();
+      named_bar_arrive(EPI_DONE_BAR, EPI_BAR_THREADS);
+    }
   }
-  // Shared memory must outlive the TMA stores that still read it.
+  // Shared memory must outlive the TMA stores that still read it (and the dH epilogue's last,
+  // empty, copy groups must have retired).
   if (EPI != EPI_DHIDDEN && lane == 0) bulk_wait_group_read<0>();
+  if (EPI == EPI_DHIDDEN) cp_async_wait_group<0>();
 }
 
 // ------------------------------------------------------------------ kernel --
-template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES, bool ASUM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
                     const __grid_constant__ CUtensorMap tmA1,
@@ -742,6 +920,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "tcgen05 N range for M = 128");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 64 == 0, "MN-major B arrives in 64-column boxes");
+  static_assert(!ASUM || (A_MN && EPI == EPI_STORE), "row sums are taken of an MN-major A beside a plain store");
   constexpr uint32_t A_BYTES = BM * 128;
   constexpr uint32_t B_BYTES = BN * 128;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -754,7 +933,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   constexpr uint32_t A_KSTEP = (A_MN ? 2048 : 32) >> 4, B_KSTEP = (B_MN ? 2048 : 32) >> 4;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4 + ASUM_BUFS];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
   __shared__ volatile int epi_go[2];
@@ -781,6 +960,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    for (int b = 0; b < ASUM_BUFS; ++b) mbar_init(bar_base + 8u * (2 * STAGES + 4 + b), 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), EPI_WARPS);  // one arrival per epilogue warp
@@ -895,11 +1075,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
       }
     }
   } else if (warp == WATCHER_WARP) {
-    watcher_role(args, lane, blockIdx.x, gridDim.x, total_tiles, tfull_bar(0), epi_go, &abort_flag);
+    watcher_role<T, BM, ASUM>(args, &tmA0, &tmA1, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles, n_tiles, 0,
+                              tfull_bar(0), bar_base + 8u * (2 * STAGES + 4), smem_base + STAGES * STAGE_BYTES,
+                              epi_go, &abort_flag);
   } else {
     // ------------------------------------------------------------ epilogue --
     const OutMaps maps{&tmO0, &tmO1, &tmO2};
-    epilogue_role<BN, EPI, T, BM, false>(args, maps, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
+    epilogue_role<BN, EPI, T, BM, false, ASUM>(args, maps, warp, lane, blockIdx.x, gridDim.x, total_tiles, m_tiles,
                                          n_tiles, 0, tmem_base, tempty_bar(0),
                                          smem_base + STAGES * STAGE_BYTES, epi_go);
   }
@@ -929,7 +1111,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 //   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
 //              both copies at once.
 //   tempty[a]  lives in the leader, 32 arrivals: the 16 epilogue warps of each CTA.
-template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES>
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES, bool ASUM>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
                          const __grid_constant__ CUtensorMap tmA1,
@@ -941,6 +1123,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tcgen05 N range for M = 256");
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
+  static_assert(!ASUM || (A_MN && EPI == EPI_STORE), "row sums are taken of an MN-major A beside a plain store");
   constexpr int HALF_N = BN / 2;  // B columns staged by each CTA
   constexpr uint32_t A_BYTES = BM * 128;
   constexpr uint32_t B_BYTES = HALF_N * 128;
@@ -952,7 +1135,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   constexpr uint32_t A_KSTEP = (A_MN ? 2048 : 32) >> 4, B_KSTEP = (B_MN ? 2048 : 32) >> 4;
 
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4 + ASUM_BUFS];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
   __shared__ volatile int epi_go[2];
@@ -982,6 +1165,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    for (int b = 0; b < ASUM_BUFS; ++b) mbar_init(bar_base + 8u * (2 * STAGES + 4 + b), 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 2 * EPI_WARPS);  // the epilogue warps of both CTAs of the pair
@@ -1098,11 +1282,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       }
     }
   } else if (warp == WATCHER_WARP) {
-    watcher_role(args, lane, pair, num_pairs, total_tiles, tfull_bar(0), epi_go, &abort_flag);
+    watcher_role<T, PAIR_M, ASUM>(args, &tmA0, &tmA1, lane, pair, num_pairs, total_tiles, m_tiles, n_tiles,
+                                  static_cast<int>(rank) * BM, tfull_bar(0), bar_base + 8u * (2 * STAGES + 4),
+                                  smem_base + STAGES * STAGE_BYTES, epi_go, &abort_flag);
   } else {
     // ------------------------------------------------------------ epilogue --
     const OutMaps maps{&tmO0, &tmO1, &tmO2};
-    epilogue_role<BN, EPI, T, PAIR_M, true>(args, maps, warp, lane, pair, num_pairs, total_tiles, m_tiles,
+    epilogue_role<BN, EPI, T, PAIR_M, true, ASUM>(args, maps, warp, lane, pair, num_pairs, total_tiles, m_tiles,
                                             n_tiles, static_cast<int>(rank) * BM, tmem_base, tempty_bar(0),
                                             smem_base + STAGES * STAGE_BYTES, epi_go);
   }

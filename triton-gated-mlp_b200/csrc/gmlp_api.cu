@@ -196,6 +196,10 @@ struct Epilogue {
   int64_t ld_out = 0;
   int64_t ld_in = 0;
   DropoutParams drop = {};
+  // row sums of the MN-major A operand (bias gradients), see GemmArgs
+  void* asum_out[2] = {nullptr, nullptr};
+  float* asum_part = nullptr;
+  int* asum_cnt = nullptr;
 };
 
 // Process-wide DEFAULTS of the three tuning knobs (set by gmlp_set_*). A call that
@@ -244,7 +248,7 @@ static int ensure_smem_attr(K kfn, size_t smem, std::atomic<uint64_t>& done) {
   return GMLP_OK;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI, typename T>
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T, bool ASUM>
 static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
                          const Operand& a0, const Operand* a1, const Operand& b0,
                          const Operand* b1, int64_t k1, int batches, const Epilogue& ep,
@@ -313,6 +317,10 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.ld_out = ep.ld_out;
   args.ld_in = ep.ld_in;
   args.drop = ep.drop;
+  args.asum_out[0] = ep.asum_out[0];
+  args.asum_out[1] = ep.asum_out[1];
+  args.asum_part = ep.asum_part;
+  args.asum_cnt = ep.asum_cnt;
 
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int64_t tile_m = pair ? 2 * BM : BM;
@@ -330,7 +338,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     constexpr size_t smem = gemm_smem_bytes<B_ROWS_PAIR, EPI, PAIR_STAGES>();
     static_assert(smem + 512 <= SMEM_LIMIT, "pair kernel exceeds the shared memory of an SM");
-    auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES>;
+    auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, PAIR_STAGES, ASUM>;
     static std::atomic<uint64_t> attr_done{0};
     if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
     kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, args);
@@ -339,7 +347,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
     const int grid = static_cast<int>(tiles < budget ? tiles : budget);
     constexpr size_t smem = gemm_smem_bytes<B_ROWS_SINGLE, EPI, STAGES>();
     static_assert(smem + 512 <= SMEM_LIMIT, "kernel exceeds the shared memory of an SM");
-    auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES>;
+    auto kfn = gemm_tcgen05_kernel<BN, A_MN, B_MN, EPI, T, STAGES, ASUM>;
     static std::atomic<uint64_t> attr_done{0};
     if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
     kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, args);
@@ -349,15 +357,15 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   return GMLP_OK;
 }
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
+template <int BN, bool A_MN, bool B_MN, int EPI, bool ASUM = false>
 static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, const Operand& a0,
                        const Operand* a1, const Operand& b0, const Operand* b1, int64_t k1,
                        int batches, const Epilogue& ep, uint32_t tuning_word, cudaStream_t stream) {
   if (dtype == GMLP_BF16)
-    return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16>(dev, dtype, M, N, a0, a1, b0, b1, k1,
-                                                             batches, ep, tuning_word, stream);
-  return launch_gemm_t<BN, A_MN, B_MN, EPI, __half>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
-                                                    ep, tuning_word, stream);
+    return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16, ASUM>(dev, dtype, M, N, a0, a1, b0, b1, k1,
+                                                                   batches, ep, tuning_word, stream);
+  return launch_gemm_t<BN, A_MN, B_MN, EPI, __half, ASUM>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches,
+                                                          ep, tuning_word, stream);
 }
 
 static int check_problem(const gmlp_problem_t* p) {
@@ -557,8 +565,23 @@ int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
                                                   static_cast<cudaStream_t>(stream));
 }
 
-int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
-                        const void* x, void* dw_gate, void* dw_up, void* stream) {
+// Scratch of the fused bias-gradient sums for an output of `mn` rows whose GEMM has `cols`
+// output columns and `batches` problems: arrival counters (one per 128 rows and batch;
+// must be zero) followed by the fp32 partial sums [batches][column tiles][rows padded to 256].
+struct AsumLayout {
+  size_t cnt_bytes, part_bytes;
+};
+static AsumLayout asum_layout(int64_t mn, int64_t cols, int batches) {
+  const int64_t mn_pad = (mn + 255) / 256 * 256, n_tiles = (cols + 255) / 256;
+  AsumLayout l;
+  l.cnt_bytes = (static_cast<size_t>(batches) * (mn_pad / 128) * sizeof(int) + 255) / 256 * 256;
+  l.part_bytes = static_cast<size_t>(batches) * n_tiles * mn_pad * sizeof(float);
+  return l;
+}
+
+static int dw_gate_up_impl(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                           const void* x, void* dw_gate, void* dw_up, void* db_gate, void* db_up,
+                           void* scratch, size_t scratch_bytes, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if ((rc = check_ptrs({d_gate, d_up, x, dw_gate, dw_up}))) return rc;
@@ -573,12 +596,27 @@ int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void*
   ep.out0 = dw_gate;
   ep.out1 = dw_up;
   ep.ld_out = p->K;
-  return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr, 0,
-                                                 2, ep, p->tuning, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!db_gate && !db_up)
+    return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr, 0,
+                                                   2, ep, p->tuning, st);
+  // db[n] = sum over tokens of d[token, n]: the row sums of this GEMM's A operand
+  if ((db_gate && !aligned16(db_gate)) || (db_up && !aligned16(db_up)))
+    return fail(GMLP_ERR_ALIGN, "bias gradient buffers must be 16-byte aligned");
+  const AsumLayout l = asum_layout(p->N, p->K, 2);
+  if (!scratch || !aligned16(scratch) || scratch_bytes < l.cnt_bytes + l.part_bytes)
+    return fail(GMLP_ERR_SCRATCH, "bias-gradient scratch holds %zu bytes, %zu needed", scratch_bytes,
+                l.cnt_bytes + l.part_bytes);
+  ep.asum_out[0] = db_gate;
+  ep.asum_out[1] = db_up;
+  ep.asum_cnt = static_cast<int*>(scratch);
+  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + l.cnt_bytes);
+  return launch_gemm<256, true, true, EPI_STORE, true>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr,
+                                                       0, 2, ep, p->tuning, st);
 }
 
-int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
-                     void* stream) {
+static int dw_down_impl(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                        void* db_down, void* scratch, size_t scratch_bytes, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if ((rc = check_ptrs({dy, h, dw_down}))) return rc;
@@ -590,8 +628,84 @@ int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, voi
   Epilogue ep;
   ep.out0 = dw_down;
   ep.ld_out = p->N;
-  return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->K, p->N, a, nullptr, b, nullptr,
-                                                 0, 1, ep, p->tuning, static_cast<cudaStream_t>(stream));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!db_down)
+    return launch_gemm<256, true, true, EPI_STORE>(dev, p->dtype, p->K, p->N, a, nullptr, b, nullptr,
+                                                   0, 1, ep, p->tuning, st);
+  if (!aligned16(db_down)) return fail(GMLP_ERR_ALIGN, "bias gradient buffer must be 16-byte aligned");
+  const AsumLayout l = asum_layout(p->K, p->N, 1);
+  if (!scratch || !aligned16(scratch) || scratch_bytes < l.cnt_bytes + l.part_bytes)
+    return fail(GMLP_ERR_SCRATCH, "bias-gradient scratch holds %zu bytes, %zu needed", scratch_bytes,
+                l.cnt_bytes + l.part_bytes);
+  ep.asum_out[0] = db_down;
+  ep.asum_cnt = static_cast<int*>(scratch);
+  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + l.cnt_bytes);
+  return launch_gemm<256, true, true, EPI_STORE, true>(dev, p->dtype, p->K, p->N, a, nullptr, b,
+                                                       nullptr, 0, 1, ep, p->tuning, st);
+}
+
+int gmlp_bwd_dw_gate_up(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                        const void* x, void* dw_gate, void* dw_up, void* stream) {
+  return dw_gate_up_impl(p, d_gate, d_up, x, dw_gate, dw_up, nullptr, nullptr, nullptr, 0, stream);
+}
+
+int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                     void* stream) {
+  return dw_down_impl(p, dy, h, dw_down, nullptr, nullptr, 0, stream);
+}
+
+size_t gmlp_bias_grad_scratch_bytes(const gmlp_problem_t* p) {
+  if (!p || p->K <= 0 || p->N <= 0) return 0;
+  const AsumLayout a = asum_layout(p->N, p->K, 2), b = asum_layout(p->K, p->N, 1);
+  return std::max(a.cnt_bytes + a.part_bytes, b.cnt_bytes + b.part_bytes);
+}
+
+int gmlp_bwd_dw_gate_up_bias(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
+                             const void* x, void* dw_gate, void* dw_up, void* db_gate, void* db_up,
+                             void* scratch, size_t scratch_bytes, void* stream) {
+  return dw_gate_up_impl(p, d_gate, d_up, x, dw_gate, dw_up, db_gate, db_up, scratch, scratch_bytes,
+                         stream);
+}
+
+int gmlp_bwd_dw_down_bias(const gmlp_problem_t* p, const void* dy, const void* h, void* dw_down,
+                          void* db_down, void* scratch, size_t scratch_bytes, void* stream) {
+  return dw_down_impl(p, dy, h, dw_down, db_down, scratch, scratch_bytes, stream);
+}
+
+int gmlp_mlp_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate, const void* b_gate,
+                 const void* w_up, const void* b_up, const void* w_down, const void* b_down,
+                 const void* residual, void* h, void* g_save, void* u_save, void* y, void* stream) {
+  int rc;
+  if ((rc = gmlp_hidden_fwd(p, x, w_gate, b_gate, w_up, b_up, h, g_save, u_save, stream))) return rc;
+  return gmlp_down_fwd(p, h, w_down, b_down, residual, y, stream);
+}
+
+int gmlp_mlp_bwd(const gmlp_problem_t* p, const void* dy, const void* x, const void* w_gate,
+                 const void* w_up, const void* w_down, const void* g, const void* u, const void* h,
+                 void* d_gate, void* d_up, void* dx, void* dw_gate, void* dw_up, void* dw_down,
+                 void* db_gate, void* db_up, void* db_down, void* scratch, size_t scratch_bytes,
+                 void* stream) {
+  int rc;
+  if ((dw_gate == nullptr) != (dw_up == nullptr))
+    return fail(GMLP_ERR_ARG, "dw_gate and dw_up must both be given or both be NULL");
+  if ((db_gate || db_up) && !dw_gate)
+    return fail(GMLP_ERR_ARG, "db_gate / db_up are taken inside the dW_gate / dW_up GEMM: pass dw_gate and "
+                              "dw_up as well, or use gmlp_colsum");
+  if (db_down && !dw_down)
+    return fail(GMLP_ERR_ARG, "db_down is taken inside the dW_down GEMM: pass dw_down as well, or use "
+                              "gmlp_colsum");
+  const bool hidden = dx || dw_gate;
+  if (hidden) {
+    if (!d_gate || !d_up) return fail(GMLP_ERR_ARG, "d_gate and d_up buffers are needed for dx / dW_gate / dW_up");
+    if ((rc = gmlp_bwd_dhidden(p, dy, w_down, g, u, d_gate, d_up, stream))) return rc;
+    if (dx && (rc = gmlp_bwd_dx(p, d_gate, d_up, w_gate, w_up, dx, stream))) return rc;
+    if (dw_gate && (rc = gmlp_bwd_dw_gate_up_bias(p, d_gate, d_up, x, dw_gate, dw_up, db_gate, db_up, scratch,
+                                                  scratch_bytes, stream)))
+      return rc;
+  }
+  if (dw_down && (rc = gmlp_bwd_dw_down_bias(p, dy, h, dw_down, db_down, scratch, scratch_bytes, stream)))
+    return rc;
+  return GMLP_OK;
 }
 
 int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const void* u,

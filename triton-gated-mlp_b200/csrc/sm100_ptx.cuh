@@ -141,6 +141,11 @@ __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
 }
 
+// Ask L2 to fetch the line that holds `p` (no register or shared-memory destination).
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p) : "memory");
+}
+
 // ---------------------------------------------------- named CTA barriers ----
 // Barrier 0 is __syncthreads(). A warp parked at bar.sync costs no issue slots, unlike
 // one that polls an mbarrier. `threads` counts whole warps (a multiple of 32).
@@ -376,6 +381,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 // ---- Ampere-style asynchronous copies (global -> shared, 16 bytes, L2 only) ----
 __device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gmem_src) : "memory");
+}
+// The same with `src_bytes` (0 or 16) bytes read and the rest of the 16 filled with zeros.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Blocks until at most N of the calling thread's cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() {
   asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");

@@ -10,9 +10,9 @@ path silently drops (:172-180, :200).
 
 One autograd.Function spans all three projections. Forward: one tcgen05 kernel
 for gate/up + bias + SiLU*up + dropout, one for the down projection. Backward:
-dH fused with the activation derivative, then dX, dW_gate/dW_up, dW_down, and
-column sums for the bias gradients; the gate / up pre-activations are saved, not
-recomputed.
+dH fused with the activation derivative, then dX, dW_gate/dW_up and dW_down with
+the bias gradients (column sums of d_gate, d_up, dy) taken inside the weight-gradient
+kernels; the gate / up pre-activations are saved, not recomputed.
 """
 from __future__ import annotations
 
@@ -71,16 +71,16 @@ class FusedGatedMLPFunction(Function):
                 inplace_backward: bool = True) -> Tensor:
         tp_chunk_fwd, tp_chunk_bwd = tp_chunk_rows
         need_bwd = any(ctx.needs_input_grad)
-        if need_bwd:
-            h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True, act=act)
-        else:
-            h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False, act=act)
-            g = u = None
         # With the intermediate dimension sharded, every rank holds a partial sum
         # of y; the output bias is added once, by the rank that owns column 0.
         owner = tp_group is None or shard.col0 == 0
         bias, res = (b_down if owner else None), (residual if owner else None)
         if tp_group is not None and tp_chunk_fwd > 0:
+            if need_bwd:
+                h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True, act=act)
+            else:
+                h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False, act=act)
+                g = u = None
             # Down projection chunk by chunk over the token rows: chunk i's all-reduce
             # (NCCL, on its own stream) runs beside chunk i+1's GEMM.
             y = torch.empty((x.shape[0], W_down.shape[0]), dtype=x.dtype, device=x.device)
@@ -91,7 +91,9 @@ class FusedGatedMLPFunction(Function):
                 tp_group, tp_chunk_fwd, limit)
             parallel.wait_all(works)
         else:
-            y = kernels.down_fwd(h, W_down, bias, res)
+            # both kernels from one library call
+            y, h, g, u = kernels.mlp_fwd(x, W_gate, b_gate, W_up, b_up, W_down, bias, drop=drop, shard=shard,
+                                         save=need_bwd, act=act, residual=res)
             if tp_group is not None:
                 parallel.all_reduce_sum(y, tp_group)
         if need_bwd:
@@ -108,8 +110,6 @@ class FusedGatedMLPFunction(Function):
         need = ctx.needs_input_grad
         dy = dy.contiguous()
         dx = dW_gate = db_gate = dW_up = db_up = dW_down = db_down = None
-        limit = _SmLimit(x.device, ctx.tp_comm_sms)
-        works = []
         need_hidden = need[0] or need[1] or need[2] or need[3] or need[4]
         if need_hidden:
             if ctx.consumed:
@@ -117,32 +117,59 @@ class FusedGatedMLPFunction(Function):
                     "FusedGatedMLP: this graph's saved gate/up pre-activations were overwritten by an earlier "
                     "backward pass (inplace_backward=True writes d_gate / d_up over them). Set "
                     "module.inplace_backward = False to run backward more than once over one forward.")
-            # d_gate / d_up land in the buffers G / U were saved in: two [M, N] allocations fewer.
+            ctx.consumed = ctx.inplace_backward
+        # The bias gradients are column sums of d_gate / d_up / dy; the weight-gradient GEMMs deliver
+        # them on the side (their A operand is exactly that matrix, transposed). Only a caller that
+        # wants a bias gradient without its weight gradient pays a separate pass.
+        want_bg, want_bu, want_bd = need[2] and ctx.has_bias[0], need[4] and ctx.has_bias[1], need[6] and ctx.has_bias[2]
+        want_wgu = need[1] or need[3]
+        works = []
+        if ctx.tp_group is not None and ctx.tp_chunk_rows > 0 and need[0]:
+            # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
+            limit = _SmLimit(x.device, ctx.tp_comm_sms)
             d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act,
                                                inplace=ctx.inplace_backward)
-            ctx.consumed = ctx.inplace_backward
-            if need[0]:
-                if ctx.tp_group is not None and ctx.tp_chunk_rows > 0:
-                    # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
-                    dx = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
-                    works = parallel.overlapped_all_reduce(
-                        dx, lambda r0, r1: kernels.bwd_dx(d_gate[r0:r1], d_up[r0:r1], W_gate, W_up, out=dx[r0:r1],
-                                                          tuning=limit.tuning),
-                        ctx.tp_group, ctx.tp_chunk_rows, limit)
-                    limit(True)
+            dx = torch.empty((x.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+            works = parallel.overlapped_all_reduce(
+                dx, lambda r0, r1: kernels.bwd_dx(d_gate[r0:r1], d_up[r0:r1], W_gate, W_up, out=dx[r0:r1],
+                                                  tuning=limit.tuning),
+                ctx.tp_group, ctx.tp_chunk_rows, limit)
+            limit(True)
+            if want_wgu:
+                if want_bg or want_bu:
+                    dW_gate, dW_up, db_gate, db_up = kernels.bwd_dw_gate_up(d_gate, d_up, x, tuning=limit.tuning,
+                                                                            bias_grads=True)
                 else:
-                    dx = kernels.bwd_dx(d_gate, d_up, W_gate, W_up)
-                    if ctx.tp_group is not None:
-                        parallel.all_reduce_sum(dx, ctx.tp_group)
-            if need[1] or need[3]:
-                dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x, tuning=limit.tuning)
-            if need[2] and ctx.has_bias[0]:
-                db_gate = kernels.colsum(d_gate)
-            if need[4] and ctx.has_bias[1]:
-                db_up = kernels.colsum(d_up)
-        if need[5]:
-            dW_down = kernels.bwd_dw_down(dy, h, tuning=limit.tuning)
-        if need[6] and ctx.has_bias[2]:
+                    dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x, tuning=limit.tuning)
+            if need[5]:
+                if want_bd:
+                    dW_down, db_down = kernels.bwd_dw_down(dy, h, tuning=limit.tuning, bias_grad=True)
+                else:
+                    dW_down = kernels.bwd_dw_down(dy, h, tuning=limit.tuning)
+        else:
+            # every kernel of the pass from one library call
+            r = kernels.mlp_bwd(dy, x, W_gate, W_up, W_down, g, u, h, drop=ctx.drop, shard=ctx.shard, act=ctx.act,
+                                want_dx=bool(need[0]), want_dw_gate_up=bool(want_wgu), want_dw_down=bool(need[5]),
+                                want_db_gate=bool(want_bg and want_wgu), want_db_up=bool(want_bu and want_wgu),
+                                want_db_down=bool(want_bd and need[5]), inplace=ctx.inplace_backward) \
+                if (need_hidden or need[5]) else {}
+            dx, dW_gate, dW_up, dW_down = r.get("dx"), r.get("dw_gate"), r.get("dw_up"), r.get("dw_down")
+            db_gate, db_up, db_down = r.get("db_gate"), r.get("db_up"), r.get("db_down")
+            d_gate, d_up = r.get("d_gate"), r.get("d_up")
+            if dx is not None and ctx.tp_group is not None:
+                parallel.all_reduce_sum(dx, ctx.tp_group)
+        # bias gradients asked for without their weight gradients: stand-alone column sums
+        if (want_bg or want_bu) and not want_wgu:
+            if d_gate is None:
+                d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act,
+                                                   inplace=ctx.inplace_backward)
+            db_gate = kernels.colsum(d_gate) if want_bg else None
+            db_up = kernels.colsum(d_up) if want_bu else None
+        if not want_bg:
+            db_gate = None
+        if not want_bu:
+            db_up = None
+        if want_bd and not need[5]:
             db_down = kernels.colsum(dy)
         parallel.wait_all(works)
         d_res = dy if (len(need) > 11 and need[11]) else None  # y = ... + residual

@@ -6,6 +6,7 @@ kernel on torch's current stream. They never compute anything themselves.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 from dataclasses import dataclass
 
@@ -36,6 +37,14 @@ class Shard:
 
 NO_DROPOUT = Dropout()
 NO_SHARD = Shard()
+
+
+_SAME_DEVICE = contextlib.nullcontext()
+
+
+def _on(dev: torch.device):
+    """Context that makes `dev` current for a library call; free when it already is."""
+    return _SAME_DEVICE if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
 
 
 def act_code(act: str) -> int:
@@ -87,7 +96,7 @@ def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     u = torch.empty((M, N), dtype=dt, device=dev) if save else None
     if M > 0:
         prob = _problem(M, K, N, dt, drop, shard, act, tuning)
-        with torch.cuda.device(dev):
+        with _on(dev):
             check(load().gmlp_hidden_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up),
                                          ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
     return (h, g, u) if save else h
@@ -112,10 +121,85 @@ def down_fwd(h: Tensor, w_down: Tensor, b_down: Tensor | None, residual: Tensor 
     y = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
         prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
-        with torch.cuda.device(dev):
+        with _on(dev):
             check(load().gmlp_down_fwd(C.byref(prob), ptr(h), ptr(w_down), ptr(b_down), ptr(residual),
                                        ptr(y), stream_of(h)))
     return y
+
+
+def mlp_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None, w_down: Tensor,
+            b_down: Tensor | None, drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False,
+            act: str = "silu", residual: Tensor | None = None, tuning: int = 0):
+    """The whole forward pass in one library call: (y, h, g, u) with g = u = None unless save=True."""
+    dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
+    dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
+    x, w_gate, w_up, w_down = _c(x), _c(w_gate), _c(w_up), _c(w_down)
+    b_gate, b_up, b_down, residual = _c(b_gate), _c(b_up), _c(b_down), _c(residual)
+    M, K = x.shape
+    N = w_gate.shape[0]
+    h = torch.empty((M, N), dtype=dt, device=dev)
+    g = torch.empty((M, N), dtype=dt, device=dev) if save else None
+    u = torch.empty((M, N), dtype=dt, device=dev) if save else None
+    y = torch.empty((M, K), dtype=dt, device=dev)
+    if M > 0:
+        prob = _problem(M, K, N, dt, drop, shard, act, tuning)
+        with _on(dev):
+            check(load().gmlp_mlp_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),
+                                      ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(g), ptr(u), ptr(y),
+                                      stream_of(x)))
+    return y, h, g, u
+
+
+def mlp_bwd(dy: Tensor, x: Tensor, w_gate: Tensor, w_up: Tensor, w_down: Tensor, g: Tensor, u: Tensor, h: Tensor,
+            drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, act: str = "silu", want_dx: bool = True,
+            want_dw_gate_up: bool = True, want_dw_down: bool = True, want_db_gate: bool = False,
+            want_db_up: bool = False, want_db_down: bool = False, inplace: bool = False, tuning: int = 0):
+    """The whole backward pass in one library call. Returns a dict with the gradients asked for
+    ("dx", "dw_gate", "dw_up", "dw_down", "db_gate", "db_up", "db_down") and "d_gate" / "d_up" when they were
+    computed. Bias gradients come out of the weight-gradient kernels, so want_db_gate / want_db_up need
+    want_dw_gate_up and want_db_down needs want_dw_down. inplace=True writes d_gate / d_up over g / u."""
+    dev = require_cuda(dy, x, w_gate, w_up, w_down, g, u, h)
+    dt = _same_dtype(dy, x, w_gate, w_up, w_down, g, u, h)
+    if (want_db_gate or want_db_up) and not want_dw_gate_up or (want_db_down and not want_dw_down):
+        raise ValueError("bias gradients are produced by the weight-gradient kernels: ask for those too")
+    if inplace and not (g.is_contiguous() and u.is_contiguous()):
+        raise ValueError("inplace=True needs contiguous g and u")
+    dy, x, w_gate, w_up, w_down, g, u, h = (_c(t) for t in (dy, x, w_gate, w_up, w_down, g, u, h))
+    M, K = dy.shape
+    N = w_down.shape[1]
+    new = lambda *shape: torch.empty(shape, dtype=dt, device=dev)
+    out = {}
+    hidden = want_dx or want_dw_gate_up
+    if hidden:
+        out["d_gate"] = g if inplace else new(M, N)
+        out["d_up"] = u if inplace else new(M, N)
+    if want_dx:
+        out["dx"] = new(M, K)
+    if want_dw_gate_up:
+        out["dw_gate"], out["dw_up"] = new(N, K), new(N, K)
+    if want_dw_down:
+        out["dw_down"] = new(K, N)
+    if want_db_gate:
+        out["db_gate"] = new(N)
+    if want_db_up:
+        out["db_up"] = new(N)
+    if want_db_down:
+        out["db_down"] = new(K)
+    if M == 0:
+        for k_, t in out.items():
+            if k_ not in ("d_gate", "d_up"):
+                t.zero_()
+        return out
+    prob = _problem(M, K, N, dt, drop, shard, act, tuning)
+    o = out.get
+    with _on(dev):
+        scratch = bias_grad_scratch(K, N, dt, dev) if (want_db_gate or want_db_up or want_db_down) else None
+        check(load().gmlp_mlp_bwd(
+            C.byref(prob), ptr(dy), ptr(x), ptr(w_gate), ptr(w_up), ptr(w_down), ptr(g), ptr(u), ptr(h),
+            ptr(o("d_gate")), ptr(o("d_up")), ptr(o("dx")), ptr(o("dw_gate")), ptr(o("dw_up")), ptr(o("dw_down")),
+            ptr(o("db_gate")), ptr(o("db_up")), ptr(o("db_down")), ptr(scratch),
+            0 if scratch is None else scratch.numel() * scratch.element_size(), stream_of(dy)))
+    return out
 
 
 def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT,
@@ -135,7 +219,7 @@ def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout 
     d_up = u if inplace else torch.empty((M, N), dtype=dt, device=dev)
     if M > 0:
         prob = _problem(M, K, N, dt, drop, shard, act, tuning)
-        with torch.cuda.device(dev):
+        with _on(dev):
             check(load().gmlp_bwd_dhidden(C.byref(prob), ptr(dy), ptr(w_down), ptr(g), ptr(u),
                                           ptr(d_gate), ptr(d_up), stream_of(dy)))
     return d_gate, d_up
@@ -152,7 +236,7 @@ def bwd_dact(dh: Tensor, g: Tensor, u: Tensor, drop: Dropout = NO_DROPOUT, shard
     d_up = torch.empty((M, N), dtype=dt, device=dev)
     if M > 0:
         prob = _problem(M, 8, N, dt, drop, shard, act)
-        with torch.cuda.device(dev):
+        with _on(dev):
             check(load().gmlp_bwd_dact(C.byref(prob), ptr(dh), ptr(g), ptr(u), ptr(d_gate), ptr(d_up),
                                        stream_of(dh)))
     return d_gate, d_up
@@ -169,44 +253,84 @@ def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tens
     dx = _out_buffer(out, (M, K), dt, dev)
     if M > 0:
         prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
-        with torch.cuda.device(dev):
+        with _on(dev):
             check(load().gmlp_bwd_dx(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(w_gate), ptr(w_up),
                                      ptr(dx), stream_of(d_gate)))
     return dx
 
 
-def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor, tuning: int = 0):
-    """(dW_gate, dW_up) = (d_gate^T x, d_up^T x)."""
+_bias_scratch = {}
+
+
+def bias_grad_scratch(K: int, N: int, dt: torch.dtype, dev: torch.device) -> Tensor:
+    """Scratch of the fused bias-gradient sums (arrival counters, kept zero by the kernels, and fp32 partial
+    sums) for a module of hidden size K and intermediate size N. One buffer per (device, stream, shape): calls
+    on one stream are ordered, so they can share it. A new buffer is made when a kernel has given up a wait
+    since (the counters may then be dirty)."""
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream, K, N, dt, _lib.scratch_epoch())
+    buf = _bias_scratch.get(key)
+    if buf is None:
+        prob = _problem(8, K, N, dt, NO_DROPOUT, NO_SHARD)
+        nbytes = load().gmlp_bias_grad_scratch_bytes(C.byref(prob))
+        buf = torch.zeros(((nbytes + 3) // 4,), dtype=torch.int32, device=dev)
+        if len(_bias_scratch) > 64:
+            _bias_scratch.clear()
+        _bias_scratch[key] = buf
+    return buf
+
+
+def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor, tuning: int = 0, bias_grads: bool = False):
+    """(dW_gate, dW_up) = (d_gate^T x, d_up^T x); with bias_grads=True also (db_gate, db_up), the column
+    sums of d_gate and d_up, taken inside the same kernel."""
     dev = require_cuda(d_gate, d_up, x)
     dt = _same_dtype(d_gate, d_up, x)
     d_gate, d_up, x = _c(d_gate), _c(d_up), _c(x)
     M, N = d_gate.shape
     K = x.shape[1]
     if M == 0:
-        return (torch.zeros((N, K), dtype=dt, device=dev), torch.zeros((N, K), dtype=dt, device=dev))
+        z = lambda *s: torch.zeros(s, dtype=dt, device=dev)
+        return (z(N, K), z(N, K), z(N), z(N)) if bias_grads else (z(N, K), z(N, K))
     dw_gate = torch.empty((N, K), dtype=dt, device=dev)
     dw_up = torch.empty((N, K), dtype=dt, device=dev)
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
-    with torch.cuda.device(dev):
-        check(load().gmlp_bwd_dw_gate_up(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(x), ptr(dw_gate),
-                                         ptr(dw_up), stream_of(x)))
-    return dw_gate, dw_up
+    if not bias_grads:
+        with _on(dev):
+            check(load().gmlp_bwd_dw_gate_up(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(x), ptr(dw_gate),
+                                             ptr(dw_up), stream_of(x)))
+        return dw_gate, dw_up
+    db_gate = torch.empty((N,), dtype=dt, device=dev)
+    db_up = torch.empty((N,), dtype=dt, device=dev)
+    with _on(dev):
+        scratch = bias_grad_scratch(K, N, dt, dev)
+        check(load().gmlp_bwd_dw_gate_up_bias(C.byref(prob), ptr(d_gate), ptr(d_up), ptr(x), ptr(dw_gate), ptr(dw_up),
+                                              ptr(db_gate), ptr(db_up), ptr(scratch),
+                                              scratch.numel() * scratch.element_size(), stream_of(x)))
+    return dw_gate, dw_up, db_gate, db_up
 
 
-def bwd_dw_down(dy: Tensor, h: Tensor, tuning: int = 0) -> Tensor:
-    """dW_down = dy^T h."""
+def bwd_dw_down(dy: Tensor, h: Tensor, tuning: int = 0, bias_grad: bool = False):
+    """dW_down = dy^T h; with bias_grad=True returns (dW_down, db_down), db_down = column sums of dy from
+    the same kernel."""
     dev = require_cuda(dy, h)
     dt = _same_dtype(dy, h)
     dy, h = _c(dy), _c(h)
     M, K = dy.shape
     N = h.shape[1]
     if M == 0:
-        return torch.zeros((K, N), dtype=dt, device=dev)
+        dw = torch.zeros((K, N), dtype=dt, device=dev)
+        return (dw, torch.zeros((K,), dtype=dt, device=dev)) if bias_grad else dw
     dw = torch.empty((K, N), dtype=dt, device=dev)
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, tuning=tuning)
-    with torch.cuda.device(dev):
-        check(load().gmlp_bwd_dw_down(C.byref(prob), ptr(dy), ptr(h), ptr(dw), stream_of(dy)))
-    return dw
+    if not bias_grad:
+        with _on(dev):
+            check(load().gmlp_bwd_dw_down(C.byref(prob), ptr(dy), ptr(h), ptr(dw), stream_of(dy)))
+        return dw
+    db = torch.empty((K,), dtype=dt, device=dev)
+    with _on(dev):
+        scratch = bias_grad_scratch(K, N, dt, dev)
+        check(load().gmlp_bwd_dw_down_bias(C.byref(prob), ptr(dy), ptr(h), ptr(dw), ptr(db), ptr(scratch),
+                                           scratch.numel() * scratch.element_size(), stream_of(dy)))
+    return dw, db
 
 
 DECODE_MAX_TOKENS = 64
@@ -248,7 +372,7 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     h = torch.empty((M, N), dtype=dt, device=dev)
     y = _out_buffer(out, (M, K), dt, dev)
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(load().gmlp_decode_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),
                                      ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(y), ptr(scratch),
                                      scratch.numel() * scratch.element_size(), stream_of(x)))
@@ -266,7 +390,7 @@ def colsum(src: Tensor) -> Tensor:
     nbytes = lib.gmlp_colsum_scratch_bytes(rows, cols)
     scratch = torch.empty((nbytes // 4,), dtype=torch.float32, device=dev)
     dst = torch.empty((cols,), dtype=src.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(lib.gmlp_colsum(rows, cols, dtype_code(src.dtype), ptr(src), src.stride(0), ptr(scratch),
                               nbytes, ptr(dst), stream_of(src)))
     return dst
@@ -293,7 +417,7 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool = False, b_mn: bool = False, bias: Ten
     if K != Kb:
         raise ValueError(f"reduction extents differ: {K} vs {Kb}")
     c = torch.empty((M, N), dtype=dt, device=dev)
-    with torch.cuda.device(dev):
+    with _on(dev):
         check(load().gmlp_gemm(dtype_code(dt), int(a_mn), int(b_mn), M, N, K, ptr(a), a.stride(0), ptr(b),
                                b.stride(0), ptr(c), c.stride(0), ptr(bias), stream_of(a)))
     return c
