@@ -96,6 +96,26 @@ int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, void* h,
                     void* g_save, void* u_save, void* stream);
 
+/* ---- RMSNorm ahead of the MLP (no counterpart in the reference, whose module starts at
+ * the projections, src/triton_gated_mlp/gated_mlp.py:224-227; this is the step that
+ * precedes it in a Llama block: y = MLP(x / rms(x) * weight)) ----
+ * gmlp_rms_rowscale: rs[m] = 1 / sqrt(mean_k x[m,k]^2 + eps) as fp32 [M]; when xn is not
+ * NULL also xn[m,k] = x[m,k] * rs[m] ([M,K], contiguous, x's type). x has row pitch ld.
+ * gmlp_hidden_fwd_scaled: gmlp_hidden_fwd with both accumulators multiplied by
+ * row_scale[row] (fp32 [M], may be NULL) before the bias is added. With
+ * W' = W * diag(norm weight) folded on the host this gives
+ * act((x / rms * weight) W_gate^T + b_gate) * (... W_up^T + b_up) without the normalised
+ * activations ever being written.
+ * gmlp_rms_bwd: the backward of xn = x * rs:
+ * dx[m,:] = rs[m] * (dxn[m,:] - xn[m,:] * mean_k(dxn[m,k] * xn[m,k])). */
+int gmlp_rms_rowscale(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, float eps,
+                      float* rs, void* xn, void* stream);
+int gmlp_hidden_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                           const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                           void* h, void* g_save, void* u_save, void* stream);
+int gmlp_rms_bwd(int64_t M, int64_t K, int32_t dtype, const void* dxn, const void* xn, const float* rs,
+                 void* dx, void* stream);
+
 /* y[M,K] = h W_down^T (+ b_down) (+ residual[M,K]).
  * Replaces self.down_proj(hidden_states) (src/triton_gated_mlp/gated_mlp.py:236). */
 int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
@@ -232,6 +252,13 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
                     const void* b_down, const void* residual, void* h, void* y, void* scratch,
                     size_t scratch_bytes, void* stream);
+
+/* gmlp_decode_fwd with the gate / up accumulators multiplied by row_scale[token] (fp32 [M],
+ * may be NULL) before the bias: the RMSNorm prologue of gmlp_hidden_fwd_scaled on the decode path. */
+int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                           const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                           const void* w_down, const void* b_down, const void* residual, void* h, void* y,
+                           void* scratch, size_t scratch_bytes, void* stream);
 
 /* mask[M,N] (one byte per element, 1 = kept) for the problem's dropout settings:
  * the device side of the bit-exact mask check. */

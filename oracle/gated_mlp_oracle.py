@@ -144,6 +144,36 @@ def backward(x, w_gate, b_gate, w_up, b_up, w_down, b_down, dy, keep_scale: Opti
     return out
 
 
+# -------------------------------------------------------------- RMSNorm ----
+# The step before the MLP in a Llama block. The reference has no norm; the definition
+# restated here is torch.nn.RMSNorm's: x * rsqrt(mean(x^2, -1) + eps) * weight. Pinned by the
+# fixture norm_mlp_bf16 (torch.nn.RMSNorm followed by the reference's EagerGatedMLP).
+def rmsnorm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight
+
+
+def rmsnorm_backward(x: Tensor, weight: Tensor, eps: float, dout: Tensor):
+    """(dx, dweight) of rmsnorm for upstream gradient dout (closed form)."""
+    rs = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    xn = x * rs
+    dxn = dout * weight
+    dx = rs * (dxn - xn * (dxn * xn).mean(-1, keepdim=True))
+    return dx, (dout * xn).reshape(-1, x.shape[-1]).sum(0)
+
+
+def norm_forward_backward(case: "Case", norm_weight: Tensor, eps: float) -> Dict[str, Tensor]:
+    """fp32 oracle outputs of y = MLP(rmsnorm(x)): {"y", "dx", "dinput_norm_weight", "dgate_proj.weight", ...}."""
+    x, wg, bg, wu, bu, wd, bd, dy = case.f32()
+    w = norm_weight.float()
+    xn = rmsnorm(x, w, eps)
+    out = {"y": forward(xn, wg, bg, wu, bu, wd, bd)}
+    grads = backward(xn, wg, bg, wu, bu, wd, bd, dy)
+    dx, dw = rmsnorm_backward(x, w, eps, grads.pop("dx"))
+    out.update(grads)
+    out["dx"], out["dinput_norm_weight"] = dx, dw
+    return out
+
+
 def keep_scale_tensor(rows: int, cols: int, p: float, seed: int, offset: int, *, row0: int = 0,
                       col0: int = 0, n_global: Optional[int] = None) -> Optional[Tensor]:
     """mask * 1/(1-p) as fp32, or None when p == 0."""

@@ -100,6 +100,33 @@ def module_case(ref, name, K, N, bias, x_shape, dt, seed_w, seed_x, seed_dy, x_u
     print(name, {k: v.shape for k, v in out.items() if hasattr(v, "shape") and v.ndim})
 
 
+def norm_case(ref, name):
+    """A Llama block's norm + MLP: torch.nn.RMSNorm followed by the reference's eager module, through autograd."""
+    dt = torch.bfloat16
+    K, N, M, eps = 128, 256, 72, 1e-5
+    torch.manual_seed(60)
+    m = ref.EagerGatedMLP(hidden_size=K, intermediate_size=N, bias=True, dropout_p=0.0)
+    norm = torch.nn.RMSNorm(K, eps=eps)
+    with torch.no_grad():
+        norm.weight.copy_(rounded(1.0 + 0.2 * torch.randn(K), dt))
+        for p in m.parameters():
+            p.copy_(rounded(p, dt))
+    torch.manual_seed(61)
+    x = rounded(torch.randn((M, K)) * 1.7, dt).requires_grad_(True)
+    torch.manual_seed(62)
+    dy = rounded(torch.randn((M, K)) * 0.1, dt)
+    y = m(norm(x))
+    y.backward(dy)
+    out = {"x": np16(x.detach(), dt), "dy": np16(dy, dt), "y": y.detach().numpy(), "dx": x.grad.numpy(),
+           "norm_weight": np16(norm.weight.detach(), dt), "dinput_norm_weight": norm.weight.grad.numpy(),
+           "meta.dtype": np.array("bfloat16"), "meta.eps": np.array(eps), "meta.bias": np.array(True)}
+    for pname, p in m.named_parameters():
+        out["p." + pname] = np16(p.detach(), dt)
+        out["d" + pname] = p.grad.numpy()
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "ok")
+
+
 def ops_case(ref, name):
     """The known-answer recipe of the reference's tests/test_gated_mlp_bwd.py:96-123 through its own
     eager_fwd / eager_bwd."""
@@ -138,6 +165,7 @@ def main():
         module_case(ref, f"act_{act}_bf16", K=64, N=128, bias=True, x_shape=(40, 64), dt=torch.bfloat16,
                     seed_w=30 + i, seed_x=40 + i, seed_dy=50 + i, x_uniform=False, dy_std=0.1, hidden_act=act)
     ops_case(ref, "ops_closed_form_bf16")
+    norm_case(ref, "norm_mlp_bf16")
 
 
 if __name__ == "__main__":

@@ -60,3 +60,21 @@ def test_parity_metric():
     orc.assert_parity((big + 0.125).to(torch.bfloat16), big, "next bf16 above 16")
     with pytest.raises(AssertionError):
         orc.assert_parity(big + 0.5, big, "too far")
+
+
+def test_oracle_rmsnorm_matches_torch_rmsnorm_plus_reference_module():
+    """Fixture norm_mlp_bf16: torch.nn.RMSNorm followed by the reference's EagerGatedMLP, through autograd."""
+    t, meta, _ = load_golden("norm_mlp_bf16")
+    f = lambda v: None if v is None else v.float()
+    wg, bg, wu, bu, wd, bd = [f(v) for v in golden_params(t)]
+    case = orc.Case(t["x"], t["p.gate_proj.weight"], t["p.gate_proj.bias"], t["p.up_proj.weight"],
+                    t["p.up_proj.bias"], t["p.down_proj.weight"], t["p.down_proj.bias"], t["dy"])
+    got = orc.norm_forward_backward(case, t["norm_weight"], float(meta["eps"]))
+    for k, v in got.items():
+        torch.testing.assert_close(v, t[k], rtol=3e-5, atol=3e-5, msg=lambda m, k=k: f"{k}: {m}")
+    # and the norm alone against torch's module
+    norm = torch.nn.RMSNorm(case.x.shape[-1], eps=float(meta["eps"]))
+    with torch.no_grad():
+        norm.weight.copy_(t["norm_weight"].float())
+    torch.testing.assert_close(orc.rmsnorm(case.x.float(), t["norm_weight"].float(), float(meta["eps"])),
+                               norm(case.x.float()), rtol=1e-6, atol=1e-6)

@@ -19,7 +19,8 @@ ACT_CODES = {"silu": 0, "swish": 0, "no_act": 1, "relu": 2, "gelu": 3, "sigmoid"
 
 # Every symbol include/gmlp.h declares; tests check that the library exports all of them.
 EXPORTS = (
-    "gmlp_hidden_fwd", "gmlp_down_fwd", "gmlp_mlp_fwd", "gmlp_mlp_bwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
+    "gmlp_hidden_fwd", "gmlp_hidden_fwd_scaled", "gmlp_rms_rowscale", "gmlp_rms_bwd", "gmlp_decode_fwd_scaled",
+    "gmlp_down_fwd", "gmlp_mlp_fwd", "gmlp_mlp_bwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_bias_grad_scratch_bytes", "gmlp_bwd_dw_gate_up_bias",
     "gmlp_bwd_dw_down_bias", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group", "gmlp_set_sm_limit",
@@ -51,6 +52,10 @@ def _declare(lib: C.CDLL) -> None:
     vp, i32, i64, u8p = C.c_void_p, C.c_int32, C.c_int64, C.c_void_p
     pp = C.POINTER(Problem)
     lib.gmlp_hidden_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_hidden_fwd_scaled.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.gmlp_rms_rowscale.argtypes = [i64, i64, i32, vp, i64, C.c_float, vp, vp, vp]
+    lib.gmlp_rms_bwd.argtypes = [i64, i64, i32, vp, vp, vp, vp, vp]
+    lib.gmlp_decode_fwd_scaled.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
     lib.gmlp_down_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp]
     lib.gmlp_mlp_fwd.argtypes = [pp] + [vp] * 13
     lib.gmlp_mlp_bwd.argtypes = [pp] + [vp] * 18 + [C.c_size_t, vp]

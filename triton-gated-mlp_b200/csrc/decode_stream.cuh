@@ -41,6 +41,7 @@ struct DecodeArgs {
   const void* bias1;  // up bias (DUAL)
   void* out;          // H[M, rows] or Y[M, rows]
   const void* residual;  // optional [M, rows] added to the output (down projection only)
+  const float* row_scale;  // optional [M] per-token factors on both accumulators before the bias (DUAL only)
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
   int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry, and on exit
@@ -95,10 +96,19 @@ __device__ __forceinline__ long long unit_start(long long c, long long total, lo
 // with the activation a compile-time constant.
 template <int ACT, int COUNT, typename T>
 __device__ __forceinline__ void store_gated(T* po, long long ld, int M, const float* gate, const float* up,
-                                            float b0, float b1) {
+                                            float b0, float b1, const float* row_scale) {
+  if (row_scale == nullptr) {
 #pragma unroll
-  for (int m = 0; m < COUNT; ++m)
-    if (m < M) po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] + b0) * (up[m] + b1));
+    for (int m = 0; m < COUNT; ++m)
+      if (m < M) po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] + b0) * (up[m] + b1));
+  } else {
+#pragma unroll
+    for (int m = 0; m < COUNT; ++m)
+      if (m < M) {
+        const float r = row_scale[m];  // the same address for every lane: one broadcast load
+        po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] * r + b0) * (up[m] * r + b1));
+      }
+  }
 }
 
 template <int MPAD, bool DUAL, typename T>
@@ -331,15 +341,15 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         T* const po = out + wrow;
         if (DUAL) {
           switch (args.act) {
-            case ACT_SILU: store_gated<ACT_SILU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
-            case ACT_NONE: store_gated<ACT_NONE, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
-            case ACT_RELU: store_gated<ACT_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
-            case ACT_GELU: store_gated<ACT_GELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_SILU: store_gated<ACT_SILU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            case ACT_NONE: store_gated<ACT_NONE, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            case ACT_RELU: store_gated<ACT_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            case ACT_GELU: store_gated<ACT_GELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
             case ACT_SIGMOID:
-              store_gated<ACT_SIGMOID, MPAD>(po, args.ld_out, args.M, first, second, b0, b1);
+              store_gated<ACT_SIGMOID, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale);
               break;
-            case ACT_TANH: store_gated<ACT_TANH, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
-            default: store_gated<ACT_LEAKY_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1); break;
+            case ACT_TANH: store_gated<ACT_TANH, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            default: store_gated<ACT_LEAKY_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
           }
         } else {
           const T* const pr = residual ? residual + wrow : nullptr;

@@ -61,6 +61,75 @@ dropout_mask_kernel(uint8_t* __restrict__ mask, long long M, long long N, Dropou
   }
 }
 
+// RMSNorm ahead of the MLP (the step before it in a Llama block). One warp per token row.
+//   rs[m] = 1 / sqrt(mean_k x[m,k]^2 + eps)          (fp32)
+//   xn[m,k] = x[m,k] * rs[m]                         (optional, in x's type)
+// The forward pass needs only rs: the gate/up kernel multiplies its accumulators by rs[row]
+// (the norm's weight is folded into W_gate / W_up), so the normalised activations are never
+// written. Training keeps xn for the backward pass below.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_rowscale_kernel(const T* __restrict__ x, long long M, long long K, long long ld, float eps,
+                    float* __restrict__ rs, T* __restrict__ xn) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const T* xr = x + row * ld;
+  float ss = 0.f;
+  for (long long k = lane * 8LL; k < K; k += 256) {
+    float v[8];
+    load8(xr + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float r = rsqrtf(ss / static_cast<float>(K) + eps);
+  if (lane == 0) rs[row] = r;
+  if (xn != nullptr) {
+    T* out = xn + row * K;
+    for (long long k = lane * 8LL; k < K; k += 256) {
+      float v[8];
+      load8(xr + k, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= r;
+      store8(out + k, v);
+    }
+  }
+}
+
+// Backward of xn = x * rs: dx[m,:] = rs[m] * (dxn[m,:] - xn[m,:] * mean_k(dxn[m,k] * xn[m,k])).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_bwd_kernel(const T* __restrict__ dxn, const T* __restrict__ xn, const float* __restrict__ rs,
+               long long M, long long K, T* __restrict__ dx) {
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
+  if (row >= M) return;
+  const T* a = dxn + row * K;
+  const T* b = xn + row * K;
+  float dot = 0.f;
+  for (long long k = lane * 8LL; k < K; k += 256) {
+    float u[8], v[8];
+    load8(a + k, u);
+    load8(b + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot = fmaf(u[i], v[i], dot);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  const float c = dot / static_cast<float>(K), r = rs[row];
+  T* out = dx + row * K;
+  for (long long k = lane * 8LL; k < K; k += 256) {
+    float u[8], v[8];
+    load8(a + k, u);
+    load8(b + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) u[i] = r * (u[i] - v[i] * c);
+    store8(out + k, u);
+  }
+}
+
 // Column sums, pass 1: block (cb, rb) sums rows [rb*rows_per_block, ...) of the
 // 128 columns starting at cb*128 and writes them to partial[rb, :].
 constexpr int COLSUM_COLS = 128;

@@ -51,6 +51,8 @@ struct GemmArgs {
   const void* in1;
   const void* bias0;
   const void* bias1;
+  const float* row_scale;  // EPI_SWIGLU: optional [M] factors applied to both accumulators before the bias
+                           // (1 / rms of the input row when an RMSNorm precedes the MLP)
   long long ld_out;  // row pitch (elements) of out*
   long long ld_in;   // row pitch (elements) of in*
   DropoutParams drop;
@@ -524,6 +526,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMap
     const bool save = args.out1 != nullptr;  // keep the pre-activations for the backward pass
     const uint32_t buf_a = stage, buf_b = stage + STORE_STAGE_BYTES / 2;
     const long long grow = args.drop.row0_global + row;
+    const bool scaled = args.row_scale != nullptr;
+    const float rsv = (scaled && row_ok) ? args.row_scale[row] : 1.0f;
     if (lane == 0) bulk_wait_group_read<0>();
     __syncwarp();
     uint4 qu[4];  // U waits in registers until H has left its block
@@ -541,6 +545,13 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMap
         for (int i = 0; i < 8; ++i) {
           g[i] = __uint_as_float(rg[j * 8 + i]);
           u[i] = __uint_as_float(ru[j * 8 + i]);
+        }
+        if (scaled) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            g[i] *= rsv;
+            u[i] *= rsv;
+          }
         }
         if (gc < N) {
           if (bias0) {

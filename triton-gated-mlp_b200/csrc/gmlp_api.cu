@@ -193,6 +193,7 @@ struct Epilogue {
   const void* in1 = nullptr;
   const void* bias0 = nullptr;
   const void* bias1 = nullptr;
+  const float* row_scale = nullptr;
   int64_t ld_out = 0;
   int64_t ld_in = 0;
   DropoutParams drop = {};
@@ -314,6 +315,7 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.in1 = ep.in1;
   args.bias0 = ep.bias0;
   args.bias1 = ep.bias1;
+  args.row_scale = ep.row_scale;
   args.ld_out = ep.ld_out;
   args.ld_in = ep.ld_in;
   args.drop = ep.drop;
@@ -469,9 +471,9 @@ int gmlp_status_read(int* value) {
   return GMLP_OK;
 }
 
-int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
-                    const void* b_gate, const void* w_up, const void* b_up, void* h,
-                    void* g_save, void* u_save, void* stream) {
+int gmlp_hidden_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                           const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                           void* h, void* g_save, void* u_save, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if ((rc = check_ptrs({x, w_gate, w_up, h}))) return rc;
@@ -480,6 +482,8 @@ int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   if ((b_gate && !aligned16(b_gate)) || (b_up && !aligned16(b_up)) ||
       (g_save && (!aligned16(g_save) || !aligned16(u_save))))
     return fail(GMLP_ERR_ALIGN, "bias / save buffers must be 16-byte aligned");
+  if (row_scale && (reinterpret_cast<uintptr_t>(row_scale) & 3u) != 0)
+    return fail(GMLP_ERR_ALIGN, "row_scale must be 4-byte aligned");
   const DeviceInfo* dev;
   if ((rc = device_info(&dev))) return rc;
   const Operand a{x, p->M, p->K, p->K, false};
@@ -491,11 +495,68 @@ int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   ep.out2 = u_save;
   ep.bias0 = b_gate;
   ep.bias1 = b_up;
+  ep.row_scale = row_scale;
   ep.ld_out = p->N;
   ep.drop = make_dropout(p);
   ep.act = p->act;
   return launch_gemm<256, false, false, EPI_SWIGLU>(dev, p->dtype, p->M, p->N, a, nullptr, bg, &bu,
                                                     0, 1, ep, p->tuning, static_cast<cudaStream_t>(stream));
+}
+
+int gmlp_hidden_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, void* h,
+                    void* g_save, void* u_save, void* stream) {
+  return gmlp_hidden_fwd_scaled(p, x, nullptr, w_gate, b_gate, w_up, b_up, h, g_save, u_save, stream);
+}
+
+int gmlp_rms_rowscale(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, float eps,
+                      float* rs, void* xn, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (M <= 0 || K <= 0 || (K % 8) != 0 || (ld % 8) != 0 || ld < K)
+    return fail(GMLP_ERR_SHAPE, "rms_rowscale needs M > 0, K and ld multiples of 8, ld >= K");
+  if (!(eps >= 0.0f)) return fail(GMLP_ERR_ARG, "eps must be >= 0");
+  if (!x || !rs) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(x) || (xn && !aligned16(xn))) return fail(GMLP_ERR_ALIGN, "x / xn must be 16-byte aligned");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  const unsigned blocks = static_cast<unsigned>((M + 7) / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == GMLP_BF16)
+    rms_rowscale_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), M, K, ld, eps, rs,
+                                                               static_cast<__nv_bfloat16*>(xn));
+  else
+    rms_rowscale_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(x), M, K, ld, eps, rs,
+                                                        static_cast<__half*>(xn));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+int gmlp_rms_bwd(int64_t M, int64_t K, int32_t dtype, const void* dxn, const void* xn, const float* rs,
+                 void* dx, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (M <= 0 || K <= 0 || (K % 8) != 0) return fail(GMLP_ERR_SHAPE, "rms_bwd needs M > 0 and K a multiple of 8");
+  if (!dxn || !xn || !rs || !dx) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(dxn) || !aligned16(xn) || !aligned16(dx))
+    return fail(GMLP_ERR_ALIGN, "dxn / xn / dx must be 16-byte aligned");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  const unsigned blocks = static_cast<unsigned>((M + 7) / 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == GMLP_BF16)
+    rms_bwd_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dxn),
+                                                          static_cast<const __nv_bfloat16*>(xn), rs, M, K,
+                                                          static_cast<__nv_bfloat16*>(dx));
+  else
+    rms_bwd_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(dxn), static_cast<const __half*>(xn),
+                                                   rs, M, K, static_cast<__half*>(dx));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
 }
 
 int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
@@ -857,9 +918,9 @@ static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
 template <int MPAD, bool DUAL, typename T>
 static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
                            const void* w0, const void* w1, const void* act, int64_t act_ld,
-                           const void* bias0, const void* bias1, const void* residual, void* out,
-                           int64_t ld_out, float* slots, int* counters, bool dependent, int gate_act,
-                           cudaStream_t stream) {
+                           const void* bias0, const void* bias1, const void* residual,
+                           const float* row_scale, void* out, int64_t ld_out, float* slots, int* counters,
+                           bool dependent, int gate_act, cudaStream_t stream) {
   CUtensorMap mW0, mW1, mAct;
   int rc;
   constexpr int BOX_ROWS = decode_box_rows<MPAD, DUAL>();
@@ -882,6 +943,7 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   a.bias1 = bias1;
   a.out = out;
   a.residual = residual;
+  a.row_scale = row_scale;
   a.ld_out = ld_out;
   a.slots = slots;
   a.counters = counters;
@@ -936,10 +998,10 @@ size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p) {
   return decode_layout(p, ctas).total;
 }
 
-int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
-                    const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
-                    const void* b_down, const void* residual, void* h, void* y, void* scratch,
-                    size_t scratch_bytes, void* stream) {
+int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                           const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                           const void* w_down, const void* b_down, const void* residual, void* h, void* y,
+                           void* scratch, size_t scratch_bytes, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if (p->M > 64) return fail(GMLP_ERR_SHAPE, "decode path takes at most 64 tokens, got %lld",
@@ -948,6 +1010,8 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   if ((rc = check_ptrs({x, w_gate, w_up, w_down, h, y, scratch}))) return rc;
   if ((p->K % 64) != 0 || (p->N % 64) != 0)
     return fail(GMLP_ERR_SHAPE, "decode path needs K and N multiples of 64");
+  if (row_scale && (reinterpret_cast<uintptr_t>(row_scale) & 3u) != 0)
+    return fail(GMLP_ERR_ALIGN, "row_scale must be 4-byte aligned");
   const DeviceInfo* dev;
   if ((rc = device_info(&dev))) return rc;
   const DecodeLayout l = decode_layout(p, dev->sm_count);
@@ -962,14 +1026,22 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
   // start streaming weights at once and wait for the predecessor only before they read
   // activations or touch h, y or the scratch (which a preceding decode call may still use).
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
-                           b_gate, b_up, static_cast<const void*>(nullptr), h, p->N, slots,
+                           b_gate, b_up, static_cast<const void*>(nullptr), row_scale, h, p->N, slots,
                            reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
                               static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
-                              static_cast<const void*>(nullptr), residual, y, p->K, slots,
-                              reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
+                              static_cast<const void*>(nullptr), residual, static_cast<const float*>(nullptr), y,
+                              p->K, slots, reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
+}
+
+int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
+                    const void* b_gate, const void* w_up, const void* b_up, const void* w_down,
+                    const void* b_down, const void* residual, void* h, void* y, void* scratch,
+                    size_t scratch_bytes, void* stream) {
+  return gmlp_decode_fwd_scaled(p, x, nullptr, w_gate, b_gate, w_up, b_up, w_down, b_down, residual, h, y,
+                                scratch, scratch_bytes, stream);
 }
 
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,

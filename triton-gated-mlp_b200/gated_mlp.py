@@ -177,6 +177,26 @@ class FusedGatedMLPFunction(Function):
                 None)
 
 
+class _InputRMSNorm(Function):
+    """x / rms(x) * weight for the training path (the inference path never writes the normalised
+    activations: see FusedGatedMLP.attach_input_norm). Row statistics and both passes over the rows are
+    library kernels; the products with `weight` are elementwise torch ops on [M, K]."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, eps: float) -> Tensor:
+        rs, xn = kernels.rms_rowscale(x, eps, normalised=True)
+        ctx.save_for_backward(xn, rs, weight)
+        return xn * weight
+
+    @staticmethod
+    def backward(ctx, dout: Tensor):
+        xn, rs, weight = ctx.saved_tensors
+        dout = dout.contiguous()
+        dw = (dout.float() * xn.float()).sum(0).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        dx = kernels.rms_bwd(dout * weight, xn, rs) if ctx.needs_input_grad[0] else None
+        return dx, dw, None
+
+
 class FusedGatedMLP(nn.Module):
     """Gated MLP block; see the module docstring.
 
@@ -262,6 +282,35 @@ class FusedGatedMLP(nn.Module):
         self.peer_max_bytes = 1024 * 1024
         self.check_status_every = 0
         self._decode_calls = 0
+        self.input_norm_weight = None
+        self.input_norm_eps = 1e-6
+        self._folded = None
+
+    def attach_input_norm(self, weight: Tensor, eps: float = 1e-6) -> None:
+        """Put an RMSNorm in front of the MLP: forward(x) becomes MLP(x / rms(x) * weight), the step that
+        precedes the MLP in a Llama block (no counterpart in the reference, whose module starts at the
+        projections, gated_mlp.py:224-227). `weight` ([hidden_size]) becomes the parameter
+        `input_norm_weight`. Without gradients the norm costs one pass over x for the row statistics: the
+        weight is folded into copies of W_gate / W_up (refreshed whenever a parameter changes) and 1 / rms is
+        applied to the accumulators of the gate/up kernel, so the normalised activations are never written.
+        With gradients the normalised activations are materialised once and the norm's backward is a
+        row-wise kernel of its own."""
+        if weight.shape != (self.hidden_size,):
+            raise ValueError(f"norm weight must have shape ({self.hidden_size},), got {tuple(weight.shape)}")
+        self.input_norm_weight = nn.Parameter(weight.detach().clone().to(self.gate_proj.weight.device,
+                                                                          self.gate_proj.weight.dtype))
+        self.input_norm_eps = float(eps)
+        self._folded = None
+
+    def _folded_weights(self):
+        """(W_gate * weight, W_up * weight), cached until any of the three tensors is modified."""
+        key = (self.gate_proj.weight._version, self.up_proj.weight._version, self.input_norm_weight._version,
+               self.gate_proj.weight.data_ptr(), self.up_proj.weight.data_ptr(), self.input_norm_weight.data_ptr())
+        if self._folded is None or self._folded[0] != key:
+            with torch.no_grad():
+                w = self.input_norm_weight
+                self._folded = (key, (self.gate_proj.weight * w).contiguous(), (self.up_proj.weight * w).contiguous())
+        return self._folded[1], self._folded[2]
 
     def set_philox(self, seed: int, offset: int = 0) -> None:
         self.philox_seed, self.philox_offset = int(seed), int(offset)
@@ -283,10 +332,13 @@ class FusedGatedMLP(nn.Module):
             self._decode_scratch = (key, kernels.decode_scratch(
                 x.shape[0], self.hidden_size, self.intermediate_size, x.dtype, x.device))
         own_bias = tp_group is None or self.tp_rank == 0
-        y = kernels.decode_fwd(x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight,
+        w_gate, w_up, rs = self.gate_proj.weight, self.up_proj.weight, None
+        if self.input_norm_weight is not None:
+            (w_gate, w_up), rs = self._folded_weights(), kernels.rms_rowscale(x, self.input_norm_eps)
+        y = kernels.decode_fwd(x, w_gate, self.gate_proj.bias, w_up,
                                self.up_proj.bias, self.down_proj.weight,
                                self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1],
-                               act=self.act_fn, residual=residual if own_bias else None)
+                               act=self.act_fn, residual=residual if own_bias else None, row_scale=rs)
         if tp_group is not None:
             if (self._peer is not None and self._peer.supports(y)
                     and y.numel() * y.element_size() <= self.peer_max_bytes):
@@ -340,6 +392,20 @@ class FusedGatedMLP(nn.Module):
                 and kernels.decode_supported(x.shape[0], self.hidden_size, self.intermediate_size)):
             y = self._decode_forward(x, tp_group, residual)
             return y.view(shapes) if len(shapes) > 2 else y
+        if self.input_norm_weight is not None:
+            if not needs_grad:
+                # 1 / rms on the gate/up accumulators, norm weight folded into the weights
+                w_gate, w_up = self._folded_weights()
+                h = kernels.hidden_fwd(x, w_gate, self.gate_proj.bias, w_up, self.up_proj.bias, drop=drop,
+                                       shard=self._shard(), act=self.act_fn,
+                                       row_scale=kernels.rms_rowscale(x, self.input_norm_eps))
+                own = tp_group is None or self.tp_rank == 0
+                y = kernels.down_fwd(h, self.down_proj.weight, self.down_proj.bias if own else None,
+                                     residual if own else None)
+                if tp_group is not None:
+                    parallel.all_reduce_sum(y, tp_group)
+                return y.view(shapes) if len(shapes) > 2 else y
+            x = _InputRMSNorm.apply(x, self.input_norm_weight, self.input_norm_eps)
         y = FusedGatedMLPFunction.apply(
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
             self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group, self.act_fn, residual,

@@ -83,9 +83,10 @@ def _same_dtype(*ts: Tensor | None) -> torch.dtype:
 
 def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
                drop: Dropout = NO_DROPOUT, shard: Shard = NO_SHARD, save: bool = False, act: str = "silu",
-               tuning: int = 0):
+               tuning: int = 0, row_scale: Tensor | None = None):
     """H = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)); with save=True also
-    returns the biased pre-activations (G, U). `tuning`: _lib.tune_word() for this launch."""
+    returns the biased pre-activations (G, U). `tuning`: _lib.tune_word() for this launch.
+    row_scale: optional fp32 [M] factors on both products before the bias (rms_rowscale's output)."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up)
     dt = _same_dtype(x, w_gate, b_gate, w_up, b_up)
     x, w_gate, w_up, b_gate, b_up = _c(x), _c(w_gate), _c(w_up), _c(b_gate), _c(b_up)
@@ -96,10 +97,46 @@ def hidden_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     u = torch.empty((M, N), dtype=dt, device=dev) if save else None
     if M > 0:
         prob = _problem(M, K, N, dt, drop, shard, act, tuning)
+        _check_row_scale(row_scale, M, dev)
         with _on(dev):
-            check(load().gmlp_hidden_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up),
-                                         ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
+            check(load().gmlp_hidden_fwd_scaled(C.byref(prob), ptr(x), ptr(row_scale), ptr(w_gate), ptr(b_gate),
+                                                ptr(w_up), ptr(b_up), ptr(h), ptr(g), ptr(u), stream_of(x)))
     return (h, g, u) if save else h
+
+
+def _check_row_scale(rs: Tensor | None, M: int, dev: torch.device) -> None:
+    if rs is not None and (rs.dtype != torch.float32 or rs.shape != (M,) or rs.device != dev
+                           or not rs.is_contiguous()):
+        raise ValueError(f"row_scale must be a contiguous float32 tensor of shape ({M},) on {dev}")
+
+
+def rms_rowscale(x: Tensor, eps: float, normalised: bool = False):
+    """rs[m] = 1 / sqrt(mean_k x[m,k]^2 + eps) as fp32 [M]; with normalised=True also x * rs[:, None] in
+    x's dtype (what the backward pass of the norm needs)."""
+    dev = require_cuda(x)
+    x = _c(x)
+    M, K = x.shape
+    rs = torch.empty((M,), dtype=torch.float32, device=dev)
+    xn = torch.empty((M, K), dtype=x.dtype, device=dev) if normalised else None
+    if M > 0:
+        with _on(dev):
+            check(load().gmlp_rms_rowscale(M, K, dtype_code(x.dtype), ptr(x), x.stride(0), float(eps), ptr(rs),
+                                           ptr(xn), stream_of(x)))
+    return (rs, xn) if normalised else rs
+
+
+def rms_bwd(dxn: Tensor, xn: Tensor, rs: Tensor) -> Tensor:
+    """Backward of xn = x * rs[:, None]: dx = rs * (dxn - xn * mean_k(dxn * xn))."""
+    dev = require_cuda(dxn, xn, rs)
+    dt = _same_dtype(dxn, xn)
+    dxn, xn = _c(dxn), _c(xn)
+    M, K = dxn.shape
+    _check_row_scale(rs, M, dev)
+    dx = torch.empty((M, K), dtype=dt, device=dev)
+    if M > 0:
+        with _on(dev):
+            check(load().gmlp_rms_bwd(M, K, dtype_code(dt), ptr(dxn), ptr(xn), ptr(rs), ptr(dx), stream_of(dxn)))
+    return dx
 
 
 def _out_buffer(out: Tensor | None, shape, dt: torch.dtype, dev: torch.device) -> Tensor:
@@ -355,7 +392,7 @@ def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device
 
 def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
                w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
-               residual: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+               residual: Tensor | None = None, out: Tensor | None = None, row_scale: Tensor | None = None) -> Tensor:
     """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens,
     written into `out` when given."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
@@ -372,10 +409,11 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     h = torch.empty((M, N), dtype=dt, device=dev)
     y = _out_buffer(out, (M, K), dt, dev)
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
+    _check_row_scale(row_scale, M, dev)
     with _on(dev):
-        check(load().gmlp_decode_fwd(C.byref(prob), ptr(x), ptr(w_gate), ptr(b_gate), ptr(w_up), ptr(b_up),
-                                     ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(y), ptr(scratch),
-                                     scratch.numel() * scratch.element_size(), stream_of(x)))
+        check(load().gmlp_decode_fwd_scaled(C.byref(prob), ptr(x), ptr(row_scale), ptr(w_gate), ptr(b_gate), ptr(w_up),
+                                            ptr(b_up), ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(y),
+                                            ptr(scratch), scratch.numel() * scratch.element_size(), stream_of(x)))
     return y
 
 
