@@ -748,6 +748,10 @@ def run_gpu(args, w, name):
                 e1.record()
                 k1_events.append((e0, e1))
             return K_.down_fwd(h, wd, bdt)
+        # one training step's worth of work: gradients start from None, as after an optimiser's
+        # zero_grad(set_to_none=True) (otherwise torch adds every new gradient into the old one,
+        # three more passes over the weights that are not part of the hot path)
+        mlp.zero_grad(set_to_none=True)
         xx = x.detach().requires_grad_(True)
         y = mlp(xx)
         y.backward(dy)
@@ -793,6 +797,7 @@ def run_gpu(args, w, name):
         dy_host.copy_(dy.cpu())
 
         def api_step(x_dev, dy_dev):
+            mlp.zero_grad(set_to_none=True)
             xx = x_dev.detach().requires_grad_(True)
             mlp(xx).backward(dy_dev)
             return xx.grad
@@ -842,11 +847,7 @@ def run_gpu(args, w, name):
             em(xx).backward(dy)
             return xx.grad
 
-        def engine_step():
-            r = step_device()
-            if train:
-                mlp.zero_grad(set_to_none=True)
-            return r
+        engine_step = step_device
 
         time.sleep(1.0)
         for _ in range(max(args.warmup, 3)):

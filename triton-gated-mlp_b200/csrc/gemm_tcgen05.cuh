@@ -80,6 +80,14 @@ constexpr int WATCHER_WARP = 2 + EPI_WARPS;
 constexpr int GEMM_THREADS = 32 * (3 + EPI_WARPS);        // 608
 constexpr uint32_t EPI_BAR_THREADS = 32 * (EPI_WARPS + 1);  // epilogue warps + watcher
 constexpr uint32_t EPI_BAR_ID0 = 1;                       // named barriers 1, 2: one per accumulator
+#ifndef GMLP_PRODUCER_SLEEP_NS
+#define GMLP_PRODUCER_SLEEP_NS 100
+#endif
+#ifndef GMLP_WATCHER_SLEEP_NS
+#define GMLP_WATCHER_SLEEP_NS 400
+#endif
+constexpr int PRODUCER_SLEEP_NS = GMLP_PRODUCER_SLEEP_NS;  // between polls of a full ring (stages ahead of the MMAs)
+constexpr int WATCHER_SLEEP_NS = GMLP_WATCHER_SLEEP_NS;    // between polls for a tile's completion (10 us or more apart)
 constexpr uint32_t EPI_DONE_BAR = 3;                      // ASUM kernels: the epilogue warps have left the staging area
 constexpr int ASUM_BUFS = 4;                              // the watcher's private ring: 4 x 16 KB in the staging area
 
@@ -820,7 +828,7 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtenso
         ok = asum_tile<T>(args, tc.batch ? mapA1 : mapA0, tc, lane, n_tiles, mn0, m_tiles * TILE_M, epi_smem,
                           asum_bar0, seq, abortp);
     }
-    ok = mbar_wait_warp(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane) && ok;
+    ok = mbar_wait_warp<WATCHER_SLEEP_NS>(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane) && ok;
     tc_fence_after_sync();
     if (lane == 0) {
       epi_go[acc] = ok ? 1 : 0;
@@ -1002,7 +1010,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
         const int m0 = tc.m_tile * BM;
         const int n0 = tc.n_tile * TILE_N;
         for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) {
+          if (!mbar_wait<PRODUCER_SLEEP_NS>(empty_bar(stage), phase ^ 1u, abortp)) {
             ok = false;
             break;
           }
@@ -1208,7 +1216,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
         const int m0 = tc.m_tile * PAIR_M + static_cast<int>(rank) * BM;
         const int n0 = tc.n_tile * TILE_N;
         for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) {
+          if (!mbar_wait<PRODUCER_SLEEP_NS>(empty_bar(stage), phase ^ 1u, abortp)) {
             ok = false;
             break;
           }

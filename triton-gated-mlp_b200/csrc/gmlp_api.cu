@@ -333,7 +333,11 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // Raster groups: a group of row tiles sweeps all column tiles, so the tiles in
   // flight at any time (one per SM or SM pair) share a small set of A and B tiles
   // in L2, and the group's rows of A stay resident while B streams past once per group.
-  args.group_m = tune.group_m > 0 ? tune.group_m : (pair ? 16 : 32);
+  // The gate/up kernel's A panel (x) is small enough to stay resident for 16 row tiles (4096
+  // rows) while its wide B streams past once per group; the other kernels' panels are not,
+  // and a squarer wave of tiles (8 row tiles x about 9 column tiles on 74 SM pairs) moves
+  // fewer bytes.
+  args.group_m = tune.group_m > 0 ? tune.group_m : (pair ? (EPI == EPI_SWIGLU ? 16 : 8) : 32);
   cudaError_t e;
   if (pair) {
     const int64_t max_pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;

@@ -68,8 +68,11 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
 // Bounded wait. `abort_flag` lives in shared memory and is set by whichever role
 // first gives up, so the other roles stop within one poll instead of each
 // sitting out its own limit. Waiting threads are parked by the hardware between polls
-// (suspend hint): eighteen warps spinning on barriers cost enough power on a
-// power-capped part to lower the clock the tensor pipe runs at.
+// (suspend hint), and a waiter that is not on the critical path (SLEEP_NS > 0: the
+// producer waiting for a free ring slot several stages ahead, the watcher waiting for a
+// tile to finish) also sleeps between polls: on a power-capped part every polling loop
+// that issues instructions all the time lowers the clock the tensor pipe runs at.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -78,13 +81,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     if (mbar_try_wait_suspend(bar, parity, 4000u)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
   }
 }
 // The same for a whole warp: lane 0 waits, the others sleep at the warp barrier.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity,
                                                volatile int* abort_flag, int lane) {
   int ok = 1;
-  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  if (lane == 0) ok = mbar_wait<SLEEP_NS>(bar, parity, abort_flag) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
