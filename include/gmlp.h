@@ -260,6 +260,29 @@ int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* 
                            const void* w_down, const void* b_down, const void* residual, void* h, void* y,
                            void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- decode with 8-bit (e4m3) weights: half the bytes of the HBM-bound weight stream ----
+ * No counterpart in the reference (its benchmark runs fp16 only,
+ * src/triton_gated_mlp/benchmark.py:26-123). Weights are e4m3 bytes with one fp32 scale per
+ * weight ROW (W ~= w8 * scale[row]; prepared once by the host); activations are quantised
+ * per TOKEN on the fly by gmlp_quantize_rows_e4m3; both operands go to
+ * tcgen05.mma.kind::f8f6f4 (fp32 accumulation) and the accumulators are multiplied by
+ * (token scale * weight-row scale) before bias and activation.
+ * gmlp_quantize_rows_e4m3: scale[m] = max(amax_k |x[m,k]|, 1e-30) / 448;
+ *   q[m,k] = e4m3(x[m,k] / scale[m]) (round to nearest even, saturating). q is [M,K] bytes.
+ * gmlp_decode_fwd_fp8: x [M,K] 16-bit in; work buffers x8 [M,K] bytes, x_scale [M],
+ *   h [M,N] 16-bit, h8 [M,N] bytes, h_scale [M]; y [M,K] 16-bit out. K and N multiples of
+ *   128, M <= 64; scratch and the rules about it, about the stream and about what may
+ *   precede the call as for gmlp_decode_fwd. Four launches: quantise x, gate/up, quantise
+ *   h, down. */
+int gmlp_quantize_rows_e4m3(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, void* q,
+                            float* scale, void* stream);
+int gmlp_decode_fwd_fp8(const gmlp_problem_t* p, const void* x, const void* w_gate8,
+                        const float* w_gate_scale, const void* b_gate, const void* w_up8,
+                        const float* w_up_scale, const void* b_up, const void* w_down8,
+                        const float* w_down_scale, const void* b_down, const void* residual, void* x8,
+                        float* x_scale, void* h, void* h8, float* h_scale, void* y, void* scratch,
+                        size_t scratch_bytes, void* stream);
+
 /* mask[M,N] (one byte per element, 1 = kept) for the problem's dropout settings:
  * the device side of the bit-exact mask check. */
 int gmlp_dropout_mask(const gmlp_problem_t* p, uint8_t* mask, void* stream);

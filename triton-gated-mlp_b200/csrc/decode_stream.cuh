@@ -41,7 +41,9 @@ struct DecodeArgs {
   const void* bias1;  // up bias (DUAL)
   void* out;          // H[M, rows] or Y[M, rows]
   const void* residual;  // optional [M, rows] added to the output (down projection only)
-  const float* row_scale;  // optional [M] per-token factors on both accumulators before the bias (DUAL only)
+  const float* row_scale;  // optional [M] per-token factors on the accumulators before the bias
+  const float* wscale0;    // optional [rows] per-weight-row factors (8-bit weights: their dequantisation scales)
+  const float* wscale1;    // the same for the second weight matrix (DUAL)
   long long ld_out;
   float* slots;       // [2 * gridDim.x][NACC][128][MPAD] fp32 partial tiles
   int* counters;      // [row tiles] reduction blocks whose partials are in the slots; zero on entry, and on exit
@@ -62,9 +64,22 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 constexpr int DECODE_THREADS = 192;
 // One CTA per SM, one weight sub-tile per unit (two CTAs per SM with half the ring each,
 // and larger units with whole row tiles owned by CTAs, were both slower).
+#ifndef GMLP_DECODE_SUB64_DUAL
+#define GMLP_DECODE_SUB64_DUAL 1
+#endif
+#ifndef GMLP_DECODE_SUB64_DOWN
+#define GMLP_DECODE_SUB64_DOWN 1
+#endif
+#ifndef GMLP_DECODE_SUB32_DUAL
+#define GMLP_DECODE_SUB32_DUAL 1
+#endif
+#ifndef GMLP_DECODE_SUB32_DOWN
+#define GMLP_DECODE_SUB32_DOWN 1
+#endif
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_subtiles() {
-  return 1;
+  return MPAD == 64 ? (DUAL ? GMLP_DECODE_SUB64_DUAL : GMLP_DECODE_SUB64_DOWN)
+         : MPAD == 32 ? (DUAL ? GMLP_DECODE_SUB32_DUAL : GMLP_DECODE_SUB32_DOWN) : 1;
 }
 template <int MPAD, bool DUAL>
 __host__ __device__ constexpr int decode_stage_bytes() {
@@ -94,10 +109,13 @@ __device__ __forceinline__ long long unit_start(long long c, long long total, lo
 
 // out[m * ld] = act(gate[m] + b0) * (up[m] + b1) for the tokens m < M of one weight row,
 // with the activation a compile-time constant.
+// With scales: gate and up are first multiplied by row_scale[m] (per token; null = 1) and by this
+// weight row's own factors ws0 / ws1.
 template <int ACT, int COUNT, typename T>
 __device__ __forceinline__ void store_gated(T* po, long long ld, int M, const float* gate, const float* up,
-                                            float b0, float b1, const float* row_scale) {
-  if (row_scale == nullptr) {
+                                            float b0, float b1, const float* row_scale, bool scaled, float ws0,
+                                            float ws1) {
+  if (!scaled) {
 #pragma unroll
     for (int m = 0; m < COUNT; ++m)
       if (m < M) po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] + b0) * (up[m] + b1));
@@ -105,13 +123,17 @@ __device__ __forceinline__ void store_gated(T* po, long long ld, int M, const fl
 #pragma unroll
     for (int m = 0; m < COUNT; ++m)
       if (m < M) {
-        const float r = row_scale[m];  // the same address for every lane: one broadcast load
-        po[static_cast<long long>(m) * ld] = static_cast<T>(act_value(ACT, gate[m] * r + b0) * (up[m] * r + b1));
+        const float r = row_scale ? row_scale[m] : 1.0f;  // the same address for every lane: one broadcast load
+        po[static_cast<long long>(m) * ld] =
+            static_cast<T>(act_value(ACT, gate[m] * (r * ws0) + b0) * (up[m] * (r * ws1) + b1));
       }
   }
 }
 
-template <int MPAD, bool DUAL, typename T>
+// FP8: weights and activations are e4m3 bytes (128 reduction elements per 128-byte row instead
+// of 64), multiplied by tcgen05.mma.kind::f8f6f4; T is still the type of bias, residual and
+// output. Everything else (rings, stream-K split, owners) is the same code.
+template <int MPAD, bool DUAL, typename T, bool FP8 = false>
 __global__ void __launch_bounds__(DECODE_THREADS, 1)
 decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
                      const __grid_constant__ CUtensorMap tmW1,
@@ -122,7 +144,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
   constexpr int TILE_ROWS = 128 * SUB;                // weight rows per unit ("row tile")
   constexpr int BOX_ROWS = decode_box_rows<MPAD, DUAL>();
   constexpr int STAGES = decode_stages<MPAD, DUAL>();
-  constexpr uint32_t W_BYTES = 128 * 128;  // one [128 x 64] 16-bit weight sub-tile
+  constexpr int RED = FP8 ? 128 : BK;      // reduction elements per stage: one 128-byte row
+  constexpr uint32_t W_BYTES = 128 * 128;  // one [128 rows x 128 bytes] weight sub-tile
   constexpr uint32_t ACT_BYTES = MPAD * 128;
   constexpr uint32_t ACT_OFF = NACC * SUB * W_BYTES;  // stage: [W0 sub-tiles][W1 sub-tiles][activations]
   constexpr uint32_t STAGE_BYTES = ACT_OFF + ACT_BYTES;
@@ -196,15 +219,15 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         // Rows past the end of the matrix (a last tile that is not full) arrive as zeros.
 #pragma unroll
         for (int b = 0; b < TILE_ROWS / BOX_ROWS; ++b) {
-          tma_load_2d_hint(sw + b * BOX_ROWS * 128, &tmW0, fb, kb * BK, tile * TILE_ROWS + b * BOX_ROWS, pol_w);
+          tma_load_2d_hint(sw + b * BOX_ROWS * 128, &tmW0, fb, kb * RED, tile * TILE_ROWS + b * BOX_ROWS, pol_w);
           if (DUAL)
-            tma_load_2d_hint(sw + SUB * W_BYTES + b * BOX_ROWS * 128, &tmW1, fb, kb * BK,
+            tma_load_2d_hint(sw + SUB * W_BYTES + b * BOX_ROWS * 128, &tmW1, fb, kb * RED,
                              tile * TILE_ROWS + b * BOX_ROWS, pol_w);
         }
       };
       auto load_act = [&](long long u, int st) {
         const int kb = static_cast<int>(u % args.kbt);
-        tma_load_2d_hint(smem_base + st * STAGE_BYTES + ACT_OFF, &tmAct, full_bar(st), kb * BK, 0, pol_a);
+        tma_load_2d_hint(smem_base + st * STAGE_BYTES + ACT_OFF, &tmAct, full_bar(st), kb * RED, 0, pol_a);
       };
       long long u = u_begin;
       if (args.dependent) {
@@ -270,13 +293,21 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
             const uint64_t w0desc = make_smem_desc(sw + t * W_BYTES, 16, 1024);
             const uint64_t w1desc = make_smem_desc(sw + (SUB + t) * W_BYTES, 16, 1024);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
+            for (int k = 0; k < 4; ++k) {  // four 32-byte steps per 128-byte row, whatever the element size
               const uint32_t accum = (first && k == 0) ? 0u : 1u;
-              umma_f16(d_tmem + (t * NACC) * MPAD, w0desc + static_cast<uint64_t>(2 * k),
-                       xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
-              if (DUAL)
-                umma_f16(d_tmem + (t * NACC + 1) * MPAD, w1desc + static_cast<uint64_t>(2 * k),
+              if (FP8) {
+                umma_f8(d_tmem + (t * NACC) * MPAD, w0desc + static_cast<uint64_t>(2 * k),
+                        xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+                if (DUAL)
+                  umma_f8(d_tmem + (t * NACC + 1) * MPAD, w1desc + static_cast<uint64_t>(2 * k),
+                          xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+              } else {
+                umma_f16(d_tmem + (t * NACC) * MPAD, w0desc + static_cast<uint64_t>(2 * k),
                          xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+                if (DUAL)
+                  umma_f16(d_tmem + (t * NACC + 1) * MPAD, w1desc + static_cast<uint64_t>(2 * k),
+                           xdesc + static_cast<uint64_t>(2 * k), args.idesc, accum);
+              }
             }
           }
           first = false;
@@ -339,24 +370,28 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       auto emit = [&](long long wrow, float b0, float b1, const float* first, const float* second) {
         if (wrow >= args.rows) return;
         T* const po = out + wrow;
+        const bool scaled = args.row_scale != nullptr || args.wscale0 != nullptr;
+        const float ws0 = args.wscale0 ? args.wscale0[wrow] : 1.0f;
+        const float ws1 = (DUAL && args.wscale1) ? args.wscale1[wrow] : 1.0f;
         if (DUAL) {
           switch (args.act) {
-            case ACT_SILU: store_gated<ACT_SILU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
-            case ACT_NONE: store_gated<ACT_NONE, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
-            case ACT_RELU: store_gated<ACT_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
-            case ACT_GELU: store_gated<ACT_GELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            case ACT_SILU: store_gated<ACT_SILU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
+            case ACT_NONE: store_gated<ACT_NONE, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
+            case ACT_RELU: store_gated<ACT_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
+            case ACT_GELU: store_gated<ACT_GELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
             case ACT_SIGMOID:
-              store_gated<ACT_SIGMOID, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale);
+              store_gated<ACT_SIGMOID, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled,
+                                             ws0, ws1);
               break;
-            case ACT_TANH: store_gated<ACT_TANH, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
-            default: store_gated<ACT_LEAKY_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale); break;
+            case ACT_TANH: store_gated<ACT_TANH, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
+            default: store_gated<ACT_LEAKY_RELU, MPAD>(po, args.ld_out, args.M, first, second, b0, b1, args.row_scale, scaled, ws0, ws1); break;
           }
         } else {
           const T* const pr = residual ? residual + wrow : nullptr;
 #pragma unroll
           for (int m = 0; m < MPAD; ++m) {
             if (m < args.M) {
-              float o = first[m] + b0;
+              float o = (scaled ? first[m] * ((args.row_scale ? args.row_scale[m] : 1.0f) * ws0) : first[m]) + b0;
               if (pr) o += static_cast<float>(pr[static_cast<long long>(m) * args.ld_out]);
               po[static_cast<long long>(m) * args.ld_out] = static_cast<T>(o);
             }

@@ -2,6 +2,8 @@
 // caller-supplied dH, column sums for the bias gradients, and the dropout-mask
 // dump used by the bit-exact mask check.
 #pragma once
+#include <cuda_fp8.h>
+
 #include "gemm_tcgen05.cuh"
 
 namespace gmlp {
@@ -127,6 +129,57 @@ rms_bwd_kernel(const T* __restrict__ dxn, const T* __restrict__ xn, const float*
 #pragma unroll
     for (int i = 0; i < 8; ++i) u[i] = r * (u[i] - v[i] * c);
     store8(out + k, u);
+  }
+}
+
+// Per-row dynamic quantisation to e4m3 for the 8-bit decode path. One 256-thread block per row
+// (the decode path has at most 64 rows, each up to tens of thousands of elements long):
+//   scale[m] = max(amax_k |x[m,k]|, tiny) / 448       (448 = largest e4m3 value)
+//   q[m,k]   = e4m3(x[m,k] / scale[m]), round to nearest even, saturating
+// so that x ~= q * scale. The CPU restatement is oracle/fp8.py.
+// `dependent`: launched as a programmatic dependent of the kernel that writes x. The grid lets
+// ITS dependent (a weight-streaming kernel) start at once and waits for x's producer itself.
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_rows_e4m3_kernel(const T* __restrict__ x, long long M, long long K, long long ld,
+                          uint8_t* __restrict__ q, float* __restrict__ scale, int dependent) {
+  __shared__ float warp_max[8];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (dependent) asm volatile("griddepcontrol.wait;" ::: "memory");
+  const long long row = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const T* xr = x + row * ld;
+  float amax = 0.f;
+  for (long long k = tid * 8LL; k < K; k += 2048) {
+    float v[8];
+    load8(xr + k, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) warp_max[tid >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, warp_max[w]);
+  const float sc = fmaxf(amax, 1e-30f) / 448.0f;
+  if (tid == 0) scale[row] = sc;
+  uint8_t* out = q + row * K;
+  for (long long k = tid * 8LL; k < K; k += 2048) {
+    float v[8];
+    load8(xr + k, v);
+    uint32_t w[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      // true division, so that the CPU restatement (which divides) agrees bit for bit
+      const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h] / sc, v[4 * h + 1] / sc),
+                                                               __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h + 2] / sc, v[4 * h + 3] / sc),
+                                                               __NV_SATFINITE, __NV_E4M3);
+      w[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+    }
+    *reinterpret_cast<uint2*>(out + k) = make_uint2(w[0], w[1]);
   }
 }
 

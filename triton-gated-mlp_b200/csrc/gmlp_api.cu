@@ -127,7 +127,9 @@ static uint32_t map_hash(const MapKey& k) {
   return static_cast<uint32_t>(h >> 40) % MAP_CACHE_SLOTS;
 }
 
-// 2-D row-major matrix [outer, inner] of 16-bit elements, swizzled rows of
+constexpr int DTYPE_U8 = 100;  // internal: one-byte elements (e4m3 operands of the 8-bit decode path)
+
+// 2-D row-major matrix [outer, inner] of 16-bit (or, with DTYPE_U8, 8-bit) elements, swizzled rows of
 // `swizzle_bytes` (32 / 64 / 128), out-of-bounds elements read as zero and are not
 // written by stores.
 static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
@@ -140,11 +142,12 @@ static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t o
     return GMLP_OK;
   }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * (dtype == DTYPE_U8 ? 1 : 2)};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt =
-      dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == DTYPE_U8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUtensorMapSwizzle sw = swizzle_bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
                                 : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                                                       : CU_TENSOR_MAP_SWIZZLE_128B;
@@ -919,29 +922,39 @@ static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
   return l;
 }
 
-template <int MPAD, bool DUAL, typename T>
+// Per-weight-row dequantisation scales of the 8-bit path (null on the 16-bit path).
+struct WeightScales {
+  const float* s0 = nullptr;
+  const float* s1 = nullptr;
+};
+
+template <int MPAD, bool DUAL, typename T, bool FP8>
 static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows, int64_t red,
                            const void* w0, const void* w1, const void* act, int64_t act_ld,
                            const void* bias0, const void* bias1, const void* residual,
-                           const float* row_scale, void* out, int64_t ld_out, float* slots, int* counters,
-                           bool dependent, int gate_act, cudaStream_t stream) {
+                           const float* row_scale, WeightScales ws, void* out, int64_t ld_out, float* slots,
+                           int* counters, bool dependent, int gate_act, cudaStream_t stream) {
   CUtensorMap mW0, mW1, mAct;
   int rc;
   constexpr int BOX_ROWS = decode_box_rows<MPAD, DUAL>();
   constexpr int TILE_ROWS = 128 * decode_subtiles<MPAD, DUAL>();
-  if ((rc = encode_map(&mW0, w0, red, rows, red, BK, BOX_ROWS, dtype))) return rc;
+  constexpr int RED = FP8 ? 128 : BK;            // reduction elements per 128-byte row
+  const int op_dtype = FP8 ? DTYPE_U8 : dtype;  // element type of weights and activations
+  if ((rc = encode_map(&mW0, w0, red, rows, red, RED, BOX_ROWS, op_dtype))) return rc;
   if (DUAL) {
-    if ((rc = encode_map(&mW1, w1, red, rows, red, BK, BOX_ROWS, dtype))) return rc;
+    if ((rc = encode_map(&mW1, w1, red, rows, red, RED, BOX_ROWS, op_dtype))) return rc;
   } else {
     mW1 = mW0;
   }
-  if ((rc = encode_map(&mAct, act, red, M, act_ld, BK, MPAD, dtype))) return rc;
+  if ((rc = encode_map(&mAct, act, red, M, act_ld, RED, MPAD, op_dtype))) return rc;
   DecodeArgs a;
   memset(&a, 0, sizeof(a));
   a.M = M;
   a.rows = static_cast<int>(rows);
-  a.kbt = static_cast<int>((red + BK - 1) / BK);
-  a.idesc = make_idesc_f16(128, MPAD, dtype == GMLP_BF16 ? 1 : 0, false, false);
+  a.kbt = static_cast<int>((red + RED - 1) / RED);
+  a.idesc = FP8 ? make_idesc_f8(128, MPAD) : make_idesc_f16(128, MPAD, dtype == GMLP_BF16 ? 1 : 0, false, false);
+  a.wscale0 = ws.s0;
+  a.wscale1 = ws.s1;
   a.status = dev->status_ptr;
   a.bias0 = bias0;
   a.bias1 = bias1;
@@ -956,11 +969,10 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   const long long total = ((rows + TILE_ROWS - 1) / TILE_ROWS) * static_cast<long long>(a.kbt);
   const int grid = static_cast<int>(total < dev->sm_count ? total : dev->sm_count);
   constexpr size_t smem = decode_smem_bytes<MPAD, DUAL>();
-  auto kfn = decode_stream_kernel<MPAD, DUAL, T>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem));
-  if (e != cudaSuccess)
-    return fail(GMLP_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  auto kfn = decode_stream_kernel<MPAD, DUAL, T, FP8>;
+  static std::atomic<uint64_t> attr_done{0};
+  if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
+  cudaError_t e;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid);
@@ -982,14 +994,17 @@ static int launch_decode_t(const DeviceInfo* dev, int dtype, int M, int64_t rows
   return GMLP_OK;
 }
 
-template <bool DUAL, typename... Args>
+template <bool DUAL, bool FP8 = false, typename... Args>
 static int launch_decode(int mpad, int dtype, Args... args) {
   const bool bf = dtype == GMLP_BF16;
   if (mpad == 16)
-    return bf ? launch_decode_t<16, DUAL, __nv_bfloat16>(args...) : launch_decode_t<16, DUAL, __half>(args...);
+    return bf ? launch_decode_t<16, DUAL, __nv_bfloat16, FP8>(args...)
+              : launch_decode_t<16, DUAL, __half, FP8>(args...);
   if (mpad == 32)
-    return bf ? launch_decode_t<32, DUAL, __nv_bfloat16>(args...) : launch_decode_t<32, DUAL, __half>(args...);
-  return bf ? launch_decode_t<64, DUAL, __nv_bfloat16>(args...) : launch_decode_t<64, DUAL, __half>(args...);
+    return bf ? launch_decode_t<32, DUAL, __nv_bfloat16, FP8>(args...)
+              : launch_decode_t<32, DUAL, __half, FP8>(args...);
+  return bf ? launch_decode_t<64, DUAL, __nv_bfloat16, FP8>(args...)
+            : launch_decode_t<64, DUAL, __half, FP8>(args...);
 }
 
 extern "C" {
@@ -1030,14 +1045,103 @@ int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* 
   // start streaming weights at once and wait for the predecessor only before they read
   // activations or touch h, y or the scratch (which a preceding decode call may still use).
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
-                           b_gate, b_up, static_cast<const void*>(nullptr), row_scale, h, p->N, slots,
-                           reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
+                           b_gate, b_up, static_cast<const void*>(nullptr), row_scale, WeightScales{}, h, p->N,
+                           slots, reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
                               static_cast<const void*>(nullptr), static_cast<const void*>(h), p->N, b_down,
-                              static_cast<const void*>(nullptr), residual, static_cast<const float*>(nullptr), y,
-                              p->K, slots, reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
+                              static_cast<const void*>(nullptr), residual, static_cast<const float*>(nullptr),
+                              WeightScales{}, y, p->K, slots, reinterpret_cast<int*>(sc + l.counters2_off), true,
+                              p->act, st);
+}
+
+static int quantize_rows_launch(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, void* q,
+                                float* scale, bool dependent, void* stream) {
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (M <= 0 || K <= 0 || (K % 8) != 0 || (ld % 8) != 0 || ld < K || M > 0x7fffffffLL)
+    return fail(GMLP_ERR_SHAPE, "quantize_rows needs M > 0, K and ld multiples of 8, ld >= K");
+  if (!x || !q || !scale) return fail(GMLP_ERR_ARG, "NULL pointer argument");
+  if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 7u) != 0)
+    return fail(GMLP_ERR_ALIGN, "x must be 16-byte and q 8-byte aligned");
+  const DeviceInfo* dev;
+  int rc;
+  if ((rc = device_info(&dev))) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(M));
+  cfg.blockDim = dim3(256);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  const int dep = dependent ? 1 : 0;
+  long long m = M, k = K, l = ld;
+  uint8_t* q8 = static_cast<uint8_t*>(q);
+  cudaError_t e;
+  if (dtype == GMLP_BF16)
+    e = cudaLaunchKernelEx(&cfg, quantize_rows_e4m3_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), m, k,
+                           l, q8, scale, dep);
+  else
+    e = cudaLaunchKernelEx(&cfg, quantize_rows_e4m3_kernel<__half>, static_cast<const __half*>(x), m, k, l, q8, scale,
+                           dep);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
+}
+
+int gmlp_quantize_rows_e4m3(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, void* q,
+                            float* scale, void* stream) {
+  return quantize_rows_launch(M, K, dtype, x, ld, q, scale, false, stream);
+}
+
+int gmlp_decode_fwd_fp8(const gmlp_problem_t* p, const void* x, const void* w_gate8,
+                        const float* w_gate_scale, const void* b_gate, const void* w_up8,
+                        const float* w_up_scale, const void* b_up, const void* w_down8,
+                        const float* w_down_scale, const void* b_down, const void* residual, void* x8,
+                        float* x_scale, void* h, void* h8, float* h_scale, void* y, void* scratch,
+                        size_t scratch_bytes, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if (p->M > 64) return fail(GMLP_ERR_SHAPE, "decode path takes at most 64 tokens, got %lld",
+                             static_cast<long long>(p->M));
+  if (p->dropout_p != 0.0f) return fail(GMLP_ERR_ARG, "decode path is inference only: dropout_p must be 0");
+  if ((rc = check_ptrs({x, w_gate8, w_up8, w_down8, x8, h, h8, y, scratch}))) return rc;
+  if (!w_gate_scale || !w_up_scale || !w_down_scale || !x_scale || !h_scale)
+    return fail(GMLP_ERR_ARG, "NULL scale pointer");
+  if ((p->K % 128) != 0 || (p->N % 128) != 0)
+    return fail(GMLP_ERR_SHAPE, "the 8-bit decode path needs K and N multiples of 128");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const DecodeLayout l = decode_layout(p, dev->sm_count);
+  if (scratch_bytes < l.total)
+    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes, l.total);
+  char* sc = static_cast<char*>(scratch);
+  float* slots = reinterpret_cast<float*>(sc + l.slots_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int M = static_cast<int>(p->M);
+  // x -> e4m3 with one scale per token; gate/up kernel on 8-bit operands (accumulators times token
+  // scale times weight-row scale); H (16-bit) -> e4m3 per token; down projection likewise.
+  // The quantisers run as programmatic dependents too, so the kernel after each of them starts
+  // streaming its weights while the one before it drains.
+  if ((rc = quantize_rows_launch(M, p->K, p->dtype, x, p->K, x8, x_scale, true, stream))) return rc;
+  rc = launch_decode<true, true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate8, w_up8,
+                                 static_cast<const void*>(x8), p->K, b_gate, b_up, static_cast<const void*>(nullptr),
+                                 static_cast<const float*>(x_scale), WeightScales{w_gate_scale, w_up_scale}, h, p->N,
+                                 slots, reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
+  if (rc) return rc;
+  if ((rc = quantize_rows_launch(M, p->N, p->dtype, h, p->N, h8, h_scale, true, stream))) return rc;
+  return launch_decode<false, true>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down8,
+                                    static_cast<const void*>(nullptr), static_cast<const void*>(h8), p->N, b_down,
+                                    static_cast<const void*>(nullptr), residual, static_cast<const float*>(h_scale),
+                                    WeightScales{w_down_scale, nullptr}, y, p->K, slots,
+                                    reinterpret_cast<int*>(sc + l.counters2_off), true, p->act, st);
 }
 
 int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,

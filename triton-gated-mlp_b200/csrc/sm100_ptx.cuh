@@ -238,6 +238,19 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same for 8-bit floating-point operands (kind::f8f6f4; the element formats come from
+// the instruction descriptor, see make_idesc_f8): 32 reduction elements per instruction.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has
 // finished (that is: has read its shared-memory operands and written TMEM).
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -306,6 +319,12 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int fmt, boo
   return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
          (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// The same layout for tcgen05.mma.kind::f8f6f4 with both operands e4m3 (format code 0),
+// K-major, fp32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 }  // namespace gmlp

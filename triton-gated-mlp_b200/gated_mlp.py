@@ -285,6 +285,7 @@ class FusedGatedMLP(nn.Module):
         self.input_norm_weight = None
         self.input_norm_eps = 1e-6
         self._folded = None
+        self._fp8 = None
 
     def attach_input_norm(self, weight: Tensor, eps: float = 1e-6) -> None:
         """Put an RMSNorm in front of the MLP: forward(x) becomes MLP(x / rms(x) * weight), the step that
@@ -301,6 +302,22 @@ class FusedGatedMLP(nn.Module):
                                                                           self.gate_proj.weight.dtype))
         self.input_norm_eps = float(eps)
         self._folded = None
+
+    def quantize_decode_weights(self, enable: bool = True) -> None:
+        """Prepare (or drop) e4m3 copies of the three weight matrices, one scale per weight row, for the
+        decode path: inference with at most 64 tokens then streams half the weight bytes (activations
+        are quantised per token on the fly; everything else stays 16-bit). Call again after the weights
+        change. Needs hidden and intermediate sizes that are multiples of 128; not combined with an
+        attached input norm or tensor parallelism."""
+        if not enable:
+            self._fp8 = None
+            return
+        if self.input_norm_weight is not None or self.parallel_mode == "tp":
+            raise NotImplementedError("8-bit decode weights are not combined with an input norm or tensor parallelism")
+        if self.hidden_size % 128 or self.intermediate_size % 128:
+            raise ValueError("8-bit decode weights need hidden_size and intermediate_size multiples of 128")
+        q = kernels.quantize_weight_rows_e4m3
+        self._fp8 = (q(self.gate_proj.weight), q(self.up_proj.weight), q(self.down_proj.weight))
 
     def _folded_weights(self):
         """(W_gate * weight, W_up * weight), cached until any of the three tensors is modified."""
@@ -331,6 +348,11 @@ class FusedGatedMLP(nn.Module):
         if self._decode_scratch is None or self._decode_scratch[0] != key:
             self._decode_scratch = (key, kernels.decode_scratch(
                 x.shape[0], self.hidden_size, self.intermediate_size, x.dtype, x.device))
+        if self._fp8 is not None and tp_group is None:
+            (wg8, wgs), (wu8, wus), (wd8, wds) = self._fp8
+            return kernels.decode_fwd_fp8(x, wg8, wgs, self.gate_proj.bias, wu8, wus, self.up_proj.bias, wd8, wds,
+                                          self.down_proj.bias, scratch=self._decode_scratch[1], act=self.act_fn,
+                                          residual=residual)
         own_bias = tp_group is None or self.tp_rank == 0
         w_gate, w_up, rs = self.gate_proj.weight, self.up_proj.weight, None
         if self.input_norm_weight is not None:

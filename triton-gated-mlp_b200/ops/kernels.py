@@ -417,6 +417,73 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     return y
 
 
+E4M3_MAX = 448.0
+
+
+def quantize_weight_rows_e4m3(w: Tensor):
+    """One-off preparation of a weight matrix for the 8-bit decode path: (w8, scale) with w8 the e4m3
+    bytes ([rows, cols] uint8) of w / scale[:, None] and scale[r] = amax|w[r, :]| / 448 (fp32), so that
+    w ~= w8 * scale[:, None]. Plain torch ops: this runs when weights are loaded, not per step."""
+    wf = w.detach().float()
+    scale = (wf.abs().amax(dim=1).clamp_min(1e-30) / E4M3_MAX).contiguous()
+    w8 = (wf / scale[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    return w8, scale
+
+
+def quantize_rows_e4m3(x: Tensor):
+    """Per-token dynamic quantisation on the GPU: (q, scale), q uint8 [M, K] holding e4m3(x / scale[:, None]),
+    scale[m] = amax|x[m, :]| / 448 (fp32)."""
+    dev = require_cuda(x)
+    x = _c(x)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.uint8, device=dev)
+    scale = torch.empty((M,), dtype=torch.float32, device=dev)
+    if M > 0:
+        with _on(dev):
+            check(load().gmlp_quantize_rows_e4m3(M, K, dtype_code(x.dtype), ptr(x), x.stride(0), ptr(q), ptr(scale),
+                                                 stream_of(x)))
+    return q, scale
+
+
+def decode_fp8_supported(M: int, K: int, N: int) -> bool:
+    return 0 < M <= DECODE_MAX_TOKENS and K % 128 == 0 and N % 128 == 0
+
+
+def decode_fwd_fp8(x: Tensor, w_gate8: Tensor, w_gate_scale: Tensor, b_gate: Tensor | None, w_up8: Tensor,
+                   w_up_scale: Tensor, b_up: Tensor | None, w_down8: Tensor, w_down_scale: Tensor,
+                   b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
+                   residual: Tensor | None = None) -> Tensor:
+    """decode_fwd on e4m3 weights (quantize_weight_rows_e4m3) with activations quantised per token on the fly;
+    x, biases, residual and the result stay 16-bit."""
+    dev = require_cuda(x, w_gate8, w_up8, w_down8, b_gate, b_up, b_down, residual)
+    dt = _same_dtype(x, b_gate, b_up, b_down, residual)
+    x, residual = _c(x), _c(residual)
+    M, K = x.shape
+    N = w_gate8.shape[0]
+    for w8, sc, shape in ((w_gate8, w_gate_scale, (N, K)), (w_up8, w_up_scale, (N, K)), (w_down8, w_down_scale, (K, N))):
+        if w8.dtype != torch.uint8 or tuple(w8.shape) != shape or not w8.is_contiguous():
+            raise ValueError(f"8-bit weights must be contiguous uint8 of shape {shape}")
+        if sc.dtype != torch.float32 or tuple(sc.shape) != (shape[0],) or not sc.is_contiguous():
+            raise ValueError(f"weight scales must be contiguous float32 of shape ({shape[0]},)")
+    if not decode_fp8_supported(M, K, N):
+        raise ValueError(f"8-bit decode path needs 1 <= M <= 64 and K, N multiples of 128; got M={M} K={K} N={N}")
+    if scratch is None:
+        scratch = decode_scratch(M, K, N, dt, dev)
+    x8 = torch.empty((M, K), dtype=torch.uint8, device=dev)
+    xs = torch.empty((M,), dtype=torch.float32, device=dev)
+    h = torch.empty((M, N), dtype=dt, device=dev)
+    h8 = torch.empty((M, N), dtype=torch.uint8, device=dev)
+    hs = torch.empty((M,), dtype=torch.float32, device=dev)
+    y = torch.empty((M, K), dtype=dt, device=dev)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
+    with _on(dev):
+        check(load().gmlp_decode_fwd_fp8(C.byref(prob), ptr(x), ptr(w_gate8), ptr(w_gate_scale), ptr(b_gate), ptr(w_up8),
+                                         ptr(w_up_scale), ptr(b_up), ptr(w_down8), ptr(w_down_scale), ptr(b_down),
+                                         ptr(residual), ptr(x8), ptr(xs), ptr(h), ptr(h8), ptr(hs), ptr(y), ptr(scratch),
+                                         scratch.numel() * scratch.element_size(), stream_of(x)))
+    return y
+
+
 def colsum(src: Tensor) -> Tensor:
     """Column sums of a [rows, cols] matrix (fp32 accumulation), in src's dtype."""
     dev = require_cuda(src)
