@@ -1,8 +1,8 @@
 """B200-native gated MLP: the reference's FusedGatedMLP API on hand-written sm_100a kernels.
 
-The directory name carries a hyphen, so the package is registered under the
-importable name `triton_gated_mlp_b200` by `load_package()` in the repository's
-`__graft_entry__.py` (tests and bench.py call it); after that
+The directory name carries a hyphen, so the package is imported under the name
+`triton_gated_mlp_b200` through the thin directory of that name at the repository
+root: with the root on sys.path,
 `from triton_gated_mlp_b200.gated_mlp import FusedGatedMLP` is the one-line swap
 for `from triton_gated_mlp.gated_mlp import FusedGatedMLP`.
 """
