@@ -35,14 +35,20 @@ typedef enum gmlp_status_t {
   GMLP_OK = 0,
   GMLP_ERR_SHAPE = -1,    /* a dimension is <= 0, or K/N not a multiple of 8 */
   GMLP_ERR_ALIGN = -2,    /* base address not 16-byte aligned or pitch not a multiple of 8 */
-  GMLP_ERR_DTYPE = -3,    /* dtype is not GMLP_BF16 / GMLP_FP16 */
+  GMLP_ERR_DTYPE = -3,    /* dtype is not a gmlp_dtype_t, or not one this entry point takes */
   GMLP_ERR_ARCH = -4,     /* current device is not compute capability 10.x */
   GMLP_ERR_LAUNCH = -5,   /* CUDA reported an error while encoding descriptors or launching */
   GMLP_ERR_ARG = -6,      /* NULL where a pointer is required, bad dropout_p, ... */
   GMLP_ERR_SCRATCH = -7   /* scratch buffer too small */
 } gmlp_status_t;
 
-typedef enum gmlp_dtype_t { GMLP_BF16 = 0, GMLP_FP16 = 1 } gmlp_dtype_t;
+/* GMLP_F32: fp32 matrices whose products are taken in tf32 (tcgen05.mma.kind::tf32, fp32
+ * accumulation), for modules kept in fp32 as the reference's own tests build them
+ * (tests/test_gated_mlp_fwd.py:23-38). Accepted by gmlp_hidden_fwd(_scaled), gmlp_down_fwd,
+ * gmlp_mlp_fwd, gmlp_gemm with both operands K-major (a_mn = b_mn = 0), gmlp_bwd_dact and
+ * gmlp_colsum; every other entry point answers GMLP_ERR_DTYPE. A compatibility path: the 16-bit
+ * types are the tuned ones. */
+typedef enum gmlp_dtype_t { GMLP_BF16 = 0, GMLP_FP16 = 1, GMLP_F32 = 2 } gmlp_dtype_t;
 
 /* Gate activations: the names the reference's module accepts (ACT_FWD,
  * src/triton_gated_mlp/gated_mlp.py:27-37); its fused kernels implement only silu and

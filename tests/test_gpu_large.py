@@ -22,8 +22,17 @@ def _randn(shape, std, dev, seed):
     return (torch.randn(shape, device=dev, generator=g) * std).to(torch.bfloat16)
 
 
+def _print_report(title, report):
+    """The literal and the contract's error figures of every tensor compared (shown with pytest -s or -rP)."""
+    print(f"\n{title}")
+    for name, r in report:
+        print(f"  {name:16s} max abs {r['max_abs']:.3e} (scaled {r['max_abs_scaled']:.3e})  mean rel {r['mean_rel']:.3e}  "
+              f"rms(want) {r['rms_want']:.3g}  max|want| {r['max_want']:.3g}")
+
+
 def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=128, n_quads=8, seed=0):
     seed_p, offset = 0x5EED, 1
+    report = []
     x = _randn((M, K), 1.0, dev, seed)
     m = pkg.FusedGatedMLP(K, N, bias=bias, dropout_p=p).to(dev).to(torch.bfloat16)
     with torch.no_grad():
@@ -55,8 +64,9 @@ def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=12
     if backward and p > 0:
         keep = np.stack([philox.keep_mask(1, N, p, seed_p, offset, row0=int(r), n_global=N)[0] for r in rows])
         ks = torch.from_numpy(keep.astype(np.float32) * philox.scale(p))
-    orc.assert_parity(f(y[ridx]), orc.forward(xs, wg, bg, wu, bu, wd, bd, ks), "y rows")
+    orc.assert_parity(f(y[ridx]), orc.forward(xs, wg, bg, wu, bu, wd, bd, ks), "y rows", report=report)
     if not backward:
+        _print_report(f"M={M} K={K} N={N} forward", report)
         return
     dys = f(dy[ridx])
     h, g, u = orc.hidden_forward(xs, wg, bg, wu, bu, ks)
@@ -64,7 +74,7 @@ def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=12
     if ks is not None:
         dh = dh * ks
     dx_want, _, _, _, _ = orc.hidden_backward(xs, wg, wu, g, u, dh)
-    orc.assert_parity(f(xr.grad[ridx]), dx_want, "dx rows")
+    orc.assert_parity(f(xr.grad[ridx]), dx_want, "dx rows", report=report)
 
     # ---- intermediate units: weight / bias gradients over all M rows
     quads = np.sort(rng.choice(N // 8, size=n_quads, replace=False))   # groups of 8 consecutive units
@@ -82,13 +92,14 @@ def _sliced_check(pkg, dev, M, K, N, bias, p, w_std, dy_std, backward, n_rows=12
         dhs, hs = dhs * kcs, hs * kcs
     d_gate = dhs * us * orc.silu_prime(gs)
     d_up = dhs * orc.silu(gs)
-    orc.assert_parity(f(m.gate_proj.weight.grad[cidx]), d_gate.T @ xf, "dW_gate units")
-    orc.assert_parity(f(m.up_proj.weight.grad[cidx]), d_up.T @ xf, "dW_up units")
-    orc.assert_parity(f(m.down_proj.weight.grad[:, cidx]), dyf.T @ hs, "dW_down units")
+    orc.assert_parity(f(m.gate_proj.weight.grad[cidx]), d_gate.T @ xf, "dW_gate units", report=report)
+    orc.assert_parity(f(m.up_proj.weight.grad[cidx]), d_up.T @ xf, "dW_up units", report=report)
+    orc.assert_parity(f(m.down_proj.weight.grad[:, cidx]), dyf.T @ hs, "dW_down units", report=report)
     if bias:
-        orc.assert_parity(f(m.gate_proj.bias.grad[cidx]), d_gate.sum(0), "db_gate units")
-        orc.assert_parity(f(m.up_proj.bias.grad[cidx]), d_up.sum(0), "db_up units")
-        orc.assert_parity(f(m.down_proj.bias.grad), dyf.sum(0), "db_down")
+        orc.assert_parity(f(m.gate_proj.bias.grad[cidx]), d_gate.sum(0), "db_gate units", report=report)
+        orc.assert_parity(f(m.up_proj.bias.grad[cidx]), d_up.sum(0), "db_up units", report=report)
+        orc.assert_parity(f(m.down_proj.bias.grad), dyf.sum(0), "db_down", report=report)
+    _print_report(f"M={M} K={K} N={N} forward+backward", report)
 
 
 def test_llama8b_forward_full_size(pkg, cuda_dev):
@@ -129,4 +140,7 @@ def test_decode_config_full_size(pkg, cuda_dev):
         x = _randn((M, K), 1.0, cuda_dev, M)
         with torch.no_grad():
             y = m(x)
-        orc.assert_parity(y.cpu(), orc.forward(x.float().cpu(), wg, None, wu, None, wd, None), f"decode M={M}")
+        report = []
+        orc.assert_parity(y.cpu(), orc.forward(x.float().cpu(), wg, None, wu, None, wd, None), f"decode M={M}",
+                          report=report)
+        _print_report(f"decode K={K} N={N}", report)

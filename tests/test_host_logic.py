@@ -54,8 +54,9 @@ def test_op_level_preconditions(pkg):
 
 def test_dtype_code(pkg):
     assert pkg._lib.dtype_code(torch.bfloat16) == 0 and pkg._lib.dtype_code(torch.float16) == 1
+    assert pkg._lib.dtype_code(torch.float32) == 2      # fp32 matrices, tf32 products
     with pytest.raises(NotImplementedError):
-        pkg._lib.dtype_code(torch.float32)
+        pkg._lib.dtype_code(torch.float64)
 
 
 def test_token_shard_ranges_cover_rows_once(pkg):

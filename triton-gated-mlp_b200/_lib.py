@@ -12,7 +12,7 @@ import torch
 
 LIB_PATH = Path(__file__).resolve().parent / "libgmlp.so"
 
-GMLP_BF16, GMLP_FP16 = 0, 1
+GMLP_BF16, GMLP_FP16, GMLP_F32 = 0, 1, 2
 
 # gmlp_act_t by the names the reference's module accepts (gated_mlp.py:27-37)
 ACT_CODES = {"silu": 0, "swish": 0, "no_act": 1, "relu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5, "leaky_relu": 6}
@@ -124,9 +124,11 @@ def dtype_code(dt: torch.dtype) -> int:
         return GMLP_BF16
     if dt == torch.float16:
         return GMLP_FP16
+    if dt == torch.float32:
+        return GMLP_F32   # fp32 matrices, tf32 products: the compatibility path
     raise NotImplementedError(
-        f"libgmlp computes in bfloat16 or float16 (fp32 accumulation); got {dt}. "
-        "Convert the module and its input with .to(torch.bfloat16) or .to(torch.float16)."
+        f"libgmlp computes in bfloat16, float16 or float32 (tf32 products); got {dt}. "
+        "Convert the module and its input with .to(torch.bfloat16), .to(torch.float16) or .to(torch.float32)."
     )
 
 

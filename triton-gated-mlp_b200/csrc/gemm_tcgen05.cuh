@@ -158,6 +158,22 @@ __device__ __forceinline__ void store8(T* p, const float (&v)[8]) {
   *reinterpret_cast<uint4*>(p) = q;
 }
 
+// fp32 matrices (the tf32 path): eight consecutive values are two 16-byte accesses.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+// Reduction elements in one 128-byte row of an operand tile: 64 for the 16-bit types, 32 for fp32.
+template <typename T>
+__host__ __device__ constexpr int row_elems() {
+  return 128 / static_cast<int>(sizeof(T));
+}
+
 // sigma(x) = 1 / (1 + e^-x) = 0.5 * tanh(x / 2) + 0.5: one MUFU op and two FMAs. The
 // hardware tanh approximation has a maximum relative error of about 2^-11, far below
 // the resolution of the 16-bit outputs.
@@ -473,10 +489,10 @@ __device__ __forceinline__ void fetch_block_async(const BlockView& bv, uint32_t 
 // DHIDDEN only: next_row0 / next_n0 locate this warp's rows and the first column of the NEXT tile
 // (next_row0 < 0: there is none); its first two units are requested at the end of this tile.
 template <int BN, int EPI, typename T, int ACTC>
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
-                                              int row0, int lane, int batch, int n0, int part,
-                                              const BlockView& bv, uint32_t stage, const T* bias0,
-                                              const T* bias1, bool drop_on, int next_row0, int next_n0) {
+__device__ __forceinline__ void epilogue_tile16(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
+                                                int row0, int lane, int batch, int n0, int part,
+                                                const BlockView& bv, uint32_t stage, const T* bias0,
+                                                const T* bias1, bool drop_on, int next_row0, int next_n0) {
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int row = row0 + lane;
   const bool row_ok = row < args.M;
@@ -701,6 +717,150 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMap
   }
 }
 
+// fp32 matrices (tf32 products): the store and gate/up epilogues for 4-byte outputs. A warp's
+// staging area holds one [32 rows x 32 columns] fp32 block (128-byte rows), so the plain store
+// sends its 64 columns as two blocks and the training gate/up kernel sends H, G and U one after
+// the other (re-reading the accumulators, which stay in TMEM until the tile is handed back).
+// This is the compatibility path for fp32 modules, not a tuned one.
+__device__ __forceinline__ void stage_store_f32(const CUtensorMap* map, uint32_t stage, int lane, int col, int row0,
+                                                const float (&v)[32]) {
+  if (lane == 0) bulk_wait_group_read<0>();  // the block may still feed the previous store
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 q;
+    q.x = __float_as_uint(v[4 * c]);
+    q.y = __float_as_uint(v[4 * c + 1]);
+    q.z = __float_as_uint(v[4 * c + 2]);
+    q.w = __float_as_uint(v[4 * c + 3]);
+    st_shared_v4(stage + staged_chunk<128>(lane, c), q);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(map, stage, col, row0);
+    bulk_commit_group();
+  }
+}
+
+template <int BN, int EPI, int ACTC>
+__device__ __forceinline__ void epilogue_tile_f32(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
+                                                  int row0, int lane, int batch, int n0, int part, uint32_t stage,
+                                                  const float* bias0, const float* bias1, bool drop_on) {
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int row = row0 + lane;
+  const bool row_ok = row < args.M;
+  const int M = args.M, N = args.N;
+  auto add8 = [&](const float* p, int gc, float* v) {  // v[0..8) += p[gc..gc+8) where inside the matrix
+    if (p != nullptr && gc < N) {
+      float b[8];
+      load8(p + gc, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += b[i];
+    }
+  };
+  if constexpr (EPI == EPI_STORE) {
+    constexpr int WCOLS = TILE_N / EPI_PARTS;
+    const int col = n0 + part * WCOLS;
+    if (col >= N || row0 >= M) return;
+    const float* const res =
+        (args.in0 && row_ok) ? static_cast<const float*>(args.in0) + static_cast<long long>(row) * args.ld_in : nullptr;
+#pragma unroll
+    for (int hh = 0; hh < WCOLS / 32; ++hh) {
+      if (col + hh * 32 >= N) break;  // warp-uniform
+      uint32_t acc[32];
+      tmem_ld_32x32(taddr + part * WCOLS + hh * 32, acc);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        add8(bias0, col + hh * 32 + j * 8, v + 8 * j);
+        add8(res, col + hh * 32 + j * 8, v + 8 * j);
+      }
+      stage_store_f32(batch ? maps.o1 : maps.o0, stage, lane, col + hh * 32, row0, v);
+    }
+  } else {  // EPI_SWIGLU
+    constexpr int WCOLS = TILE_N / EPI_PARTS;
+    static_assert(WCOLS == 32, "one [32 x 32] fp32 block per warp");
+    const int col = n0 + part * WCOLS;
+    if (col >= N || row0 >= M) return;
+    const bool save = args.out1 != nullptr;
+    const long long grow = args.drop.row0_global + row;
+    const float rsv = (args.row_scale != nullptr && row_ok) ? args.row_scale[row] : 1.0f;
+    // what: 0 = H (activation, product, dropout), 1 = G, 2 = U; sixteen columns at a time
+    auto emit = [&](const CUtensorMap* map, int what) {
+      if (lane == 0) bulk_wait_group_read<0>();  // the block may still feed the previous store
+      __syncwarp();
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t rg[16], ru[16];
+        if (what != 2) tmem_ld_32x16(taddr + part * WCOLS + hh * 16, rg);
+        if (what != 1) tmem_ld_32x16(taddr + TILE_N + part * WCOLS + hh * 16, ru);
+        tmem_ld_wait();
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int gc = col + hh * 16 + j * 8;
+          float g[8], u[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            g[i] = what != 2 ? __uint_as_float(rg[j * 8 + i]) * rsv : 0.f;
+            u[i] = what != 1 ? __uint_as_float(ru[j * 8 + i]) * rsv : 0.f;
+          }
+          if (what != 2) add8(bias0, gc, g);
+          if (what != 1) add8(bias1, gc, u);
+          if (what == 0) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = act_value(ACTC >= 0 ? ACTC : args.act, g[i]) * u[i];
+            if (drop_on) {
+              float f[8];
+              dropout_factors8_fast(args.drop, grow, args.drop.col0_global + gc, f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) g[i] *= f[i];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[j * 8 + i] = what == 2 ? u[i] : g[i];
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 q;
+          q.x = __float_as_uint(v[4 * c]);
+          q.y = __float_as_uint(v[4 * c + 1]);
+          q.z = __float_as_uint(v[4 * c + 2]);
+          q.w = __float_as_uint(v[4 * c + 3]);
+          st_shared_v4(stage + staged_chunk<128>(lane, hh * 4 + c), q);
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(map, stage, col, row0);
+        bulk_commit_group();
+      }
+    };
+    if (save) {
+      emit(maps.o1, 1);
+      emit(maps.o2, 2);
+    }
+    emit(maps.o0, 0);
+  }
+}
+
+template <int BN, int EPI, typename T, int ACTC>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& args, const OutMaps& maps, uint32_t taddr,
+                                              int row0, int lane, int batch, int n0, int part,
+                                              const BlockView& bv, uint32_t stage, const T* bias0,
+                                              const T* bias1, bool drop_on, int next_row0, int next_n0) {
+  if constexpr (sizeof(T) == 4)
+    epilogue_tile_f32<BN, EPI, ACTC>(args, maps, taddr, row0, lane, batch, n0, part, stage, bias0, bias1, drop_on);
+  else
+    epilogue_tile16<BN, EPI, T, ACTC>(args, maps, taddr, row0, lane, batch, n0, part, bv, stage, bias0, bias1,
+                                      drop_on, next_row0, next_n0);
+}
+
 // Row sums of this CTA's 128 rows of the MN-major A operand over the tile's SHARE of the
 // reduction blocks (block kb belongs to the column tile kb mod n_tiles of its row tile, so
 // the column tiles of one row tile divide the work between them), by the watcher warp while
@@ -820,7 +980,7 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtenso
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
     const int acc = local & 1;
     bool ok = true;
-    if (ASUM) {
+    if constexpr (ASUM) {
       const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
       const int mn0 = tc.m_tile * TILE_M + row_off;
       if (local > 0) named_bar_sync(EPI_DONE_BAR, EPI_BAR_THREADS);  // the staging area is free
@@ -865,7 +1025,7 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMap
   const bool drop_on = args.drop.thresh != 0u;
   const BlockView bv(lane);
   const uint32_t stage = epi_smem + ew * STORE_STAGE_BYTES;
-  if (EPI == EPI_DHIDDEN) {
+  if constexpr (EPI == EPI_DHIDDEN) {
     // the first tile's first two units; every later request is made from inside epilogue_tile
     if (first_tile < total_tiles) {
       const TileCoord t0 = decode_tile(first_tile, m_tiles, n_tiles, args.group_m);
@@ -940,6 +1100,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 64 == 0, "MN-major B arrives in 64-column boxes");
   static_assert(!ASUM || (A_MN && EPI == EPI_STORE), "row sums are taken of an MN-major A beside a plain store");
+  static_assert(sizeof(T) == 2 || (!A_MN && !B_MN && EPI != EPI_DHIDDEN),
+                "fp32 (tf32) operands: K-major only, store and gate/up epilogues only");
   constexpr uint32_t A_BYTES = BM * 128;
   constexpr uint32_t B_BYTES = BN * 128;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -1015,7 +1177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
             break;
           }
           const int seg = kb >= args.kb0 ? 1 : 0;
-          const int k0 = (seg ? kb - args.kb0 : kb) * BK;
+          const int k0 = (seg ? kb - args.kb0 : kb) * row_elems<T>();
           const CUtensorMap* ma = (seg | tc.batch) ? &tmA1 : &tmA0;
           const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
@@ -1076,9 +1238,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
           const uint64_t bdesc = make_smem_desc(sa + A_BYTES, B_LBO, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_f16(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
-                     bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
-                     (kb | k) != 0 ? 1u : 0u);
+            if (sizeof(T) == 4)
+              umma_tf32(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                        bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                       bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
+                       (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
           if (++stage == STAGES) {
@@ -1143,6 +1309,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   static_assert(!(EPI == EPI_SWIGLU) || (BN == 256 && !B_MN), "gate|up tile is 128 + 128 rows");
   static_assert(!B_MN || BN % 128 == 0, "MN-major B arrives in 64-column boxes per CTA");
   static_assert(!ASUM || (A_MN && EPI == EPI_STORE), "row sums are taken of an MN-major A beside a plain store");
+  static_assert(sizeof(T) == 2 || (!A_MN && !B_MN && EPI != EPI_DHIDDEN),
+                "fp32 (tf32) operands: K-major only, store and gate/up epilogues only");
   constexpr int HALF_N = BN / 2;  // B columns staged by each CTA
   constexpr uint32_t A_BYTES = BM * 128;
   constexpr uint32_t B_BYTES = HALF_N * 128;
@@ -1221,7 +1389,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
             break;
           }
           const int seg = kb >= args.kb0 ? 1 : 0;
-          const int k0 = (seg ? kb - args.kb0 : kb) * BK;
+          const int k0 = (seg ? kb - args.kb0 : kb) * row_elems<T>();
           const CUtensorMap* ma = (seg | tc.batch) ? &tmA1 : &tmA0;
           const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
@@ -1283,9 +1451,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
           const uint64_t bdesc = make_smem_desc(sa + A_BYTES, B_LBO, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_f16_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
-                          bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
-                          (kb | k) != 0 ? 1u : 0u);
+            if (sizeof(T) == 4)
+              umma_tf32_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                             bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                            bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
+                            (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(empty_bar(stage));
           if (++stage == STAGES) {

@@ -128,8 +128,9 @@ static uint32_t map_hash(const MapKey& k) {
 }
 
 constexpr int DTYPE_U8 = 100;  // internal: one-byte elements (e4m3 operands of the 8-bit decode path)
+static unsigned dtype_bytes(int dtype) { return dtype == DTYPE_U8 ? 1u : dtype == GMLP_F32 ? 4u : 2u; }
 
-// 2-D row-major matrix [outer, inner] of 16-bit (or, with DTYPE_U8, 8-bit) elements, swizzled rows of
+// 2-D row-major matrix [outer, inner] of 16-bit (DTYPE_U8: 8-bit, GMLP_F32: 32-bit) elements, swizzled rows of
 // `swizzle_bytes` (32 / 64 / 128), out-of-bounds elements read as zero and are not
 // written by stores.
 static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer,
@@ -142,10 +143,11 @@ static int encode_map(CUtensorMap* m, const void* base, int64_t inner, int64_t o
     return GMLP_OK;
   }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * (dtype == DTYPE_U8 ? 1 : 2)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * dtype_bytes(dtype)};
   const cuuint32_t box[2] = {box_inner, box_outer};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = dtype == DTYPE_U8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : dtype == GMLP_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : dtype == GMLP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUtensorMapSwizzle sw = swizzle_bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
@@ -179,11 +181,12 @@ struct Operand {
 
 static int encode_operand(CUtensorMap* m, const Operand& o, uint32_t kmajor_box_rows, int dtype) {
   if (!o.ptr) return fail(GMLP_ERR_ARG, "NULL matrix pointer");
-  if (!aligned16(o.ptr) || (o.ld % 8) != 0)
+  if (!aligned16(o.ptr) || (o.ld * dtype_bytes(dtype)) % 16 != 0)
     return fail(GMLP_ERR_ALIGN, "matrix base %p / pitch %lld not 16-byte aligned", o.ptr,
                 static_cast<long long>(o.ld));
-  if (o.mn_major) return encode_map(m, o.ptr, o.mn, o.k, o.ld, 64, BK, dtype);
-  return encode_map(m, o.ptr, o.k, o.mn, o.ld, BK, kmajor_box_rows, dtype);
+  const uint32_t row = 128u / dtype_bytes(dtype);  // elements in one 128-byte row of a tile
+  if (o.mn_major) return encode_map(m, o.ptr, o.mn, o.k, o.ld, row, BK, dtype);
+  return encode_map(m, o.ptr, o.k, o.mn, o.ld, row, kmajor_box_rows, dtype);
 }
 
 // --------------------------------------------------------------- launching --
@@ -281,35 +284,40 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   } else {
     mB1 = mB0;
   }
-  if (!ep.out0 || !aligned16(ep.out0) || (ep.ld_out % 8) != 0)
+  if (!ep.out0 || !aligned16(ep.out0) || (ep.ld_out * dtype_bytes(dtype)) % 16 != 0)
     return fail(GMLP_ERR_ALIGN, "output base / pitch not 16-byte aligned");
   // Output matrices as the epilogue's TMA stores see them: [32 rows x 64 columns] blocks
   // (128-byte rows) for the plain store, [32 x 32] (64-byte rows) for the gate/up kernel.
   // The dH epilogue stores through the load/store unit and takes no maps.
   CUtensorMap mO0 = mA0, mO1 = mA0, mO2 = mA0;
+  constexpr bool F32 = sizeof(T) == 4;  // fp32 outputs leave as [32 x 32] blocks (128-byte rows) from both epilogues
   if (EPI == EPI_STORE) {
-    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 64, 32, dtype, 128))) return rc;
+    const uint32_t bc = F32 ? 32 : 64;
+    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, bc, 32, dtype, 128))) return rc;
     if (batches == 2) {
       if (!ep.out1 || !aligned16(ep.out1))
         return fail(GMLP_ERR_ALIGN, "second output base not 16-byte aligned");
-      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 64, 32, dtype, 128))) return rc;
+      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, bc, 32, dtype, 128))) return rc;
     }
   } else if (EPI == EPI_SWIGLU) {
-    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
+    const int sw = F32 ? 128 : 64;
+    if ((rc = encode_map(&mO0, ep.out0, N, M, ep.ld_out, 32, 32, dtype, sw))) return rc;
     if (ep.out1) {
-      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
-      if ((rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 32, 32, dtype, 64))) return rc;
+      if ((rc = encode_map(&mO1, ep.out1, N, M, ep.ld_out, 32, 32, dtype, sw))) return rc;
+      if ((rc = encode_map(&mO2, ep.out2, N, M, ep.ld_out, 32, 32, dtype, sw))) return rc;
     }
   }
   GemmArgs args;
   memset(&args, 0, sizeof(args));
   args.M = static_cast<int>(M);
   args.N = static_cast<int>(N);
-  args.kb0 = static_cast<int>((a0.k + BK - 1) / BK);
-  args.kb1 = static_cast<int>((k1 + BK - 1) / BK);
+  constexpr int ROW = row_elems<T>();  // reduction elements per stage
+  args.kb0 = static_cast<int>((a0.k + ROW - 1) / ROW);
+  args.kb1 = static_cast<int>((k1 + ROW - 1) / ROW);
   args.batches = batches;
   args.act = ep.act;
-  args.idesc = make_idesc_f16(pair ? 2 * BM : BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
+  args.idesc = F32 ? make_idesc_tf32(pair ? 2 * BM : BM, BN)
+                   : make_idesc_f16(pair ? 2 * BM : BM, BN, dtype == GMLP_BF16 ? 1 : 0, A_MN, B_MN);
   args.status = dev->status_ptr;
   args.out0 = ep.out0;
   args.out1 = ep.out1;
@@ -370,6 +378,14 @@ template <int BN, bool A_MN, bool B_MN, int EPI, bool ASUM = false>
 static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, const Operand& a0,
                        const Operand* a1, const Operand& b0, const Operand* b1, int64_t k1,
                        int batches, const Epilogue& ep, uint32_t tuning_word, cudaStream_t stream) {
+  if (dtype == GMLP_F32) {
+    // fp32 matrices, tf32 products: K-major operands with the store and gate/up epilogues
+    if constexpr (!A_MN && !B_MN && EPI != EPI_DHIDDEN && !ASUM)
+      return launch_gemm_t<BN, A_MN, B_MN, EPI, float, false>(dev, dtype, M, N, a0, a1, b0, b1, k1, batches, ep,
+                                                              tuning_word, stream);
+    else
+      return fail(GMLP_ERR_DTYPE, "fp32 matrices are supported by the forward kernels and the K-major GEMM only");
+  }
   if (dtype == GMLP_BF16)
     return launch_gemm_t<BN, A_MN, B_MN, EPI, __nv_bfloat16, ASUM>(dev, dtype, M, N, a0, a1, b0, b1, k1,
                                                                    batches, ep, tuning_word, stream);
@@ -379,8 +395,8 @@ static int launch_gemm(const DeviceInfo* dev, int dtype, int64_t M, int64_t N, c
 
 static int check_problem(const gmlp_problem_t* p) {
   if (!p) return fail(GMLP_ERR_ARG, "NULL problem descriptor");
-  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
-    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", p->dtype);
+  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16 && p->dtype != GMLP_F32)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not a gmlp_dtype_t", p->dtype);
   if (p->M <= 0 || p->K <= 0 || p->N <= 0)
     return fail(GMLP_ERR_SHAPE, "M=%lld K=%lld N=%lld must be positive",
                 static_cast<long long>(p->M), static_cast<long long>(p->K),
@@ -789,7 +805,11 @@ int gmlp_bwd_dact(const gmlp_problem_t* p, const void* dh, const void* g, const 
   const long long cap = static_cast<long long>(dev->sm_count) * 16;
   if (blocks > cap) blocks = cap;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->dtype == GMLP_BF16)
+  if (p->dtype == GMLP_F32)
+    dact_kernel<float><<<static_cast<int>(blocks), 256, 0, st>>>(
+        static_cast<const float*>(dh), static_cast<const float*>(g), static_cast<const float*>(u),
+        static_cast<float*>(d_gate), static_cast<float*>(d_up), p->M, p->N, d, p->act);
+  else if (p->dtype == GMLP_BF16)
     dact_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(dh), static_cast<const __nv_bfloat16*>(g),
         static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(d_gate),
@@ -840,8 +860,8 @@ static int colsum_row_blocks(int64_t rows, int64_t cols) {
 
 static int colsum_check(int64_t rows, int64_t cols, int32_t dtype, const void* src, int64_t ld,
                         const void* dst) {
-  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
-    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16 && dtype != GMLP_F32)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not a gmlp_dtype_t", dtype);
   if (rows <= 0 || cols <= 0 || (cols % 8) != 0 || (ld % 8) != 0 || ld < cols)
     return fail(GMLP_ERR_SHAPE, "colsum needs rows > 0, cols and ld multiples of 8, ld >= cols");
   if (!src || !dst) return fail(GMLP_ERR_ARG, "NULL pointer argument");
@@ -859,7 +879,11 @@ static int colsum_launch(int64_t rows, int64_t cols, int32_t dtype, const void* 
   const dim3 grid(static_cast<unsigned>((cols + COLSUM_COLS - 1) / COLSUM_COLS),
                   static_cast<unsigned>(rb));
   const unsigned fin_blocks = static_cast<unsigned>((cols + 255) / 256);
-  if (dtype == GMLP_BF16) {
+  if (dtype == GMLP_F32) {
+    colsum_partial_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), rows, cols, ld,
+                                                       rows_per_block, part);
+    colsum_final_kernel<float><<<fin_blocks, 256, 0, st>>>(part, cols, rb, static_cast<float*>(dst));
+  } else if (dtype == GMLP_BF16) {
     colsum_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(src), rows, cols, ld, rows_per_block, part);
     colsum_final_kernel<__nv_bfloat16><<<fin_blocks, 256, 0, st>>>(
@@ -1155,8 +1179,8 @@ int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
 int gmlp_gemm(int32_t dtype, int32_t a_mn, int32_t b_mn, int64_t M, int64_t N, int64_t K,
               const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
               const void* bias, void* stream) {
-  if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
-    return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
+  if (dtype != GMLP_BF16 && dtype != GMLP_FP16 && dtype != GMLP_F32)
+    return fail(GMLP_ERR_DTYPE, "dtype %d is not a gmlp_dtype_t", dtype);
   if (M <= 0 || N <= 0 || K <= 0 || (N % 8) != 0 || (ldc % 8) != 0 || M > 0x7fffffffLL ||
       N > 0x7fffffffLL || K > 0x7fffffffLL)
     return fail(GMLP_ERR_SHAPE, "gemm needs positive M, N, K; N and ldc multiples of 8");

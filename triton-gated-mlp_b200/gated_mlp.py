@@ -117,6 +117,8 @@ class FusedGatedMLPFunction(Function):
                     "FusedGatedMLP: this graph's saved gate/up pre-activations were overwritten by an earlier "
                     "backward pass (inplace_backward=True writes d_gate / d_up over them). Set "
                     "module.inplace_backward = False to run backward more than once over one forward.")
+            if dy.dtype == torch.float32:
+                ctx.inplace_backward = False   # the fp32 path composes the pass from separate kernels
             ctx.consumed = ctx.inplace_backward
         # The bias gradients are column sums of d_gate / d_up / dy; the weight-gradient GEMMs deliver
         # them on the side (their A operand is exactly that matrix, transposed). Only a caller that
@@ -200,9 +202,14 @@ class _InputRMSNorm(Function):
 class FusedGatedMLP(nn.Module):
     """Gated MLP block; see the module docstring.
 
-    The kernels compute in bfloat16 or float16 with fp32 accumulation: cast the module
-    with .to(torch.bfloat16) or .to(torch.float16) (and move it to a CUDA device) before
-    the first forward; an fp32 module raises NotImplementedError, a CPU tensor GmlpError.
+    The tuned kernels compute in bfloat16 or float16 with fp32 accumulation: cast the
+    module with .to(torch.bfloat16) or .to(torch.float16) (and move it to a CUDA device).
+    A module left in float32, as the reference's own tests build it, runs too: its products
+    are taken in tf32 (tcgen05.mma.kind::tf32, 10-bit mantissa, fp32 accumulation; the
+    tolerance class of the reference's GPU tests, atol 1e-3) through the K-major kernels,
+    with transposed copies where the backward pass needs them: a compatibility path, not
+    a fast one (no decode kernels, no input norm, no 8-bit weights). A CPU tensor raises
+    GmlpError.
 
     Extra keyword-only arguments (all default to the single-GPU reference behaviour):
       parallel_mode  "none" | "token" | "tp". "token": this rank holds a slice of
@@ -410,7 +417,9 @@ class FusedGatedMLP(nn.Module):
         needs_grad = torch.is_grad_enabled() and (
             x.requires_grad or any(q.requires_grad for q in self.parameters())
             or (residual is not None and residual.requires_grad))
-        if (not needs_grad and p == 0.0 and x.is_cuda
+        if x.dtype == torch.float32 and self.input_norm_weight is not None:
+            raise NotImplementedError("the input norm is not available for float32 modules")
+        if (not needs_grad and p == 0.0 and x.is_cuda and x.dtype != torch.float32
                 and kernels.decode_supported(x.shape[0], self.hidden_size, self.intermediate_size)):
             y = self._decode_forward(x, tp_group, residual)
             return y.view(shapes) if len(shapes) > 2 else y

@@ -26,5 +26,5 @@ def mlp_hidden_states_bwd(x: Tensor, W_up: Tensor, W_gp: Tensor, grad_output: Te
     _, g, u = kernels.hidden_fwd(x, W_gp, None, W_up, None, save=True)
     d_gate, d_up = kernels.bwd_dact(grad_output, g, u)
     dx = kernels.bwd_dx(d_gate, d_up, W_gp, W_up)
-    dW_gp, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
+    dW_gp, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)[:2]
     return dx, dW_up, dW_gp

@@ -199,6 +199,26 @@ def mlp_bwd(dy: Tensor, x: Tensor, w_gate: Tensor, w_up: Tensor, w_down: Tensor,
     dt = _same_dtype(dy, x, w_gate, w_up, w_down, g, u, h)
     if (want_db_gate or want_db_up) and not want_dw_gate_up or (want_db_down and not want_dw_down):
         raise ValueError("bias gradients are produced by the weight-gradient kernels: ask for those too")
+    if dt == torch.float32:
+        # fp32 path: the pass composed of the per-kernel calls above (each of them tf32 GEMMs on K-major copies)
+        out = {}
+        if want_dx or want_dw_gate_up:
+            out["d_gate"], out["d_up"] = bwd_dhidden(dy, w_down, g, u, drop=drop, shard=shard, act=act)
+        if want_dx:
+            out["dx"] = bwd_dx(out["d_gate"], out["d_up"], w_gate, w_up)
+        if want_dw_gate_up:
+            r = bwd_dw_gate_up(out["d_gate"], out["d_up"], x, bias_grads=want_db_gate or want_db_up)
+            out["dw_gate"], out["dw_up"] = r[0], r[1]
+            if want_db_gate:
+                out["db_gate"] = r[2]
+            if want_db_up:
+                out["db_up"] = r[3]
+        if want_dw_down:
+            r = bwd_dw_down(dy, h, bias_grad=want_db_down)
+            out["dw_down"] = r[0] if want_db_down else r
+            if want_db_down:
+                out["db_down"] = r[1]
+        return out
     if inplace and not (g.is_contiguous() and u.is_contiguous()):
         raise ValueError("inplace=True needs contiguous g and u")
     dy, x, w_gate, w_up, w_down, g, u, h = (_c(t) for t in (dy, x, w_gate, w_up, w_down, g, u, h))
@@ -247,6 +267,9 @@ def bwd_dhidden(dy: Tensor, w_down: Tensor, g: Tensor, u: Tensor, drop: Dropout 
     those tensors: two [M, N] buffers fewer, and the pre-activations are gone afterwards."""
     dev = require_cuda(dy, w_down, g, u)
     dt = _same_dtype(dy, w_down, g, u)
+    if dt == torch.float32:
+        # fp32 path: dH by the K-major tf32 GEMM (W_down transposed once), then the elementwise kernel
+        return bwd_dact(gemm(dy, w_down.t().contiguous()), g, u, drop=drop, shard=shard, act=act)
     if inplace and not (g.is_contiguous() and u.is_contiguous()):
         raise ValueError("inplace=True needs contiguous g and u")
     dy, w_down, g, u = _c(dy), _c(w_down), _c(g), _c(u)
@@ -284,6 +307,13 @@ def bwd_dx(d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, out: Tens
     """dx = d_gate W_gate + d_up W_up, written into `out` when given."""
     dev = require_cuda(d_gate, d_up, w_gate, w_up)
     dt = _same_dtype(d_gate, d_up, w_gate, w_up)
+    if dt == torch.float32:
+        # fp32 path: one K-major tf32 GEMM over the concatenated reduction [d_gate | d_up] . [W_gate ; W_up]
+        dx32 = gemm(torch.cat((d_gate, d_up), dim=1), torch.cat((w_gate, w_up), dim=0).t().contiguous())
+        if out is None:
+            return dx32
+        out.copy_(dx32)
+        return out
     d_gate, d_up, w_gate, w_up = _c(d_gate), _c(d_up), _c(w_gate), _c(w_up)
     M, N = d_gate.shape
     K = w_gate.shape[1]
@@ -321,6 +351,11 @@ def bwd_dw_gate_up(d_gate: Tensor, d_up: Tensor, x: Tensor, tuning: int = 0, bia
     sums of d_gate and d_up, taken inside the same kernel."""
     dev = require_cuda(d_gate, d_up, x)
     dt = _same_dtype(d_gate, d_up, x)
+    if dt == torch.float32 and d_gate.shape[0] > 0:
+        # fp32 path: K-major tf32 GEMMs on transposed copies; bias gradients by the column-sum kernels
+        xt = x.t().contiguous()
+        dwg, dwu = gemm(d_gate.t().contiguous(), xt), gemm(d_up.t().contiguous(), xt)
+        return (dwg, dwu, colsum(d_gate), colsum(d_up)) if bias_grads else (dwg, dwu)
     d_gate, d_up, x = _c(d_gate), _c(d_up), _c(x)
     M, N = d_gate.shape
     K = x.shape[1]
@@ -350,6 +385,9 @@ def bwd_dw_down(dy: Tensor, h: Tensor, tuning: int = 0, bias_grad: bool = False)
     the same kernel."""
     dev = require_cuda(dy, h)
     dt = _same_dtype(dy, h)
+    if dt == torch.float32 and dy.shape[0] > 0:
+        dw32 = gemm(dy.t().contiguous(), h.t().contiguous())
+        return (dw32, colsum(dy)) if bias_grad else dw32
     dy, h = _c(dy), _c(h)
     M, K = dy.shape
     N = h.shape[1]
@@ -516,6 +554,9 @@ def gemm(a: Tensor, b: Tensor, a_mn: bool = False, b_mn: bool = False, bias: Ten
     """C = A B^T on the tcgen05 engine. a_mn: `a` is stored [K, M]; b_mn: `b` is stored [K, N]."""
     dev = require_cuda(a, b, bias)
     dt = _same_dtype(a, b, bias)
+    if dt == torch.float32 and (a_mn or b_mn):
+        # the tf32 kernels take K-major operands only: transpose the MN-major ones once
+        return gemm(a.t() if a_mn else a, b.t() if b_mn else b, bias=bias)
     a, b, bias = _c(a), _c(b), _c(bias)
     K, M = (a.shape if a_mn else a.shape[::-1])
     Kb, N = (b.shape if b_mn else b.shape[::-1])
