@@ -91,6 +91,11 @@ typedef struct gmlp_problem_t {
 #define GMLP_TUNE_PAIR_MODE(m) ((uint32_t)(m) & 3u)               /* 1 single-CTA kernel, 2 CTA pair */
 #define GMLP_TUNE_RASTER_GROUP(g) (((uint32_t)(g) & 0xFFFu) << 2)  /* row tiles per raster group */
 #define GMLP_TUNE_SM_LIMIT(n) (((uint32_t)(n) & 0xFFFu) << 14)     /* SMs a GEMM grid may occupy */
+/* gmlp_decode_fwd*: launch the first kernel as an ordinary kernel instead of a programmatic
+ * dependent, so that it reads no weight before everything ahead of it on the stream has
+ * finished. For the call that follows a kernel which WRITES the weights (optimiser step,
+ * dequantisation, weight merge). */
+#define GMLP_TUNE_ORDINARY_LAUNCH (1u << 26)
 
 /* H[M,N] = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)), act = p->act (SiLU by default).
  * Replaces mlp_hidden_states_fwd (src/triton_gated_mlp/ops/fwd.py:198-279, kernel
@@ -252,7 +257,8 @@ int gmlp_colsum_static(int64_t rows, int64_t cols, int32_t dtype, const void* sr
  * wait for it only before touching x, h, y or the scratch). The kernel immediately
  * before the call on the stream must therefore not write w_gate, w_up or w_down:
  * after an optimiser step, a dequantisation or a weight merge into those buffers,
- * put any other kernel (or an event wait) between it and the call. */
+ * set GMLP_TUNE_ORDINARY_LAUNCH in p->tuning for that call (or put any other kernel
+ * or an event wait between the writer and the call). */
 size_t gmlp_decode_scratch_bytes(const gmlp_problem_t* p);
 int gmlp_decode_fwd(const gmlp_problem_t* p, const void* x, const void* w_gate,
                     const void* b_gate, const void* w_up, const void* b_up, const void* w_down,

@@ -110,3 +110,46 @@ def test_decode_writes_into_given_buffer(pkg, cuda_dev):
     got = K_.decode_fwd(x, wg, None, wu, None, wd, None, out=buf[M:])
     assert got.data_ptr() == buf[M:].data_ptr() and torch.equal(got, want)
     assert buf[:M].abs().max().item() == 0
+
+
+def test_decode_right_after_the_weights_were_written(pkg, cuda_dev):
+    """The decode kernels start streaming weights while the kernel ahead of them is still running, unless the
+    call asks for an ordinary launch. With that flag a call placed directly behind the kernels that write the
+    weights must see the new weights, every time; the module sets the flag by itself when a parameter's
+    version counter has moved since its last decode call."""
+    K_ = pkg.ops.kernels
+    g = torch.Generator(device="cpu").manual_seed(21)
+    M, K, N = 16, 2048, 8192
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16).to(cuda_dev)
+    sets = []
+    for _ in range(2):
+        wg, wu = ((torch.randn((N, K), generator=g) * 0.03).to(torch.bfloat16).to(cuda_dev) for _ in range(2))
+        wd = (torch.randn((K, N), generator=g) * 0.03).to(torch.bfloat16).to(cuda_dev)
+        sets.append((wg, wu, wd))
+    scratch = K_.decode_scratch(M, K, N, torch.bfloat16, cuda_dev)
+    want = [K_.decode_fwd(x, s[0], None, s[1], None, s[2], None, scratch=scratch) for s in sets]
+    assert not torch.equal(want[0], want[1])
+    live = [t.clone() for t in sets[0]]
+    for i in range(1, 13):
+        for dst, src in zip(live, sets[i % 2]):
+            dst.copy_(src)                                   # the writers: three copy kernels, back to back
+        y = K_.decode_fwd(x, live[0], None, live[1], None, live[2], None, scratch=scratch, ordinary_launch=True)
+        assert torch.equal(y, want[i % 2]), f"call {i} read weights from before the copy"
+
+    case = orc.make_case(M, 512, 1024, False, torch.bfloat16, seed=5, w_std=0.03)
+    m = build_module(pkg, case, torch.bfloat16, cuda_dev).eval()
+    seen = []
+    real = K_.decode_fwd
+    try:
+        K_.decode_fwd = lambda *a, **kw: (seen.append(kw.get("ordinary_launch")), real(*a, **kw))[1]
+        with torch.no_grad():
+            xd = case.x.to(cuda_dev)
+            m(xd); m(xd)
+            m.up_proj.weight.mul_(1.5)                       # what an optimiser step or a weight merge does
+            y = m(xd); m(xd)
+    finally:
+        K_.decode_fwd = real
+    assert seen == [True, False, True, False]
+    import dataclasses
+    case2 = dataclasses.replace(case, w_up=(case.w_up.to(torch.bfloat16) * 1.5).to(case.w_up.dtype))
+    orc.assert_parity(y.cpu(), orc.forward_backward(case2, grads=False)["y"], "y after the update")

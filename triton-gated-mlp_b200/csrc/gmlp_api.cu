@@ -1064,13 +1064,16 @@ int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* 
   float* slots = reinterpret_cast<float*>(sc + l.slots_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int M = static_cast<int>(p->M);
+  // GMLP_TUNE_ORDINARY_LAUNCH: the first kernel is launched as an ordinary kernel, i.e. it starts
+  // (and reads weights) only when everything before it on the stream has finished.
+  const bool dep = (p->tuning & (1u << 26)) == 0;
   // H[M,N] = act(x Wg^T + bg) * (x Wu^T + bu): weight rows = N, reduction = K. Both kernels
   // are launched as programmatic dependents of whatever precedes them in the stream: they
   // start streaming weights at once and wait for the predecessor only before they read
   // activations or touch h, y or the scratch (which a preceding decode call may still use).
   rc = launch_decode<true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate, w_up, x, p->K,
                            b_gate, b_up, static_cast<const void*>(nullptr), row_scale, WeightScales{}, h, p->N,
-                           slots, reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
+                           slots, reinterpret_cast<int*>(sc + l.counters1_off), dep, p->act, st);
   if (rc) return rc;
   // y[M,K] = h Wd^T + bd: weight rows = K, reduction = N
   return launch_decode<false>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down,
@@ -1154,11 +1157,12 @@ int gmlp_decode_fwd_fp8(const gmlp_problem_t* p, const void* x, const void* w_ga
   // scale times weight-row scale); H (16-bit) -> e4m3 per token; down projection likewise.
   // The quantisers run as programmatic dependents too, so the kernel after each of them starts
   // streaming its weights while the one before it drains.
-  if ((rc = quantize_rows_launch(M, p->K, p->dtype, x, p->K, x8, x_scale, true, stream))) return rc;
+  const bool dep = (p->tuning & (1u << 26)) == 0;  // GMLP_TUNE_ORDINARY_LAUNCH, as in gmlp_decode_fwd
+  if ((rc = quantize_rows_launch(M, p->K, p->dtype, x, p->K, x8, x_scale, dep, stream))) return rc;
   rc = launch_decode<true, true>(l.mpad, p->dtype, dev, p->dtype, M, p->N, p->K, w_gate8, w_up8,
                                  static_cast<const void*>(x8), p->K, b_gate, b_up, static_cast<const void*>(nullptr),
                                  static_cast<const float*>(x_scale), WeightScales{w_gate_scale, w_up_scale}, h, p->N,
-                                 slots, reinterpret_cast<int*>(sc + l.counters1_off), true, p->act, st);
+                                 slots, reinterpret_cast<int*>(sc + l.counters1_off), dep, p->act, st);
   if (rc) return rc;
   if ((rc = quantize_rows_launch(M, p->N, p->dtype, h, p->N, h8, h_scale, true, stream))) return rc;
   return launch_decode<false, true>(l.mpad, p->dtype, dev, p->dtype, M, p->K, p->N, w_down8,

@@ -293,6 +293,7 @@ class FusedGatedMLP(nn.Module):
         self.input_norm_eps = 1e-6
         self._folded = None
         self._fp8 = None
+        self._decode_weight_versions = None
 
     def attach_input_norm(self, weight: Tensor, eps: float = 1e-6) -> None:
         """Put an RMSNorm in front of the MLP: forward(x) becomes MLP(x / rms(x) * weight), the step that
@@ -325,6 +326,7 @@ class FusedGatedMLP(nn.Module):
             raise ValueError("8-bit decode weights need hidden_size and intermediate_size multiples of 128")
         q = kernels.quantize_weight_rows_e4m3
         self._fp8 = (q(self.gate_proj.weight), q(self.up_proj.weight), q(self.down_proj.weight))
+        self._decode_weight_versions = None     # the next decode call follows the kernels that wrote the copies
 
     def _folded_weights(self):
         """(W_gate * weight, W_up * weight), cached until any of the three tensors is modified."""
@@ -355,11 +357,17 @@ class FusedGatedMLP(nn.Module):
         if self._decode_scratch is None or self._decode_scratch[0] != key:
             self._decode_scratch = (key, kernels.decode_scratch(
                 x.shape[0], self.hidden_size, self.intermediate_size, x.dtype, x.device))
+        # The decode kernels begin to stream weights while the kernel ahead of them on the stream is still
+        # running. If a parameter has been modified in place since the last decode call (an optimiser step, a
+        # weight merge), that kernel may be the writer: this one call starts as an ordinary launch.
+        versions = (self.gate_proj.weight._version, self.up_proj.weight._version, self.down_proj.weight._version)
+        ordinary = versions != self._decode_weight_versions
+        self._decode_weight_versions = versions
         if self._fp8 is not None and tp_group is None:
             (wg8, wgs), (wu8, wus), (wd8, wds) = self._fp8
             return kernels.decode_fwd_fp8(x, wg8, wgs, self.gate_proj.bias, wu8, wus, self.up_proj.bias, wd8, wds,
                                           self.down_proj.bias, scratch=self._decode_scratch[1], act=self.act_fn,
-                                          residual=residual)
+                                          residual=residual, ordinary_launch=ordinary)
         own_bias = tp_group is None or self.tp_rank == 0
         w_gate, w_up, rs = self.gate_proj.weight, self.up_proj.weight, None
         if self.input_norm_weight is not None:
@@ -367,7 +375,8 @@ class FusedGatedMLP(nn.Module):
         y = kernels.decode_fwd(x, w_gate, self.gate_proj.bias, w_up,
                                self.up_proj.bias, self.down_proj.weight,
                                self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1],
-                               act=self.act_fn, residual=residual if own_bias else None, row_scale=rs)
+                               act=self.act_fn, residual=residual if own_bias else None, row_scale=rs,
+                               ordinary_launch=ordinary)
         if tp_group is not None:
             if (self._peer is not None and self._peer.supports(y)
                     and y.numel() * y.element_size() <= self.peer_max_bytes):

@@ -430,9 +430,12 @@ def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device
 
 def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
                w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
-               residual: Tensor | None = None, out: Tensor | None = None, row_scale: Tensor | None = None) -> Tensor:
+               residual: Tensor | None = None, out: Tensor | None = None, row_scale: Tensor | None = None,
+               ordinary_launch: bool = False) -> Tensor:
     """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens,
-    written into `out` when given."""
+    written into `out` when given. The kernels normally start streaming weights while the preceding kernel
+    on the stream is still running; ordinary_launch=True makes the call wait for it first (for the call that
+    follows a kernel which writes the weights)."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
     dt = _same_dtype(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
     residual = _c(residual)
@@ -446,7 +449,7 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
         scratch = decode_scratch(M, K, N, dt, dev)
     h = torch.empty((M, N), dtype=dt, device=dev)
     y = _out_buffer(out, (M, K), dt, dev)
-    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act, _lib.tune_word(ordinary_launch=ordinary_launch))
     _check_row_scale(row_scale, M, dev)
     with _on(dev):
         check(load().gmlp_decode_fwd_scaled(C.byref(prob), ptr(x), ptr(row_scale), ptr(w_gate), ptr(b_gate), ptr(w_up),
@@ -490,7 +493,7 @@ def decode_fp8_supported(M: int, K: int, N: int) -> bool:
 def decode_fwd_fp8(x: Tensor, w_gate8: Tensor, w_gate_scale: Tensor, b_gate: Tensor | None, w_up8: Tensor,
                    w_up_scale: Tensor, b_up: Tensor | None, w_down8: Tensor, w_down_scale: Tensor,
                    b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
-                   residual: Tensor | None = None) -> Tensor:
+                   residual: Tensor | None = None, ordinary_launch: bool = False) -> Tensor:
     """decode_fwd on e4m3 weights (quantize_weight_rows_e4m3) with activations quantised per token on the fly;
     x, biases, residual and the result stay 16-bit."""
     dev = require_cuda(x, w_gate8, w_up8, w_down8, b_gate, b_up, b_down, residual)
@@ -513,7 +516,7 @@ def decode_fwd_fp8(x: Tensor, w_gate8: Tensor, w_gate_scale: Tensor, b_gate: Ten
     h8 = torch.empty((M, N), dtype=torch.uint8, device=dev)
     hs = torch.empty((M,), dtype=torch.float32, device=dev)
     y = torch.empty((M, K), dtype=dt, device=dev)
-    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act)
+    prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act, _lib.tune_word(ordinary_launch=ordinary_launch))
     with _on(dev):
         check(load().gmlp_decode_fwd_fp8(C.byref(prob), ptr(x), ptr(w_gate8), ptr(w_gate_scale), ptr(b_gate), ptr(w_up8),
                                          ptr(w_up_scale), ptr(b_up), ptr(w_down8), ptr(w_down_scale), ptr(b_down),
