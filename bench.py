@@ -58,6 +58,11 @@ WORKLOADS = {
     "decode-m32-bf16": dict(M=32, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
     "decode-m64-bf16": dict(M=64, K=8192, N=28672, bias=False, p=0.0, mode="decode"),
     # the same with e4m3 weights (one scale per weight row) and per-token e4m3 activations
+    # the same through the one-launch kernel (both weight streams in one persistent kernel)
+    "decode-m1-bf16-one-launch": dict(M=1, K=8192, N=28672, bias=False, p=0.0, mode="decode", one_launch=True),
+    "decode-m8-bf16-one-launch": dict(M=8, K=8192, N=28672, bias=False, p=0.0, mode="decode", one_launch=True),
+    "decode-m32-bf16-one-launch": dict(M=32, K=8192, N=28672, bias=False, p=0.0, mode="decode", one_launch=True),
+    "decode-m64-bf16-one-launch": dict(M=64, K=8192, N=28672, bias=False, p=0.0, mode="decode", one_launch=True),
     "decode-m1-fp8": dict(M=1, K=8192, N=28672, bias=False, p=0.0, mode="decode", fp8=True),
     "decode-m8-fp8": dict(M=8, K=8192, N=28672, bias=False, p=0.0, mode="decode", fp8=True),
     "decode-m64-fp8": dict(M=64, K=8192, N=28672, bias=False, p=0.0, mode="decode", fp8=True),
@@ -421,6 +426,7 @@ def run_decode(args, w, name):
                 p_.copy_((torch.randn(p_.shape, device=dev, generator=wgen) * 0.02).to(dt))
         if w.get("fp8"):
             mlp.quantize_decode_weights()
+        mlp.decode_one_launch = bool(w.get("one_launch"))
         sets.append(mlp)
     x = torch.randn((M, K), device=dev, dtype=dt, generator=torch.Generator(device=dev).manual_seed(1234 + rank))
 
@@ -519,13 +525,15 @@ def run_decode(args, w, name):
             "e2e": {"value": world * nbytes / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": (4 if w.get("fp8") else 2) * args.steps,
+            "gpu_launches": (4 if w.get("fp8") else 1 if w.get("one_launch") else 2) * args.steps,
             "launch_mode": "CUDA graph of two steps (one per weight set) replayed steps/2 times",
             "clocks": clocks.summary(),
             "check": check,
             "roofline": {
-                "kernel": "decode_stream_kernel<MPAD, gate+up> then <MPAD, down>, chained by programmatic dependent "
-                          "launch (timed together: timing them apart would break the chain)",
+                "kernel": ("decode_fused_kernel<MPAD>: gate+up and down streams from one persistent kernel"
+                           if w.get("one_launch") else
+                           "decode_stream_kernel<MPAD, gate+up> then <MPAD, down>, chained by programmatic dependent "
+                           "launch (timed together: timing them apart would break the chain)"),
                 "bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s", "frac": value / world / peak,
                 "peak_source": peak_src, "frac_of_nominal": value / world / NOMINAL_HBM_GBS,
                 "traffic": traffic, "traffic_note": traffic_note,
@@ -870,6 +878,20 @@ def run_gpu(args, w, name):
     x_dev2 = torch.empty_like(x)
     h2d_ms, _ = timed_steps(lambda: x_dev2.copy_(x_host, non_blocking=True), 10, barrier)
     d2h_ms, _ = timed_steps(lambda: y_host.copy_(x_dev2, non_blocking=True), 10, barrier)
+    # both directions at once (what the pipeline asks of the host in steady state), all ranks at once, no kernels
+    x_dev3 = torch.empty_like(x)
+    side = torch.cuda.Stream(dev)
+
+    def both_ways():
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            y_host.copy_(x_dev3, non_blocking=True)
+        for h in host_inputs:
+            x_dev2.copy_(h, non_blocking=True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    duplex_ms, _ = timed_steps(both_ways, 10, barrier)
+    del x_dev3
     status = pkg._lib.status_read(dev)
 
     # ---- comparator and sustained figures (default-size GEMM workloads; skipped for the largest shape)
@@ -911,10 +933,11 @@ def run_gpu(args, w, name):
 
     if dist_on:
         t = torch.tensor([elapsed_ms, e2e_ms, float(status), h2d_ms, d2h_ms,
-                          0.0 if check.get("ok", True) else 1.0], device=dev, dtype=torch.float64)
+                          0.0 if check.get("ok", True) else 1.0, duplex_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms, e2e_ms, status, h2d_ms, d2h_ms = t[0].item(), t[1].item(), int(t[2].item()), t[3].item(), t[4].item()
         check["ok_all_ranks"] = t[5].item() == 0.0
+        duplex_ms = t[6].item()
     assert status == 0, f"a kernel recorded a device-side timeout (code {status})"
 
     tp = None
@@ -953,8 +976,13 @@ def run_gpu(args, w, name):
                     "d2h_gbs_in_pipeline": d2h_bytes / (e2e_step * 1e-3) / 1e9,
                     "h2d_alone_gbs": x_host.numel() * x_host.element_size() / (h2d_ms / 10 * 1e-3) / 1e9,
                     "d2h_alone_gbs": d2h_bytes / (d2h_ms / 10 * 1e-3) / 1e9,
-                    "host_copy_floor_ms": max(h2d_ms / 10 * (2 if train else 1), d2h_ms / 10),
-                    "bound": "host copies" if max(h2d_ms / 10 * (2 if train else 1), d2h_ms / 10) > ms_step else "kernels"},
+                    # one step's copies in both directions at once, nothing else running: what the host side
+                    # (PCIe root, host memory) allows per step when every rank copies, i.e. the floor of e2e
+                    "copies_both_ways_ms": duplex_ms / 10,
+                    "copies_both_ways_gbs_per_direction": d2h_bytes / (duplex_ms / 10 * 1e-3) / 1e9,
+                    "host_copy_floor_ms": duplex_ms / 10,
+                    "frac_of_host_copy_floor": (duplex_ms / 10) / e2e_step,
+                    "bound": "host copies" if duplex_ms / 10 > ms_step else "kernels"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "check": check,

@@ -272,6 +272,18 @@ int gmlp_decode_fwd_scaled(const gmlp_problem_t* p, const void* x, const float* 
                            const void* w_down, const void* b_down, const void* residual, void* h, void* y,
                            void* scratch, size_t scratch_bytes, void* stream);
 
+/* gmlp_decode_fwd_scaled from ONE kernel launch (bf16 / fp16): a persistent kernel streams W_gate and
+ * W_up, then runs on into W_down without draining its operand ring; the CTAs hand the columns of H
+ * to each other through a device-wide count in the scratch instead of a kernel boundary. Same
+ * arguments, scratch (gmlp_decode_scratch_bytes), preconditions and result as the two-launch form.
+ * All CTAs of the grid (one per SM) must be able to run at the same time: launched beside another
+ * kernel that holds SMs for about a second, its waits run out and the status word is set. Replaces the
+ * reference's two separate steps src/triton_gated_mlp/gated_mlp.py:227-236 for small batches. */
+int gmlp_decode_fwd_fused(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                          const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                          const void* w_down, const void* b_down, const void* residual, void* h, void* y,
+                          void* scratch, size_t scratch_bytes, void* stream);
+
 /* ---- decode with 8-bit (e4m3) weights: half the bytes of the HBM-bound weight stream ----
  * No counterpart in the reference (its benchmark runs fp16 only,
  * src/triton_gated_mlp/benchmark.py:26-123). Weights are e4m3 bytes with one fp32 scale per

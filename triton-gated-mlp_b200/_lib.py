@@ -20,6 +20,7 @@ ACT_CODES = {"silu": 0, "swish": 0, "no_act": 1, "relu": 2, "gelu": 3, "sigmoid"
 # Every symbol include/gmlp.h declares; tests check that the library exports all of them.
 EXPORTS = (
     "gmlp_hidden_fwd", "gmlp_hidden_fwd_scaled", "gmlp_rms_rowscale", "gmlp_rms_bwd", "gmlp_decode_fwd_scaled",
+    "gmlp_decode_fwd_fused",
     "gmlp_quantize_rows_e4m3", "gmlp_decode_fwd_fp8",
     "gmlp_down_fwd", "gmlp_mlp_fwd", "gmlp_mlp_bwd", "gmlp_bwd_dhidden", "gmlp_bwd_dact", "gmlp_bwd_dx",
     "gmlp_bwd_dw_gate_up", "gmlp_bwd_dw_down", "gmlp_bias_grad_scratch_bytes", "gmlp_bwd_dw_gate_up_bias",
@@ -57,6 +58,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_rms_rowscale.argtypes = [i64, i64, i32, vp, i64, C.c_float, vp, vp, vp]
     lib.gmlp_rms_bwd.argtypes = [i64, i64, i32, vp, vp, vp, vp, vp]
     lib.gmlp_decode_fwd_scaled.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.c_size_t, vp]
+    lib.gmlp_decode_fwd_fused.argtypes = lib.gmlp_decode_fwd_scaled.argtypes
     lib.gmlp_quantize_rows_e4m3.argtypes = [i64, i64, i32, vp, i64, vp, vp, vp]
     lib.gmlp_decode_fwd_fp8.argtypes = [pp] + [vp] * 18 + [C.c_size_t, vp]
     lib.gmlp_down_fwd.argtypes = [pp, vp, vp, vp, vp, vp, vp]

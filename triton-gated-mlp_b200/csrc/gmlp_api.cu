@@ -12,6 +12,7 @@
 
 #include "../../include/gmlp.h"
 #include "decode_stream.cuh"
+#include "decode_fused.cuh"
 #include "elementwise.cuh"
 #include "gemm_tcgen05.cuh"
 #include "peer_reduce.cuh"
@@ -927,7 +928,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct DecodeLayout {
   int mpad;
-  size_t counters1_off, counters2_off, slots_off, total;
+  size_t counters1_off, counters2_off, sync_off, slots_off, total;
 };
 static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
   DecodeLayout l;
@@ -935,7 +936,8 @@ static DecodeLayout decode_layout(const gmlp_problem_t* p, int ctas) {
   const size_t t1 = static_cast<size_t>((p->N + 127) / 128), t2 = static_cast<size_t>((p->K + 127) / 128);
   l.counters1_off = 0;
   l.counters2_off = align_up(t1 * sizeof(int), 256);
-  l.slots_off = l.counters2_off + align_up(t2 * sizeof(int), 256);
+  l.sync_off = l.counters2_off + align_up(t2 * sizeof(int), 256);  // the one-launch kernel's two device-wide counts
+  l.slots_off = l.sync_off + 256;
   // one slot holds a CTA's partial row tile: all sub-tiles and accumulators of the larger kernel
   const size_t accs = l.mpad == 16
                           ? std::max<size_t>(2 * decode_subtiles<16, true>(), decode_subtiles<16, false>())
@@ -1029,6 +1031,68 @@ static int launch_decode(int mpad, int dtype, Args... args) {
               : launch_decode_t<32, DUAL, __half, FP8>(args...);
   return bf ? launch_decode_t<64, DUAL, __nv_bfloat16, FP8>(args...)
             : launch_decode_t<64, DUAL, __half, FP8>(args...);
+}
+
+// Both projections from one launch (decode_fused.cuh).
+template <int MPAD, typename T>
+static int launch_decode_fused_t(const DeviceInfo* dev, const gmlp_problem_t* p, const void* x,
+                                 const float* row_scale, const void* w_gate, const void* b_gate, const void* w_up,
+                                 const void* b_up, const void* w_down, const void* b_down, const void* residual,
+                                 void* h, void* y, float* slots, int* counters1, int* counters2, int* sync,
+                                 bool dependent, cudaStream_t stream) {
+  CUtensorMap mWg, mWu, mWd, mX, mH;
+  int rc;
+  const int M = static_cast<int>(p->M);
+  if ((rc = encode_map(&mWg, w_gate, p->K, p->N, p->K, BK, 128, p->dtype))) return rc;
+  if ((rc = encode_map(&mWu, w_up, p->K, p->N, p->K, BK, 128, p->dtype))) return rc;
+  if ((rc = encode_map(&mWd, w_down, p->N, p->K, p->N, BK, 128, p->dtype))) return rc;
+  if ((rc = encode_map(&mX, x, p->K, M, p->K, BK, MPAD, p->dtype))) return rc;
+  if ((rc = encode_map(&mH, h, p->N, M, p->N, BK, MPAD, p->dtype))) return rc;
+  DecodeFusedArgs a;
+  memset(&a, 0, sizeof(a));
+  a.M = M;
+  a.N = static_cast<int>(p->N);
+  a.K = static_cast<int>(p->K);
+  a.idesc = make_idesc_f16(128, MPAD, p->dtype == GMLP_BF16 ? 1 : 0, false, false);
+  a.status = dev->status_ptr;
+  a.b_gate = b_gate;
+  a.b_up = b_up;
+  a.b_down = b_down;
+  a.h = h;
+  a.y = y;
+  a.residual = residual;
+  a.row_scale = row_scale;
+  a.slots = slots;
+  a.counters1 = counters1;
+  a.counters2 = counters2;
+  a.sync = sync;
+  a.act = p->act;
+  a.dependent = dependent ? 1 : 0;
+  const long long total1 = ((p->N + 127) / 128) * (p->K / BK), total2 = ((p->K + 127) / 128) * (p->N / BK);
+  const long long most = std::max(total1, total2);
+  const int grid = static_cast<int>(most < dev->sm_count ? most : dev->sm_count);
+  constexpr size_t smem = fused_smem_bytes<MPAD>();
+  auto kfn = decode_fused_kernel<MPAD, T>;
+  static std::atomic<uint64_t> attr_done{0};
+  if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(DECODE_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  if (dependent) {
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, mWg, mWu, mWd, mX, mH, a);
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GMLP_ERR_LAUNCH, "kernel launch: %s", cudaGetErrorString(e));
+  return GMLP_OK;
 }
 
 extern "C" {
@@ -1126,6 +1190,46 @@ static int quantize_rows_launch(int64_t M, int64_t K, int32_t dtype, const void*
 int gmlp_quantize_rows_e4m3(int64_t M, int64_t K, int32_t dtype, const void* x, int64_t ld, void* q,
                             float* scale, void* stream) {
   return quantize_rows_launch(M, K, dtype, x, ld, q, scale, false, stream);
+}
+
+int gmlp_decode_fwd_fused(const gmlp_problem_t* p, const void* x, const float* row_scale,
+                          const void* w_gate, const void* b_gate, const void* w_up, const void* b_up,
+                          const void* w_down, const void* b_down, const void* residual, void* h, void* y,
+                          void* scratch, size_t scratch_bytes, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
+    return fail(GMLP_ERR_ARG, "the one-launch decode path takes bf16 or fp16");
+  if (p->M > 64) return fail(GMLP_ERR_SHAPE, "decode path takes at most 64 tokens, got %lld",
+                             static_cast<long long>(p->M));
+  if (p->dropout_p != 0.0f) return fail(GMLP_ERR_ARG, "decode path is inference only: dropout_p must be 0");
+  if ((rc = check_ptrs({x, w_gate, w_up, w_down, h, y, scratch}))) return rc;
+  if ((p->K % 64) != 0 || (p->N % 64) != 0)
+    return fail(GMLP_ERR_SHAPE, "decode path needs K and N multiples of 64");
+  if (row_scale && (reinterpret_cast<uintptr_t>(row_scale) & 3u) != 0)
+    return fail(GMLP_ERR_ALIGN, "row_scale must be 4-byte aligned");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const DecodeLayout l = decode_layout(p, dev->sm_count);
+  if (scratch_bytes < l.total)
+    return fail(GMLP_ERR_SCRATCH, "scratch holds %zu bytes, %zu needed", scratch_bytes, l.total);
+  char* sc = static_cast<char*>(scratch);
+  float* slots = reinterpret_cast<float*>(sc + l.slots_off);
+  int* c1 = reinterpret_cast<int*>(sc + l.counters1_off);
+  int* c2 = reinterpret_cast<int*>(sc + l.counters2_off);
+  int* sync = reinterpret_cast<int*>(sc + l.sync_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool dep = (p->tuning & (1u << 26)) == 0;  // GMLP_TUNE_ORDINARY_LAUNCH, as in gmlp_decode_fwd
+  const bool bf = p->dtype == GMLP_BF16;
+#define GMLP_FUSED(MP)                                                                                             \
+  (bf ? launch_decode_fused_t<MP, __nv_bfloat16>(dev, p, x, row_scale, w_gate, b_gate, w_up, b_up, w_down, b_down, \
+                                                 residual, h, y, slots, c1, c2, sync, dep, st)                     \
+      : launch_decode_fused_t<MP, __half>(dev, p, x, row_scale, w_gate, b_gate, w_up, b_up, w_down, b_down,        \
+                                          residual, h, y, slots, c1, c2, sync, dep, st))
+  if (l.mpad == 16) return GMLP_FUSED(16);
+  if (l.mpad == 32) return GMLP_FUSED(32);
+  return GMLP_FUSED(64);
+#undef GMLP_FUSED
 }
 
 int gmlp_decode_fwd_fp8(const gmlp_problem_t* p, const void* x, const void* w_gate8,

@@ -288,6 +288,7 @@ class FusedGatedMLP(nn.Module):
         self.tp_comm_sms = 16
         self.peer_max_bytes = 1024 * 1024
         self.check_status_every = 0
+        self.decode_one_launch = False   # both decode projections from one persistent kernel (16-bit weights)
         self._decode_calls = 0
         self.input_norm_weight = None
         self.input_norm_eps = 1e-6
@@ -376,7 +377,7 @@ class FusedGatedMLP(nn.Module):
                                self.up_proj.bias, self.down_proj.weight,
                                self.down_proj.bias if own_bias else None, scratch=self._decode_scratch[1],
                                act=self.act_fn, residual=residual if own_bias else None, row_scale=rs,
-                               ordinary_launch=ordinary)
+                               ordinary_launch=ordinary, one_launch=self.decode_one_launch)
         if tp_group is not None:
             if (self._peer is not None and self._peer.supports(y)
                     and y.numel() * y.element_size() <= self.peer_max_bytes):

@@ -431,9 +431,10 @@ def decode_scratch(M: int, K: int, N: int, dt: torch.dtype, device: torch.device
 def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b_up: Tensor | None,
                w_down: Tensor, b_down: Tensor | None, scratch: Tensor | None = None, act: str = "silu",
                residual: Tensor | None = None, out: Tensor | None = None, row_scale: Tensor | None = None,
-               ordinary_launch: bool = False) -> Tensor:
+               ordinary_launch: bool = False, one_launch: bool = False) -> Tensor:
     """y = (act(x W_gate^T + b_gate) * (x W_up^T + b_up)) W_down^T + b_down (+ residual) for M <= 64 tokens,
-    written into `out` when given. The kernels normally start streaming weights while the preceding kernel
+    written into `out` when given. one_launch=True runs both projections from one persistent kernel instead of
+    two chained ones. The kernels normally start streaming weights while the preceding kernel
     on the stream is still running; ordinary_launch=True makes the call wait for it first (for the call that
     follows a kernel which writes the weights)."""
     dev = require_cuda(x, w_gate, b_gate, w_up, b_up, w_down, b_down, residual)
@@ -452,7 +453,8 @@ def decode_fwd(x: Tensor, w_gate: Tensor, b_gate: Tensor | None, w_up: Tensor, b
     prob = _problem(M, K, N, dt, NO_DROPOUT, NO_SHARD, act, _lib.tune_word(ordinary_launch=ordinary_launch))
     _check_row_scale(row_scale, M, dev)
     with _on(dev):
-        check(load().gmlp_decode_fwd_scaled(C.byref(prob), ptr(x), ptr(row_scale), ptr(w_gate), ptr(b_gate), ptr(w_up),
+        fn = load().gmlp_decode_fwd_fused if one_launch else load().gmlp_decode_fwd_scaled
+        check(fn(C.byref(prob), ptr(x), ptr(row_scale), ptr(w_gate), ptr(b_gate), ptr(w_up),
                                             ptr(b_up), ptr(w_down), ptr(b_down), ptr(residual), ptr(h), ptr(y),
                                             ptr(scratch), scratch.numel() * scratch.element_size(), stream_of(x)))
     return y
