@@ -365,26 +365,39 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
       };
       auto slot_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * SLOT_BYTES; };
       // phase 1, unit u in slots s0 (W_gate + x) and s1 (W_up)
-      auto load_w1 = [&](long long u, int s0, int s1) {
-        const int tile = static_cast<int>(u / kbt1);
-        const int kb = static_cast<int>(u - static_cast<long long>(tile) * kbt1);
+      // (row tile, reduction block) of the next unit to issue, per stream, kept incrementally: a 64-bit
+      // division per unit would cost the issuing thread a good part of the time a 16 KB unit takes to stream
+      int w_tile = static_cast<int>(u1_begin / kbt1);
+      int w_kb = static_cast<int>(u1_begin - static_cast<long long>(w_tile) * kbt1);
+      int a_kb = w_kb;
+      auto load_w1 = [&](int s0, int s1) {
+        const int tile = w_tile, kb = w_kb;
+        if (++w_kb == kbt1) {
+          w_kb = 0;
+          ++w_tile;
+        }
         mbar_expect_tx(full_bar(s0), SLOT_BYTES);
         tma_load_2d_hint(slot_addr(s0), &tmWg, full_bar(s0), kb * BK, tile * 128, pol_w);
         mbar_expect_tx(full_bar(s1), W_BYTES);
         tma_load_2d_hint(slot_addr(s1), &tmWu, full_bar(s1), kb * BK, tile * 128, pol_w);
       };
-      auto load_x = [&](long long u, int s0) {
-        const int kb = static_cast<int>(u % kbt1);
+      auto load_x = [&](int s0) {
+        const int kb = a_kb;
+        if (++a_kb == kbt1) a_kb = 0;
         tma_load_2d_hint(slot_addr(s0) + W_BYTES, &tmX, full_bar(s0), kb * BK, 0, pol_a);
       };
-      auto load_w2 = [&](long long u, int s) {
-        const int tile = static_cast<int>(u / kbt2);
-        const int kb = static_cast<int>(u - static_cast<long long>(tile) * kbt2);
+      auto load_w2 = [&](int s) {
+        const int tile = w_tile, kb = w_kb;
+        if (++w_kb == kbt2) {
+          w_kb = 0;
+          ++w_tile;
+        }
         mbar_expect_tx(full_bar(s), SLOT_BYTES);
         tma_load_2d_hint(slot_addr(s), &tmWd, full_bar(s), kb * BK, tile * 128, pol_w);
       };
-      auto load_h = [&](long long u, int s) {
-        const int kb = static_cast<int>(u % kbt2);
+      auto load_h = [&](int s) {  // blocks of H go out in unit order, so the count runs on
+        const int kb = a_kb;
+        if (++a_kb == kbt2) a_kb = 0;
         tma_load_2d_hint(slot_addr(s) + W_BYTES, &tmH, full_bar(s), kb * BK, 0, pol_a);
       };
 
@@ -395,9 +408,9 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
         // kernel's last CTAs are still running, then wait for it and add the activations.
         const long long left = u1_end - u1_begin;
         const long long n0 = left < STAGES / 2 ? left : STAGES / 2;
-        for (long long i = 0; i < n0; ++i) load_w1(u1_begin + i, static_cast<int>(2 * i), static_cast<int>(2 * i + 1));
+        for (long long i = 0; i < n0; ++i) load_w1(static_cast<int>(2 * i), static_cast<int>(2 * i + 1));
         pdl_wait();
-        for (long long i = 0; i < n0; ++i) load_x(u1_begin + i, static_cast<int>(2 * i));
+        for (long long i = 0; i < n0; ++i) load_x(static_cast<int>(2 * i));
         u = u1_begin + n0;
         for (long long i = 0; i < 2 * n0; ++i) next();
       }
@@ -414,8 +427,8 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
         }
         const int s1 = stage;
         next();
-        load_w1(u, s0, s1);
-        load_x(u, s0);
+        load_w1(s0, s1);
+        load_x(s0);
       }
 
       // ---- phase 2: W_down tiles at once, their blocks of H when all of H is there
@@ -434,10 +447,13 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
         }
         return true;
       };
-      auto flush = [&](long long u_next) {  // units u_next - pending .. u_next - 1 sit in the slots before `stage`
-        for (int i = pending; i >= 1; --i) load_h(u_next - i, (stage - i + 2 * STAGES) % STAGES);
+      auto flush = [&]() {  // the last `pending` units sit in the slots before `stage`, oldest first
+        for (int i = pending; i >= 1; --i) load_h((stage - i + 2 * STAGES) % STAGES);
         pending = 0;
       };
+      w_tile = static_cast<int>(u2_begin / kbt2);
+      w_kb = static_cast<int>(u2_begin - static_cast<long long>(w_tile) * kbt2);
+      a_kb = w_kb;
       if (ok) {
         for (u = u2_begin; u < u2_end; ++u) {
           if (!h_ready && pending == STAGES) {  // the slot to reuse is itself waiting for H
@@ -446,17 +462,17 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
               break;
             }
             h_ready = true;
-            flush(u);
+            flush();
           }
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abortp)) {
             ok = false;
             break;
           }
-          load_w2(u, stage);
+          load_w2(stage);
           if (!h_ready) h_ready = h_poll();
           if (h_ready) {
-            flush(u);
-            load_h(u, stage);
+            flush();
+            load_h(stage);
           } else {
             ++pending;
           }
@@ -464,7 +480,7 @@ decode_fused_kernel(const __grid_constant__ CUtensorMap tmWg, const __grid_const
         }
         if (ok && pending > 0) {
           if (h_wait()) {
-            flush(u2_end);
+            flush();
           } else {
             ok = false;
           }

@@ -210,9 +210,17 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      auto load_weights = [&](long long u, int st) {
-        const int tile = static_cast<int>(u / args.kbt);
-        const int kb = static_cast<int>(u - static_cast<long long>(tile) * args.kbt);
+      // (row tile, reduction block) of the unit being issued, kept incrementally: a 64-bit division per
+      // unit costs the issuing thread a good part of the time one 16 KB unit takes to stream
+      int w_tile = static_cast<int>(u_begin / args.kbt);
+      int w_kb = static_cast<int>(u_begin - static_cast<long long>(w_tile) * args.kbt);
+      int a_kb = w_kb;
+      auto load_weights = [&](int st) {  // the next unit's weights
+        const int tile = w_tile, kb = w_kb;
+        if (++w_kb == args.kbt) {
+          w_kb = 0;
+          ++w_tile;
+        }
         const uint32_t sw = smem_base + st * STAGE_BYTES;
         const uint32_t fb = full_bar(st);
         mbar_expect_tx(fb, STAGE_BYTES);
@@ -225,8 +233,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
                              tile * TILE_ROWS + b * BOX_ROWS, pol_w);
         }
       };
-      auto load_act = [&](long long u, int st) {
-        const int kb = static_cast<int>(u % args.kbt);
+      auto load_act = [&](int st) {  // the next unit's activations (issued in the same order as the weights)
+        const int kb = a_kb;
+        if (++a_kb == args.kbt) a_kb = 0;
         tma_load_2d_hint(smem_base + st * STAGE_BYTES + ACT_OFF, &tmAct, full_bar(st), kb * RED, 0, pol_a);
       };
       long long u = u_begin;
@@ -235,9 +244,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
         // that kernel's last CTAs are still running, then wait for it and add the
         // activations of the same stages.
         const long long n0 = (u_end - u_begin) < STAGES ? (u_end - u_begin) : STAGES;
-        for (long long i = 0; i < n0; ++i) load_weights(u_begin + i, static_cast<int>(i));
+        for (long long i = 0; i < n0; ++i) load_weights(static_cast<int>(i));
         pdl_wait();
-        for (long long i = 0; i < n0; ++i) load_act(u_begin + i, static_cast<int>(i));
+        for (long long i = 0; i < n0; ++i) load_act(static_cast<int>(i));
         u = u_begin + n0;
         stage = static_cast<int>(n0 % STAGES);
         phase = (n0 == STAGES) ? 1u : 0u;
@@ -247,8 +256,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap tmW0,
           ok = false;
           break;
         }
-        load_weights(u, stage);
-        load_act(u, stage);
+        load_weights(stage);
+        load_act(stage);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1u;
