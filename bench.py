@@ -710,6 +710,7 @@ def tp_section(pkg, dev, rank, world, dist):
                                               want["dup_proj.weight"], dt, units=int(units.numel()))
         parity["dW_down_units"] = parity_record(m.down_proj.weight.grad[:, u_dev].float().cpu(),
                                                 want["ddown_proj.weight"], dt, units=int(units.numel()))
+    want_y = want["y"] if rank == 0 else None
     del y, xg, want
     m.zero_grad(set_to_none=True)
 
@@ -741,6 +742,28 @@ def tp_section(pkg, dev, rank, world, dist):
     pre["fwd_bwd_frac_of_nominal_per_gpu"] = pre["fwd_bwd_tflops_whole_job"] / world / NOMINAL_BF16_TFLOPS
     # what the forward would take with the all-reduce fully hidden: names the limiter
     pre["fwd_ms_minus_allreduce"] = pre["fwd_ms"] - pre["allreduce_alone_ms"]
+    # the same forward with the down projection pushing the other ranks' row blocks into their inboxes from its
+    # epilogue (scatter overlapped with the GEMM) and one kernel per rank that sums and hands round: no NCCL call
+    del buf
+    torch.cuda.empty_cache()
+    try:
+        m.enable_peer_output_sum(max_tokens=M)
+        with torch.no_grad():
+            yp = m(x)
+        if rank == 0:
+            parity["y_rows_pushed_sum"] = parity_record(yp[rows.to(dev)].float().cpu(), want_y, dt,
+                                                        rows=int(rows.numel()))
+        del yp
+        pre["fwd_ms_pushed_sum"] = event_timed(fwd, 10, dev, dist)
+        pre["fwd_pushed_sum_tflops_whole_job"] = 6.0 * M * K * N / (pre["fwd_ms_pushed_sum"] * 1e-3) / 1e12
+        pre["fwd_bwd_ms_pushed_sum_dx_chunks_of_4096_rows"] = None
+        m.tp_chunk_rows = 4096
+        pre["fwd_bwd_ms_pushed_sum_dx_chunks_of_4096_rows"] = event_timed(fwd_bwd, 5, dev, dist)
+        m.tp_chunk_rows = 0
+        m._peer_sum.close()
+        m._peer_sum = None
+    except Exception as e:   # the line must still be printed
+        pre["pushed_sum_error"] = f"{type(e).__name__}: {e}"
     out["prefill"] = pre
     oks = [r[k]["ok"] for r in decode for k in ("parity_nccl_sum", "parity_peer_sum") if k in r]
     oks += [v["ok"] for v in parity.values()]

@@ -382,6 +382,25 @@ int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, const void*
                         void* const* regions, int32_t rank, int32_t world, void* dst,
                         int32_t dependent, void* stream);
 
+/* ---- tensor-parallel down projection that scatters while it computes ----
+ * gmlp_down_fwd_push is gmlp_down_fwd (the step src/triton_gated_mlp/gated_mlp.py:236 of the reference,
+ * on this rank's shard of the intermediate dimension) whose epilogue sends every finished block
+ * of the partial y to the rank that owns its rows: rank r owns rows [r M / world, (r + 1) M / world);
+ * blocks of this rank's own rows are stored to y as usual, all others go with plain peer stores over
+ * NVLink into the owner's inbox (regions / max_elems as for gmlp_peer_allreduce, sized for
+ * M * K elements) while the remaining tiles are still being computed: the scatter half of a
+ * reduce-scatter inside the GEMM. gmlp_peer_reduce_gather, enqueued behind it on the same stream by
+ * every rank, raises and awaits the flags, adds the world partials of this rank's rows in rank order in
+ * fp32, writes them to y and hands them round, so that y ends as the full sum on every rank (identical
+ * bits). M must be a multiple of 32 * world, n = M * K a multiple of 8 * world; y contiguous. The
+ * two calls form one step of the call sequence all ranks share; regions used this way must not be
+ * used by plain gmlp_peer_allreduce calls in between on another stream. Waits are bounded as there. */
+int gmlp_down_fwd_push(const gmlp_problem_t* p, const void* h, const void* w_down, const void* b_down,
+                       const void* residual, void* y, int64_t max_elems, void* const* regions, int32_t rank,
+                       int32_t world, void* stream);
+int gmlp_peer_reduce_gather(int32_t dtype, int64_t n, int64_t max_elems, void* y, void* const* regions,
+                            int32_t rank, int32_t world, void* stream);
+
 /* Reads and clears the current device's status word (synchronises the device).
  * 0 = no kernel gave up a wait since the last read. */
 int gmlp_status_read(int* value);

@@ -148,6 +148,45 @@ def main():
             y_back = md(cased.x.to(dev))      # a closed peer group: the module is back on the NCCL sum
         assert torch.equal(y_back, y_nccl)
 
+        # ---------------- prefill / training forward whose down projection scatters its partial output into
+        # the owners' inboxes from its epilogue (no NCCL call in the forward pass)
+        Mp, Kp, Np = 512, 512, 256 * world
+        casep = orc.make_case(Mp, Kp, Np, True, dt, seed=14, w_std=0.5 * Kp ** -0.5, dy_std=0.05)
+        wantp = orc.forward_backward(casep)
+        _, colsp = P.tp_shard_range(Np, rank, world)
+        mp = pkg.FusedGatedMLP(Kp, colsp, bias=True, parallel_mode="tp")
+        mp.load_state_dict(P.shard_tp_state_dict(casep.state_dict(), rank, world))
+        mp = mp.to(dev).to(dt).eval()
+        xp = casep.x.to(dev)
+        with torch.no_grad():
+            y_ref = mp(xp)                                   # NCCL sum
+        mp.enable_peer_output_sum(max_tokens=Mp)
+        with torch.no_grad():
+            ys = [mp(xp) for _ in range(6)]                  # back to back, no host synchronisation
+            y_half = mp(xp[:256])                            # fewer rows than the capacity
+        assert all(torch.equal(ys[0], t) for t in ys[1:]), "the pushed sum is not repeatable"
+        orc.assert_parity(ys[0].cpu(), wantp["y"], "tp y (pushed sum)")
+        orc.assert_parity(y_half.cpu(), wantp["y"][:256], "tp y (pushed sum, 256 rows)")
+        assert (ys[0].float() - y_ref.float()).abs().max().item() <= 4e-2
+        every = [torch.empty_like(ys[0]) for _ in range(world)]
+        dist.all_gather(every, ys[0])
+        assert all(torch.equal(e, every[0]) for e in every), "ranks disagree on the pushed sum"
+        mp.train()
+        xg = casep.x.to(dev).requires_grad_(True)
+        yg = mp(xg)
+        yg.backward(casep.dy.to(dev))
+        assert torch.equal(yg.detach(), ys[0])
+        orc.assert_parity(xg.grad.cpu(), wantp["dx"], "tp dx (after a pushed forward)")
+        fullp = P.gather_tp_grads({n: q.grad for n, q in mp.named_parameters()})
+        for n, g in fullp.items():
+            orc.assert_parity(g.cpu(), wantp["d" + n], "tp d" + n + " (after a pushed forward)")
+        with torch.no_grad():
+            y_odd = mp.eval()(xp[:96])                       # 96 rows do not split into 32-row blocks per rank
+        orc.assert_parity(y_odd.cpu(), wantp["y"][:96], "tp y (NCCL fallback)")
+        torch.cuda.synchronize()
+        assert pkg._lib.status_read(dev) == 0
+        mp._peer_sum.close()
+
         # ---------------- token sharding: no collective, mask rows offset
         Mt = 256 * world
         caset = orc.make_case(Mt, K, 512, False, dt, seed=13, w_std=0.5 * K ** -0.5, dy_std=0.05)

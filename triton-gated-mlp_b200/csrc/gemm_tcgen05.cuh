@@ -62,6 +62,16 @@ struct GemmArgs {
   void* asum_out[2];  // per batch: [M] sums, in the matrices' 16-bit type
   float* asum_part;   // [batches][n_tiles][m_tiles * tile rows] fp32 partial sums
   int* asum_cnt;      // [batches][m_tiles * tile rows / 128] arrivals; zero on entry and on exit
+  // Tensor-parallel down projection (EPI_STORE): the row blocks of the output belong to the ranks in
+  // contiguous shares of push_rows rows. A finished block of a row that another rank owns does not go to
+  // out0 but straight into that rank's inbox (plain peer stores over NVLink), at the same [row, column]
+  // offset: the scatter half of a reduce-scatter, done tile by tile from the GEMM's epilogue while the other
+  // tiles are still being computed. push_world = 0: off.
+  char* push_base[8];          // per rank: its inbox slot for this rank's partials, parity 0
+  long long push_parity_bytes; // distance to the same slot of parity 1
+  const unsigned int* push_epoch;  // calls completed by this rank's sum kernel: the next call's number is +1
+  int push_rows;               // rows per owner (a multiple of 32)
+  int push_rank, push_world;
 };
 
 constexpr int BM = 128;        // rows per tile = TMEM lanes
@@ -536,11 +546,29 @@ __device__ __forceinline__ void epilogue_tile16(const GemmArgs& args, const OutM
         st_shared_v4(stage + staged_chunk<128>(lane, hh * 4 + j), pack8<T>(v));
       }
     }
-    fence_proxy_async_smem();  // the staged rows become visible to the TMA engine
-    __syncwarp();
-    if (lane == 0) {
-      tma_store_2d(batch ? maps.o1 : maps.o0, stage, col, row0);
-      bulk_commit_group();
+    const int owner = args.push_world > 0 ? row0 / args.push_rows : -1;
+    if (owner >= 0 && owner != args.push_rank) {
+      // another rank's rows: the staged block leaves with plain 16-byte stores into that rank's inbox,
+      // eight lanes per 128-byte row (the sum kernel that follows on every rank raises the flags)
+      __syncwarp();
+      const unsigned int call = __ldcg(args.push_epoch) + 1u;
+      T* const dst = reinterpret_cast<T*>(args.push_base[owner] + (call & 1u) * args.push_parity_bytes);
+      const int c8 = lane & 7;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        const uint4 q = ld_shared_v4(stage + staged_chunk<128>(r, c8));
+        const int gr = row0 + r, gc = col + c8 * 8;
+        if (gr < M && gc < N) *reinterpret_cast<uint4*>(dst + static_cast<long long>(gr) * args.ld_out + gc) = q;
+      }
+      __syncwarp();  // the block is free again
+    } else {
+      fence_proxy_async_smem();  // the staged rows become visible to the TMA engine
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(batch ? maps.o1 : maps.o0, stage, col, row0);
+        bulk_commit_group();
+      }
     }
   } else if constexpr (EPI == EPI_SWIGLU) {
     constexpr int WCOLS = TILE_N / EPI_PARTS;  // hidden columns per warp

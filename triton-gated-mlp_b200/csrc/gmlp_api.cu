@@ -208,6 +208,11 @@ struct Epilogue {
   void* asum_out[2] = {nullptr, nullptr};
   float* asum_part = nullptr;
   int* asum_cnt = nullptr;
+  // push of other ranks' row blocks into their inboxes (tensor-parallel down projection), see GemmArgs
+  char* push_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  long long push_parity_bytes = 0;
+  const unsigned int* push_epoch = nullptr;
+  int push_rows = 0, push_rank = 0, push_world = 0;
 };
 
 // Process-wide DEFAULTS of the three tuning knobs (set by gmlp_set_*). A call that
@@ -335,6 +340,12 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.asum_out[1] = ep.asum_out[1];
   args.asum_part = ep.asum_part;
   args.asum_cnt = ep.asum_cnt;
+  for (int i = 0; i < 8; ++i) args.push_base[i] = ep.push_base[i];
+  args.push_parity_bytes = ep.push_parity_bytes;
+  args.push_epoch = ep.push_epoch;
+  args.push_rows = ep.push_rows;
+  args.push_rank = ep.push_rank;
+  args.push_world = ep.push_world;
 
   constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int64_t tile_m = pair ? 2 * BM : BM;
@@ -451,6 +462,30 @@ static int check_ptrs(std::initializer_list<const void*> ps) {
 }  // namespace gmlp
 
 using namespace gmlp;
+
+// The down projection, optionally with the push of other ranks' row blocks (tensor parallel).
+static int down_fwd_impl(const gmlp_problem_t* p, const void* h, const void* w_down, const void* b_down,
+                         const void* residual, void* y, const Epilogue* push, void* stream) {
+  int rc;
+  if ((rc = check_problem(p))) return rc;
+  if ((rc = check_ptrs({h, w_down, y}))) return rc;
+  if ((b_down && !aligned16(b_down)) || (residual && !aligned16(residual)))
+    return fail(GMLP_ERR_ALIGN, "bias / residual must be 16-byte aligned");
+  const DeviceInfo* dev;
+  if ((rc = device_info(&dev))) return rc;
+  const Operand a{h, p->M, p->N, p->N, false};
+  const Operand b{w_down, p->K, p->N, p->N, false};
+  Epilogue ep;
+  if (push) ep = *push;
+  ep.out0 = y;
+  ep.in0 = residual;
+  ep.bias0 = b_down;
+  ep.ld_out = p->K;
+  ep.ld_in = p->K;
+  return launch_gemm<256, false, false, EPI_STORE>(dev, p->dtype, p->M, p->K, a, nullptr, b,
+                                                   nullptr, 0, 1, ep, p->tuning,
+                                                   static_cast<cudaStream_t>(stream));
+}
 
 extern "C" {
 
@@ -585,24 +620,39 @@ int gmlp_rms_bwd(int64_t M, int64_t K, int32_t dtype, const void* dxn, const voi
 
 int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
                   const void* b_down, const void* residual, void* y, void* stream) {
-  int rc;
-  if ((rc = check_problem(p))) return rc;
-  if ((rc = check_ptrs({h, w_down, y}))) return rc;
-  if ((b_down && !aligned16(b_down)) || (residual && !aligned16(residual)))
-    return fail(GMLP_ERR_ALIGN, "bias / residual must be 16-byte aligned");
-  const DeviceInfo* dev;
-  if ((rc = device_info(&dev))) return rc;
-  const Operand a{h, p->M, p->N, p->N, false};
-  const Operand b{w_down, p->K, p->N, p->N, false};
-  Epilogue ep;
-  ep.out0 = y;
-  ep.in0 = residual;
-  ep.bias0 = b_down;
-  ep.ld_out = p->K;
-  ep.ld_in = p->K;
-  return launch_gemm<256, false, false, EPI_STORE>(dev, p->dtype, p->M, p->K, a, nullptr, b,
-                                                   nullptr, 0, 1, ep, p->tuning,
-                                                   static_cast<cudaStream_t>(stream));
+  return down_fwd_impl(p, h, w_down, b_down, residual, y, nullptr, stream);
+}
+
+int gmlp_down_fwd_push(const gmlp_problem_t* p, const void* h, const void* w_down, const void* b_down,
+                       const void* residual, void* y, int64_t max_elems, void* const* regions, int32_t rank,
+                       int32_t world, void* stream) {
+  using namespace gmlp;
+  if (!p) return fail(GMLP_ERR_ARG, "NULL problem descriptor");
+  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "the pushing down projection takes bf16 or fp16");
+  if (world < 2 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+    return fail(GMLP_ERR_ARG, "needs 2 <= world <= %d and 0 <= rank < world; got rank %d of %d", PEER_MAX_WORLD,
+                rank, world);
+  if (!regions) return fail(GMLP_ERR_ARG, "NULL regions");
+  if (p->M <= 0 || (p->M % (32ll * world)) != 0)
+    return fail(GMLP_ERR_SHAPE, "M=%lld must be a positive multiple of 32 * world so that every 32-row block has "
+                                "one owner", static_cast<long long>(p->M));
+  if (p->M * p->K > max_elems)
+    return fail(GMLP_ERR_SHAPE, "M * K = %lld exceeds the regions' capacity of %lld elements",
+                static_cast<long long>(p->M * p->K), static_cast<long long>(max_elems));
+  Epilogue push;
+  const long long slot = peer_slot_bytes(max_elems);
+  for (int r = 0; r < world; ++r) {
+    if (!regions[r] || !aligned16(regions[r])) return fail(GMLP_ERR_ARG, "region of rank %d is NULL or misaligned", r);
+    push.push_base[r] = static_cast<char*>(regions[r]) + static_cast<long long>(rank) * slot;
+  }
+  push.push_parity_bytes = static_cast<long long>(world) * slot;
+  push.push_epoch = reinterpret_cast<const unsigned int*>(static_cast<char*>(regions[rank]) +
+                                                          peer_epoch_offset(max_elems, world));
+  push.push_rows = static_cast<int>(p->M / world);
+  push.push_rank = rank;
+  push.push_world = world;
+  return down_fwd_impl(p, h, w_down, b_down, residual, y, &push, stream);
 }
 
 int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down,
@@ -1438,9 +1488,26 @@ extern "C" long long gmlp_set_peer_two_shot_bytes(long long bytes) {
   return prev;
 }
 
+static int peer_allreduce_impl(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
+                               void* const* regions, int32_t rank, int32_t world, void* dst,
+                               int32_t dependent, bool scattered, void* stream);
+
 extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
                                    void* const* regions, int32_t rank, int32_t world, void* dst,
                                    int32_t dependent, void* stream) {
+  return peer_allreduce_impl(dtype, n, max_elems, src, regions, rank, world, dst, dependent, false, stream);
+}
+
+extern "C" int gmlp_peer_reduce_gather(int32_t dtype, int64_t n, int64_t max_elems, void* y,
+                                       void* const* regions, int32_t rank, int32_t world, void* stream) {
+  if (world > 0 && (n % (8ll * world)) != 0)
+    return fail(GMLP_ERR_SHAPE, "n=%lld must be a multiple of 8 * world", static_cast<long long>(n));
+  return peer_allreduce_impl(dtype, n, max_elems, y, regions, rank, world, y, 0, true, stream);
+}
+
+static int peer_allreduce_impl(int32_t dtype, int64_t n, int64_t max_elems, const void* src,
+                               void* const* regions, int32_t rank, int32_t world, void* dst,
+                               int32_t dependent, bool scattered, void* stream) {
   using namespace gmlp;
   if (dtype != GMLP_BF16 && dtype != GMLP_FP16)
     return fail(GMLP_ERR_DTYPE, "dtype %d is not GMLP_BF16 / GMLP_FP16", dtype);
@@ -1472,6 +1539,7 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
   a.rank = rank;
   a.world = world;
   a.dependent = dependent ? 1 : 0;
+  a.scattered = scattered ? 1 : 0;
   a.status = dev->status_ptr;
   // Kernel and grid depend on n and world alone, so that every rank makes the same
   // choice and block b means the same slice everywhere. The two-shot form (each rank
@@ -1480,7 +1548,7 @@ extern "C" int gmlp_peer_allreduce(int32_t dtype, int64_t n, int64_t max_elems, 
   // largest groups: it is taken from PEER_TWO_SHOT_MIN_BYTES on with eight ranks.
   const bool big = g_two_shot_bytes > 0 ? n * 2 >= g_two_shot_bytes
                                         : (g_two_shot_bytes == 0 && world >= 8 && n * 2 >= PEER_TWO_SHOT_MIN_BYTES);
-  const bool two_shot = big && (n % (8ll * world)) == 0;
+  const bool two_shot = scattered || (big && (n % (8ll * world)) == 0);
   const long long vecs = two_shot ? n / 8 / world : n / 8;
   long long blocks = (vecs + PEER_THREADS - 1) / PEER_THREADS;
   if (blocks > PEER_MAX_BLOCKS) blocks = PEER_MAX_BLOCKS;

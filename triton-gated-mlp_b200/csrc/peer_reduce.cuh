@@ -68,6 +68,8 @@ struct PeerReduceArgs {
   long long max_elems;           // the capacity the regions were sized for
   int rank, world;
   int dependent;  // launched as a programmatic dependent of the kernel that wrote src
+  int scattered;  // two-shot kernel only: the slices are in the owners' inboxes already (the down
+                  // projection pushed them from its epilogue), so the kernel starts at the first flag exchange
   int* status;
 };
 
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_twoshot_kernel(Pe
   uint4* dst = static_cast<uint4*>(a.dst);
 
   // scatter: slice p of this rank's partial goes to peer p (same offset in the slot)
-  for (long long v = v0; v < svecs; v += vstep) {
+  for (long long v = v0; v < svecs && !a.scattered; v += vstep) {
 #pragma unroll
     for (int p = 0; p < PEER_MAX_WORLD; ++p)
       if (p < a.world && p != a.rank)

@@ -68,7 +68,7 @@ class FusedGatedMLPFunction(Function):
                 b_up: Optional[Tensor], W_down: Tensor, b_down: Optional[Tensor],
                 drop: Dropout, shard: Shard, tp_group, act: str = "silu",
                 residual: Optional[Tensor] = None, tp_chunk_rows=(0, 0), tp_comm_sms: int = 16,
-                inplace_backward: bool = True) -> Tensor:
+                inplace_backward: bool = True, peer_sum=None) -> Tensor:
         tp_chunk_fwd, tp_chunk_bwd = tp_chunk_rows
         need_bwd = any(ctx.needs_input_grad)
         # With the intermediate dimension sharded, every rank holds a partial sum
@@ -90,6 +90,16 @@ class FusedGatedMLPFunction(Function):
                                                    out=y[r0:r1], tuning=limit.tuning),
                 tp_group, tp_chunk_fwd, limit)
             parallel.wait_all(works)
+        elif (tp_group is not None and peer_sum is not None
+              and peer_sum.supports_down_sum(x.shape[0], W_down.shape[0], x.dtype)):
+            # the down projection scatters its partial output into the owners' inboxes from its epilogue;
+            # one more kernel per rank sums and hands round (no NCCL call on this path)
+            if need_bwd:
+                h, g, u = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=True, act=act)
+            else:
+                h = kernels.hidden_fwd(x, W_gate, b_gate, W_up, b_up, drop=drop, shard=shard, save=False, act=act)
+                g = u = None
+            y = peer_sum.down_fwd_sum(h, W_down, bias, res)
         else:
             # both kernels from one library call
             y, h, g, u = kernels.mlp_fwd(x, W_gate, b_gate, W_up, b_up, W_down, bias, drop=drop, shard=shard,
@@ -176,7 +186,7 @@ class FusedGatedMLPFunction(Function):
         parallel.wait_all(works)
         d_res = dy if (len(need) > 11 and need[11]) else None  # y = ... + residual
         return (dx, dW_gate, db_gate, dW_up, db_up, dW_down, db_down, None, None, None, None, d_res, None, None,
-                None)
+                None, None)
 
 
 class _InputRMSNorm(Function):
@@ -282,6 +292,7 @@ class FusedGatedMLP(nn.Module):
         self.philox_offset = 0
         self._decode_scratch = None
         self._peer = None
+        self._peer_sum = None
         self.inplace_backward = True
         self.tp_chunk_rows = 0
         self.tp_chunk_rows_fwd = 0
@@ -407,6 +418,19 @@ class FusedGatedMLP(nn.Module):
         self._peer = parallel.PeerAllReduce(group, int(max_tokens) * self.hidden_size, w.dtype, w.device)
         return self._peer
 
+    def enable_peer_output_sum(self, max_tokens: int) -> "parallel.PeerAllReduce":
+        """Collective over the tensor-parallel group: from now on the prefill / training forward of up to
+        `max_tokens` rows (a multiple of 32 * world per call) sums its partial outputs without NCCL: the down
+        projection pushes the other ranks' row blocks into their inboxes from its epilogue while it computes,
+        and one more kernel adds and hands round (PeerAllReduce.down_fwd_sum). Each rank sets aside
+        2 * world * max_tokens * hidden_size * 2 bytes for the inboxes. The backward pass keeps NCCL for dx."""
+        if self.parallel_mode != "tp":
+            raise ValueError("enable_peer_output_sum applies to parallel_mode='tp'")
+        group = self.process_group if self.process_group is not None else parallel.default_group()
+        w = self.down_proj.weight
+        self._peer_sum = parallel.PeerAllReduce(group, int(max_tokens) * self.hidden_size, w.dtype, w.device)
+        return self._peer_sum
+
     def forward(self, x: Tensor, residual: Optional[Tensor] = None) -> Tensor:
         """y = down(dropout(act(gate(x)) * up(x))) (+ residual, fused into the down projection's epilogue;
         the reference adds a residual outside the module, after gated_mlp.py:236-237)."""
@@ -451,6 +475,6 @@ class FusedGatedMLP(nn.Module):
             x, self.gate_proj.weight, self.gate_proj.bias, self.up_proj.weight, self.up_proj.bias,
             self.down_proj.weight, self.down_proj.bias, drop, self._shard(), tp_group, self.act_fn, residual,
             (int(self.tp_chunk_rows_fwd), int(self.tp_chunk_rows)) if tp_group is not None else (0, 0),
-            int(self.tp_comm_sms), bool(self.inplace_backward),
+            int(self.tp_comm_sms), bool(self.inplace_backward), self._peer_sum if tp_group is not None else None,
         )
         return y.view(shapes) if len(shapes) > 2 else y

@@ -182,6 +182,21 @@ class _LibPeerBackend:
                 torch.cuda.current_stream(self.device).cuda_stream))
 
 
+    def down_push_sum(self, prob, h: Tensor, w_down: Tensor, b_down, residual, y: Tensor, max_elems: int, regions,
+                      rank: int, world: int) -> None:
+        """gmlp_down_fwd_push followed by gmlp_peer_reduce_gather on the current stream."""
+        C = self._C
+        ptr = lambda t: None if t is None else t.data_ptr()
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        regs = (C.c_void_p * world)(*regions)
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_down_fwd_push(
+                C.byref(prob), ptr(h), ptr(w_down), ptr(b_down), ptr(residual), ptr(y), max_elems, regs, rank, world,
+                st))
+            self._lib_mod.check(self.lib.gmlp_peer_reduce_gather(
+                self._lib_mod.dtype_code(y.dtype), y.numel(), max_elems, ptr(y), regs, rank, world, st))
+
+
 class PeerAllReduce:
     """Sum of a small tensor over the tensor-parallel group through the peers' memory.
 
@@ -250,6 +265,34 @@ class PeerAllReduce:
         self.backend.allreduce(self.dtype, partial.numel(), self.max_elems, partial, self.regions, self.rank,
                                self.world, out, dependent)
         return out
+
+    def supports_down_sum(self, M: int, K: int, dtype: torch.dtype) -> bool:
+        """Whether down_fwd_sum can take a partial output of M rows and K columns."""
+        n = M * K
+        return (not self.closed and dtype == self.dtype and M > 0 and M % (32 * self.world) == 0
+                and n <= self.max_elems and n % (8 * self.world) == 0)
+
+    def down_fwd_sum(self, h: Tensor, w_down: Tensor, b_down: Optional[Tensor] = None,
+                     residual: Optional[Tensor] = None, tuning: int = 0) -> Tensor:
+        """y = sum over ranks of (h W_down^T (+ b_down) (+ residual)) for tensor-parallel shards h [M, N / world],
+        W_down [K, N / world]: the down projection pushes the blocks of the other ranks' rows into their inboxes
+        from its own epilogue (the scatter half of a reduce-scatter, overlapped with the GEMM's remaining
+        tiles); a second kernel adds each rank's rows in rank order and hands them round. Every rank of the
+        group makes the call (same M); give bias and residual on one rank only. Replaces kernels.down_fwd +
+        all_reduce_sum."""
+        from .ops import kernels
+
+        M, K = h.shape[0], w_down.shape[0]
+        if not self.supports_down_sum(M, K, h.dtype):
+            raise ValueError(f"down_fwd_sum needs M a multiple of 32 * world, M * K <= {self.max_elems} and "
+                             f"{self.dtype} operands; got M={M}, K={K}, {h.dtype}")
+        h, w_down = h.contiguous(), w_down.contiguous()
+        y = torch.empty((M, K), dtype=h.dtype, device=h.device)
+        prob = kernels._problem(M, K, h.shape[1], h.dtype, kernels.NO_DROPOUT, kernels.NO_SHARD, tuning=tuning)
+        self.calls += 1
+        self.backend.down_push_sum(prob, h, w_down, b_down, residual, y, self.max_elems, self.regions, self.rank,
+                                   self.world)
+        return y
 
     def close(self) -> None:
         """Collective: unmap the peers' regions and free this rank's (after everyone has stopped using them)."""
