@@ -38,7 +38,7 @@
 namespace gmlp {
 
 constexpr int PEER_MAX_WORLD = 8;
-constexpr int PEER_MAX_BLOCKS = 64;
+constexpr int PEER_MAX_BLOCKS = 128;
 constexpr int PEER_THREADS = 512;
 constexpr int PEER_SLOT_ALIGN = 256;
 constexpr int GMLP_DEV_TIMEOUT_PEER = 4;
