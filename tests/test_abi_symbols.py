@@ -57,3 +57,26 @@ def test_argument_checks_run_before_any_device_call(pkg):
     assert lib.gmlp_colsum(4, 12, 0, 16, 16, 16, 1 << 20, 16, None) == -1
     assert lib.gmlp_colsum(4, 16, 0, 16, 16, 16, 0, 16, None) == -7
     assert lib.gmlp_colsum_scratch_bytes(16384, 8192) >= 8192 * 4
+
+
+def test_pushing_down_projection_checks_its_arguments_on_the_host(pkg):
+    """gmlp_down_fwd_push / gmlp_peer_reduce_gather reject what they cannot do before any device call."""
+    L = pkg._lib
+    lib = L.load()
+    ok = dict(M=256, K=64, N=64, dtype=0, dropout_p=0.0, seed=0, offset=0, row0_global=0, col0_global=0, N_global=0,
+              act=0, tuning=0)
+    regions = (ctypes.c_void_p * 2)(4096, 8192)
+
+    def rc(world=2, rank=0, max_elems=256 * 64, regs=regions, **kw):
+        p = L.Problem(**{**ok, **kw})
+        return lib.gmlp_down_fwd_push(ctypes.byref(p), 16, 16, None, None, 16, max_elems, regs, rank, world, None)
+
+    assert rc(world=1) == -6 and b"world" in lib.gmlp_last_error()
+    assert rc(rank=2) == -6
+    assert rc(dtype=2) == -3                           # float32 has no pushing epilogue
+    assert rc(M=96) == -1 and b"32 * world" in lib.gmlp_last_error()
+    assert rc(max_elems=1024) == -1 and b"capacity" in lib.gmlp_last_error()
+    assert rc(regs=None) == -6
+    assert lib.gmlp_peer_reduce_gather(0, 100, 1 << 20, 16, regions, 0, 2, None) == -1   # n not a multiple of 8 * world
+    assert lib.gmlp_peer_reduce_gather(0, 1 << 21, 1 << 20, 16, regions, 0, 2, None) == -1  # above the capacity
+
