@@ -710,7 +710,7 @@ def tp_section(pkg, dev, rank, world, dist):
                                               want["dup_proj.weight"], dt, units=int(units.numel()))
         parity["dW_down_units"] = parity_record(m.down_proj.weight.grad[:, u_dev].float().cpu(),
                                                 want["ddown_proj.weight"], dt, units=int(units.numel()))
-    want_y = want["y"] if rank == 0 else None
+    want_y, want_dx = (want["y"], want["dx"]) if rank == 0 else (None, None)
     del y, xg, want
     m.zero_grad(set_to_none=True)
 
@@ -756,10 +756,22 @@ def tp_section(pkg, dev, rank, world, dist):
         del yp
         pre["fwd_ms_pushed_sum"] = event_timed(fwd, 10, dev, dist)
         pre["fwd_pushed_sum_tflops_whole_job"] = 6.0 * M * K * N / (pre["fwd_ms_pushed_sum"] * 1e-3) / 1e12
-        pre["fwd_bwd_ms_pushed_sum_dx_chunks_of_4096_rows"] = None
-        m.tp_chunk_rows = 4096
-        pre["fwd_bwd_ms_pushed_sum_dx_chunks_of_4096_rows"] = event_timed(fwd_bwd, 5, dev, dist)
-        m.tp_chunk_rows = 0
+        # forward and backward without an NCCL call: y and dx both scattered from their GEMMs' epilogues, the
+        # dx sum kernel enqueued behind the weight-gradient GEMMs
+        pre["fwd_bwd_ms_pushed_sums"] = event_timed(fwd_bwd, 5, dev, dist)
+        pre["fwd_bwd_pushed_sums_tflops_whole_job"] = 18.0 * M * K * N / (pre["fwd_bwd_ms_pushed_sums"] * 1e-3) / 1e12
+        if rank == 0:
+            xq = x.clone().requires_grad_(True)
+            m(xq).backward(dy)
+            parity["dx_rows_pushed_sum"] = parity_record(xq.grad[rows.to(dev)].float().cpu(), want_dx, dt,
+                                                         rows=int(rows.numel()))
+            m.zero_grad(set_to_none=True)
+            del xq
+        else:
+            xq = x.clone().requires_grad_(True)
+            m(xq).backward(dy)
+            m.zero_grad(set_to_none=True)
+            del xq
         m._peer_sum.close()
         m._peer_sum = None
     except Exception as e:   # the line must still be printed

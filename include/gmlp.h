@@ -400,6 +400,13 @@ int gmlp_down_fwd_push(const gmlp_problem_t* p, const void* h, const void* w_dow
                        int32_t world, void* stream);
 int gmlp_peer_reduce_gather(int32_t dtype, int64_t n, int64_t max_elems, void* y, void* const* regions,
                             int32_t rank, int32_t world, void* stream);
+/* The same scatter from the epilogue of gmlp_bwd_dx (dx is the other tensor-parallel partial sum, over the
+ * shards of the intermediate dimension; _compute_dx in src/triton_gated_mlp/ops/bwd.py:231-322). The
+ * gmlp_peer_reduce_gather(dx) that completes it may be enqueued later on the stream, e.g. behind the
+ * weight-gradient GEMMs, as long as no other call uses the regions in between. */
+int gmlp_bwd_dx_push(const gmlp_problem_t* p, const void* d_gate, const void* d_up, const void* w_gate,
+                     const void* w_up, void* dx, int64_t max_elems, void* const* regions, int32_t rank,
+                     int32_t world, void* stream);
 
 /* Reads and clears the current device's status word (synchronises the device).
  * 0 = no kernel gave up a wait since the last read. */

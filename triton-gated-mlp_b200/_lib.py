@@ -27,7 +27,7 @@ EXPORTS = (
     "gmlp_bwd_dw_down_bias", "gmlp_colsum_scratch_bytes", "gmlp_colsum", "gmlp_colsum_static",
     "gmlp_dropout_mask", "gmlp_gemm", "gmlp_decode_scratch_bytes", "gmlp_decode_fwd", "gmlp_set_cta_pair_mode", "gmlp_set_raster_group", "gmlp_set_sm_limit",
     "gmlp_peer_region_bytes", "gmlp_set_peer_two_shot_bytes", "gmlp_peer_alloc", "gmlp_peer_open", "gmlp_peer_close", "gmlp_peer_free",
-    "gmlp_peer_allreduce", "gmlp_down_fwd_push", "gmlp_peer_reduce_gather", "gmlp_status_read", "gmlp_last_error", "gmlp_version",
+    "gmlp_peer_allreduce", "gmlp_down_fwd_push", "gmlp_bwd_dx_push", "gmlp_peer_reduce_gather", "gmlp_status_read", "gmlp_last_error", "gmlp_version",
 )
 
 
@@ -96,6 +96,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.gmlp_peer_allreduce.argtypes = [i32, i64, i64, vp, C.POINTER(vp), i32, i32, vp, i32, vp]
     lib.gmlp_down_fwd_push.argtypes = [pp, vp, vp, vp, vp, vp, i64, C.POINTER(vp), i32, i32, vp]
     lib.gmlp_peer_reduce_gather.argtypes = [i32, i64, i64, vp, C.POINTER(vp), i32, i32, vp]
+    lib.gmlp_bwd_dx_push.argtypes = [pp, vp, vp, vp, vp, vp, i64, C.POINTER(vp), i32, i32, vp]
     lib.gmlp_status_read.argtypes = [C.POINTER(C.c_int)]
     lib.gmlp_last_error.restype = C.c_char_p
     lib.gmlp_version.restype = C.c_int

@@ -463,6 +463,40 @@ static int check_ptrs(std::initializer_list<const void*> ps) {
 
 using namespace gmlp;
 
+static int bwd_dx_impl(const gmlp_problem_t* p, const void* d_gate, const void* d_up, const void* w_gate,
+                       const void* w_up, void* dx, const Epilogue* push, void* stream);
+
+// Fills the push fields of an epilogue: output [M, K], rows owned by the ranks in shares of M / world.
+static int make_push(Epilogue* ep, const gmlp_problem_t* p, int64_t max_elems, void* const* regions, int32_t rank,
+                     int32_t world) {
+  using namespace gmlp;
+  if (!p) return fail(GMLP_ERR_ARG, "NULL problem descriptor");
+  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
+    return fail(GMLP_ERR_DTYPE, "the pushing epilogue takes bf16 or fp16");
+  if (world < 2 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
+    return fail(GMLP_ERR_ARG, "needs 2 <= world <= %d and 0 <= rank < world; got rank %d of %d", PEER_MAX_WORLD,
+                rank, world);
+  if (!regions) return fail(GMLP_ERR_ARG, "NULL regions");
+  if (p->M <= 0 || (p->M % (32ll * world)) != 0)
+    return fail(GMLP_ERR_SHAPE, "M=%lld must be a positive multiple of 32 * world so that every 32-row block has "
+                                "one owner", static_cast<long long>(p->M));
+  if (p->M * p->K > max_elems)
+    return fail(GMLP_ERR_SHAPE, "M * K = %lld exceeds the regions' capacity of %lld elements",
+                static_cast<long long>(p->M * p->K), static_cast<long long>(max_elems));
+  const long long slot = peer_slot_bytes(max_elems);
+  for (int r = 0; r < world; ++r) {
+    if (!regions[r] || !aligned16(regions[r])) return fail(GMLP_ERR_ARG, "region of rank %d is NULL or misaligned", r);
+    ep->push_base[r] = static_cast<char*>(regions[r]) + static_cast<long long>(rank) * slot;
+  }
+  ep->push_parity_bytes = static_cast<long long>(world) * slot;
+  ep->push_epoch = reinterpret_cast<const unsigned int*>(static_cast<char*>(regions[rank]) +
+                                                         peer_epoch_offset(max_elems, world));
+  ep->push_rows = static_cast<int>(p->M / world);
+  ep->push_rank = rank;
+  ep->push_world = world;
+  return GMLP_OK;
+}
+
 // The down projection, optionally with the push of other ranks' row blocks (tensor parallel).
 static int down_fwd_impl(const gmlp_problem_t* p, const void* h, const void* w_down, const void* b_down,
                          const void* residual, void* y, const Epilogue* push, void* stream) {
@@ -626,32 +660,9 @@ int gmlp_down_fwd(const gmlp_problem_t* p, const void* h, const void* w_down,
 int gmlp_down_fwd_push(const gmlp_problem_t* p, const void* h, const void* w_down, const void* b_down,
                        const void* residual, void* y, int64_t max_elems, void* const* regions, int32_t rank,
                        int32_t world, void* stream) {
-  using namespace gmlp;
-  if (!p) return fail(GMLP_ERR_ARG, "NULL problem descriptor");
-  if (p->dtype != GMLP_BF16 && p->dtype != GMLP_FP16)
-    return fail(GMLP_ERR_DTYPE, "the pushing down projection takes bf16 or fp16");
-  if (world < 2 || world > PEER_MAX_WORLD || rank < 0 || rank >= world)
-    return fail(GMLP_ERR_ARG, "needs 2 <= world <= %d and 0 <= rank < world; got rank %d of %d", PEER_MAX_WORLD,
-                rank, world);
-  if (!regions) return fail(GMLP_ERR_ARG, "NULL regions");
-  if (p->M <= 0 || (p->M % (32ll * world)) != 0)
-    return fail(GMLP_ERR_SHAPE, "M=%lld must be a positive multiple of 32 * world so that every 32-row block has "
-                                "one owner", static_cast<long long>(p->M));
-  if (p->M * p->K > max_elems)
-    return fail(GMLP_ERR_SHAPE, "M * K = %lld exceeds the regions' capacity of %lld elements",
-                static_cast<long long>(p->M * p->K), static_cast<long long>(max_elems));
   Epilogue push;
-  const long long slot = peer_slot_bytes(max_elems);
-  for (int r = 0; r < world; ++r) {
-    if (!regions[r] || !aligned16(regions[r])) return fail(GMLP_ERR_ARG, "region of rank %d is NULL or misaligned", r);
-    push.push_base[r] = static_cast<char*>(regions[r]) + static_cast<long long>(rank) * slot;
-  }
-  push.push_parity_bytes = static_cast<long long>(world) * slot;
-  push.push_epoch = reinterpret_cast<const unsigned int*>(static_cast<char*>(regions[rank]) +
-                                                          peer_epoch_offset(max_elems, world));
-  push.push_rows = static_cast<int>(p->M / world);
-  push.push_rank = rank;
-  push.push_world = world;
+  int rc;
+  if ((rc = make_push(&push, p, max_elems, regions, rank, world))) return rc;
   return down_fwd_impl(p, h, w_down, b_down, residual, y, &push, stream);
 }
 
@@ -681,6 +692,22 @@ int gmlp_bwd_dhidden(const gmlp_problem_t* p, const void* dy, const void* w_down
 
 int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
                 const void* w_gate, const void* w_up, void* dx, void* stream) {
+  return bwd_dx_impl(p, d_gate, d_up, w_gate, w_up, dx, nullptr, stream);
+}
+
+int gmlp_bwd_dx_push(const gmlp_problem_t* p, const void* d_gate, const void* d_up, const void* w_gate,
+                     const void* w_up, void* dx, int64_t max_elems, void* const* regions, int32_t rank,
+                     int32_t world, void* stream) {
+  Epilogue push;
+  int rc;
+  if ((rc = make_push(&push, p, max_elems, regions, rank, world))) return rc;
+  return bwd_dx_impl(p, d_gate, d_up, w_gate, w_up, dx, &push, stream);
+}
+
+}  // extern "C"
+
+static int bwd_dx_impl(const gmlp_problem_t* p, const void* d_gate, const void* d_up, const void* w_gate,
+                       const void* w_up, void* dx, const Epilogue* push, void* stream) {
   int rc;
   if ((rc = check_problem(p))) return rc;
   if ((rc = check_ptrs({d_gate, d_up, w_gate, w_up, dx}))) return rc;
@@ -693,12 +720,15 @@ int gmlp_bwd_dx(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
   const Operand b0{w_gate, p->K, p->N, p->K, true};
   const Operand b1{w_up, p->K, p->N, p->K, true};
   Epilogue ep;
+  if (push) ep = *push;
   ep.out0 = dx;
   ep.ld_out = p->K;
   return launch_gemm<256, false, true, EPI_STORE>(dev, p->dtype, p->M, p->K, a0, &a1, b0, &b1,
                                                   p->N, 1, ep, p->tuning,
                                                   static_cast<cudaStream_t>(stream));
 }
+
+extern "C" {
 
 // Scratch of the fused bias-gradient sums for an output of `mn` rows whose GEMM has `cols`
 // output columns and `batches` problems: arrival counters (one per 128 rows and batch;

@@ -112,6 +112,7 @@ class FusedGatedMLPFunction(Function):
             ctx.tp_chunk_rows, ctx.tp_comm_sms = tp_chunk_bwd, tp_comm_sms
             ctx.has_bias = (b_gate is not None, b_up is not None, b_down is not None)
             ctx.inplace_backward, ctx.consumed = bool(inplace_backward), False
+            ctx.peer_sum = peer_sum if tp_group is not None else None
         return y
 
     @staticmethod
@@ -136,7 +137,26 @@ class FusedGatedMLPFunction(Function):
         want_bg, want_bu, want_bd = need[2] and ctx.has_bias[0], need[4] and ctx.has_bias[1], need[6] and ctx.has_bias[2]
         want_wgu = need[1] or need[3]
         works = []
-        if ctx.tp_group is not None and ctx.tp_chunk_rows > 0 and need[0]:
+        use_push = (ctx.tp_group is not None and ctx.peer_sum is not None and need[0] and dy.dtype != torch.float32
+                    and ctx.peer_sum.supports_down_sum(x.shape[0], x.shape[1], x.dtype))
+        if use_push:
+            # dx scattered into the owners' inboxes from its GEMM's epilogue; the sum kernel goes behind the
+            # weight-gradient GEMMs (no NCCL call in the pass)
+            d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act,
+                                               inplace=ctx.inplace_backward)
+            dx = ctx.peer_sum.dx_push(d_gate, d_up, W_gate, W_up)
+            if want_wgu:
+                if want_bg or want_bu:
+                    dW_gate, dW_up, db_gate, db_up = kernels.bwd_dw_gate_up(d_gate, d_up, x, bias_grads=True)
+                else:
+                    dW_gate, dW_up = kernels.bwd_dw_gate_up(d_gate, d_up, x)
+            if need[5]:
+                if want_bd:
+                    dW_down, db_down = kernels.bwd_dw_down(dy, h, bias_grad=True)
+                else:
+                    dW_down = kernels.bwd_dw_down(dy, h)
+            ctx.peer_sum.finish_sum(dx)
+        elif ctx.tp_group is not None and ctx.tp_chunk_rows > 0 and need[0]:
             # dx chunk by chunk; the last chunk's all-reduce runs beside the weight-gradient GEMMs
             limit = _SmLimit(x.device, ctx.tp_comm_sms)
             d_gate, d_up = kernels.bwd_dhidden(dy, W_down, g, u, drop=ctx.drop, shard=ctx.shard, act=ctx.act,

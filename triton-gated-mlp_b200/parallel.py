@@ -196,6 +196,22 @@ class _LibPeerBackend:
             self._lib_mod.check(self.lib.gmlp_peer_reduce_gather(
                 self._lib_mod.dtype_code(y.dtype), y.numel(), max_elems, ptr(y), regs, rank, world, st))
 
+    def dx_push(self, prob, d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, dx: Tensor, max_elems: int,
+                regions, rank: int, world: int) -> None:
+        C = self._C
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_bwd_dx_push(
+                C.byref(prob), d_gate.data_ptr(), d_up.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), dx.data_ptr(),
+                max_elems, (C.c_void_p * world)(*regions), rank, world,
+                torch.cuda.current_stream(self.device).cuda_stream))
+
+    def reduce_gather(self, t: Tensor, max_elems: int, regions, rank: int, world: int) -> None:
+        C = self._C
+        with torch.cuda.device(self.device):
+            self._lib_mod.check(self.lib.gmlp_peer_reduce_gather(
+                self._lib_mod.dtype_code(t.dtype), t.numel(), max_elems, t.data_ptr(), (C.c_void_p * world)(*regions),
+                rank, world, torch.cuda.current_stream(self.device).cuda_stream))
+
 
 class PeerAllReduce:
     """Sum of a small tensor over the tensor-parallel group through the peers' memory.
@@ -293,6 +309,29 @@ class PeerAllReduce:
         self.backend.down_push_sum(prob, h, w_down, b_down, residual, y, self.max_elems, self.regions, self.rank,
                                    self.world)
         return y
+
+    def dx_push(self, d_gate: Tensor, d_up: Tensor, w_gate: Tensor, w_up: Tensor, tuning: int = 0) -> Tensor:
+        """This rank's partial dx = d_gate W_gate + d_up W_up with the other ranks' row blocks pushed into their
+        inboxes from the GEMM's epilogue. The result is complete only after finish_sum(dx), which every rank
+        enqueues later on the same stream (behind the weight-gradient GEMMs, say) with no other call on this
+        object in between."""
+        from .ops import kernels
+
+        M, N = d_gate.shape
+        K = w_gate.shape[1]
+        if not self.supports_down_sum(M, K, d_gate.dtype):
+            raise ValueError(f"dx_push needs M a multiple of 32 * world and M * K <= {self.max_elems}; got M={M}, K={K}")
+        dx = torch.empty((M, K), dtype=d_gate.dtype, device=d_gate.device)
+        prob = kernels._problem(M, K, N, d_gate.dtype, kernels.NO_DROPOUT, kernels.NO_SHARD, tuning=tuning)
+        self.backend.dx_push(prob, d_gate.contiguous(), d_up.contiguous(), w_gate.contiguous(), w_up.contiguous(), dx,
+                             self.max_elems, self.regions, self.rank, self.world)
+        return dx
+
+    def finish_sum(self, t: Tensor) -> Tensor:
+        """Second half of dx_push: sum each rank's rows in rank order and hand them round, in place."""
+        self.calls += 1
+        self.backend.reduce_gather(t, self.max_elems, self.regions, self.rank, self.world)
+        return t
 
     def close(self) -> None:
         """Collective: unmap the peers' regions and free this rank's (after everyone has stopped using them)."""
