@@ -32,6 +32,15 @@ class _FakePeerBackend:
     def allreduce(self, dtype, n, max_elems, src, regions, rank, world, dst, dependent):
         self.launches.append((n, max_elems, src.data_ptr(), list(regions), rank, world, dst.data_ptr(), dependent))
 
+    def down_push_sum(self, prob, h, w_down, b_down, residual, y, max_elems, regions, rank, world):
+        self.launches.append(("down_push_sum", prob.M, prob.K, prob.N, y.data_ptr(), max_elems, rank, world))
+
+    def dx_push(self, prob, d_gate, d_up, w_gate, w_up, dx, max_elems, regions, rank, world):
+        self.launches.append(("dx_push", prob.M, prob.K, prob.N, dx.data_ptr(), max_elems, rank, world))
+
+    def reduce_gather(self, t, max_elems, regions, rank, world):
+        self.launches.append(("reduce_gather", t.numel(), t.data_ptr(), max_elems, rank, world))
+
     def close(self, ptr):
         self.closed.append(ptr)
 
@@ -61,6 +70,24 @@ def _peer_host_logic(P, rank):
             comm.all_reduce(bad)
     with pytest.raises(ValueError):
         comm.all_reduce(part, out=torch.zeros((4, 24), dtype=torch.bfloat16))
+    # the pushing GEMMs: rows must split into 32-row blocks per rank and fit the regions
+    bf = torch.bfloat16
+    big = P.PeerAllReduce(dist.group.WORLD, 128 * 24, bf, torch.device("cpu"), backend=_FakePeerBackend(rank))
+    assert big.supports_down_sum(128, 24, bf) and big.supports_down_sum(64, 24, bf)
+    assert not big.supports_down_sum(96, 24, bf)          # 96 rows are not a multiple of 32 * world
+    assert not big.supports_down_sum(256, 24, bf)         # above the capacity
+    assert not big.supports_down_sum(128, 24, torch.float16)
+    y = big.down_fwd_sum(torch.zeros((128, 40), dtype=bf), torch.zeros((24, 40), dtype=bf))
+    assert y.shape == (128, 24)
+    assert big.backend.launches[-1] == ("down_push_sum", 128, 24, 40, y.data_ptr(), 128 * 24, rank, WORLD)
+    dx = big.dx_push(torch.zeros((64, 40), dtype=bf), torch.zeros((64, 40), dtype=bf),
+                     torch.zeros((40, 24), dtype=bf), torch.zeros((40, 24), dtype=bf))
+    assert dx.shape == (64, 24) and big.backend.launches[-1][:4] == ("dx_push", 64, 24, 40)
+    assert big.finish_sum(dx) is dx
+    assert big.backend.launches[-1] == ("reduce_gather", 64 * 24, dx.data_ptr(), 128 * 24, rank, WORLD)
+    with pytest.raises(ValueError):
+        big.down_fwd_sum(torch.zeros((96, 40), dtype=bf), torch.zeros((24, 40), dtype=bf))
+    big.close()
     comm.close()
     assert fake.closed == [0x10000000 * (other + 1)] and fake.freed == [0x7000 + rank]
     comm.close()                                              # idempotent
