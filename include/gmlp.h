@@ -96,6 +96,10 @@ typedef struct gmlp_problem_t {
  * finished. For the call that follows a kernel which WRITES the weights (optimiser step,
  * dequantisation, weight merge). */
 #define GMLP_TUNE_ORDINARY_LAUNCH (1u << 26)
+/* Plain-store GEMMs (down projection, dx, weight gradients) may run on 256 x 512 tiles per CTA pair (one
+ * accumulator buffer, a quarter fewer operand bytes per flop) when that shortens the schedule; this bit keeps
+ * the call on 256 x 256 tiles. The result is the same bit for bit either way. */
+#define GMLP_TUNE_NARROW_TILES (1u << 27)
 
 /* H[M,N] = dropout(act(x W_gate^T + b_gate) * (x W_up^T + b_up)), act = p->act (SiLU by default).
  * Replaces mlp_hidden_states_fwd (src/triton_gated_mlp/ops/fwd.py:198-279, kernel

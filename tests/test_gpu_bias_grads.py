@@ -4,6 +4,9 @@ CTA-pair kernel, and repeated calls on one scratch buffer."""
 import pytest
 import torch
 
+from oracle import gated_mlp_oracle as orc
+from _util import build_module
+
 pytestmark = pytest.mark.gpu
 
 SHAPES = [
@@ -58,3 +61,22 @@ def test_fused_bias_gradients_are_repeatable(pkg, cuda_dev):
     a = K_.bwd_dw_gate_up(d_gate, d_up, x, bias_grads=True)
     b = K_.bwd_dw_gate_up(d_gate, d_up, x, bias_grads=True)
     assert all(torch.equal(p, q) for p, q in zip(a, b))
+
+
+def test_bias_gradients_stay_right_over_several_steps(pkg, cuda_dev):
+    """The two weight-gradient kernels of a module share one scratch buffer. With more than 4096 intermediate
+    columns the gate/up kernel's arrival counters reach past the down kernel's, so the down kernel's partial
+    sums must not start where its own counters end: every step after the first would find db_up's counters
+    dirty. Three steps on one module, all seven gradients against the oracle each time."""
+    M, K, N = 256, 256, 8192 + 512
+    case = orc.make_case(M, K, N, True, torch.bfloat16, seed=41, w_std=0.5 * K ** -0.5, dy_std=0.05)
+    want = orc.forward_backward(case)
+    m = build_module(pkg, case, torch.bfloat16, cuda_dev).train()
+    for step in range(3):
+        m.zero_grad(set_to_none=True)
+        x = case.x.to(cuda_dev).requires_grad_(True)
+        m(x).backward(case.dy.to(cuda_dev))
+        for name, q in m.named_parameters():
+            orc.assert_parity(q.grad.cpu(), want["d" + name], f"step {step} d{name}")
+    assert pkg._lib.status_read(cuda_dev) == 0
+

@@ -132,3 +132,27 @@ def test_per_call_tuning_from_two_threads(pkg, cuda_dev):
     for outs in results.values():
         assert all(torch.equal(o, want) for o in outs)
     assert (lib.gmlp_set_cta_pair_mode(-1), lib.gmlp_set_raster_group(-1), lib.gmlp_set_sm_limit(-1)) == before
+
+
+def test_wide_and_narrow_tiles_give_the_same_bits(pkg, cuda_dev):
+    """Plain-store GEMMs take 256 x 512 tiles per CTA pair when that shortens the schedule (here: the
+    down-projection weight gradient of the training shape, 128 wide tiles against 256 narrow ones on 74 pairs).
+    Every output element is the same sequence of MMAs either way, so the per-call switch must not change a bit,
+    with and without the bias sums taken on the side."""
+    K_ = pkg.ops.kernels
+    narrow = pkg._lib.tune_word(narrow_tiles=True)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    M, K, N = 4096, 2048, 8192
+    dy = (torch.randn((M, K), generator=g) * 0.05).to(torch.bfloat16).to(cuda_dev)
+    h = torch.randn((M, N), generator=g).to(torch.bfloat16).to(cuda_dev)
+    assert torch.equal(K_.bwd_dw_down(dy, h), K_.bwd_dw_down(dy, h, tuning=narrow))
+    w1, b1 = K_.bwd_dw_down(dy, h, bias_grad=True)
+    w2, b2 = K_.bwd_dw_down(dy, h, bias_grad=True, tuning=narrow)
+    assert torch.equal(w1, w2) and torch.equal(b1, b2)
+    ref = dy.float().t() @ h.float()
+    assert (w1.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    # ragged: the second half of the last wide tile lies outside the matrix
+    h2 = h[:, :8192 - 256 - 64].contiguous()
+    assert torch.equal(K_.bwd_dw_down(dy, h2), K_.bwd_dw_down(dy, h2, tuning=narrow))
+    assert pkg._lib.status_read(cuda_dev) == 0
+

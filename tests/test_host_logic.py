@@ -104,6 +104,7 @@ def test_tuning_travels_with_the_call_not_with_the_process(pkg):
     w = L.tune_word(pair_mode=2, raster_group=16, sm_limit=132)
     assert (w & 3, (w >> 2) & 0xFFF, (w >> 14) & 0xFFF) == (2, 16, 132)
     assert L.tune_word(ordinary_launch=True) == 1 << 26 and L.tune_word(sm_limit=4095) < 1 << 26
+    assert L.tune_word(narrow_tiles=True) == 1 << 27
     with pytest.raises(ValueError):
         L.tune_word(sm_limit=5000)
     from triton_gated_mlp_b200.gated_mlp import _SmLimit

@@ -180,13 +180,14 @@ def status_read(device: torch.device | None = None) -> int:
     return v.value
 
 
-def tune_word(pair_mode: int = 0, raster_group: int = 0, sm_limit: int = 0, ordinary_launch: bool = False) -> int:
+def tune_word(pair_mode: int = 0, raster_group: int = 0, sm_limit: int = 0, ordinary_launch: bool = False,
+              narrow_tiles: bool = False) -> int:
     """gmlp_problem_t.tuning for one call (the GMLP_TUNE_* fields of include/gmlp.h); 0 fields = defaults.
-    ordinary_launch: decode calls only, see GMLP_TUNE_ORDINARY_LAUNCH."""
+    ordinary_launch: decode calls only, see GMLP_TUNE_ORDINARY_LAUNCH; narrow_tiles: GMLP_TUNE_NARROW_TILES."""
     if not (0 <= pair_mode <= 2 and 0 <= raster_group <= 4095 and 0 <= sm_limit <= 4095):
         raise ValueError("pair_mode in 0..2, raster_group and sm_limit in 0..4095")
     return (pair_mode & 3) | ((raster_group & 0xFFF) << 2) | ((sm_limit & 0xFFF) << 14) | \
-        ((1 << 26) if ordinary_launch else 0)
+        ((1 << 26) if ordinary_launch else 0) | ((1 << 27) if narrow_tiles else 0)
 
 
 def set_cta_pair_mode(mode: int) -> int:

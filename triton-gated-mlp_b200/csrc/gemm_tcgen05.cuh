@@ -996,7 +996,8 @@ __device__ __forceinline__ bool asum_tile(const GemmArgs& args, const CUtensorMa
 // outcome, so the epilogue warps always wake up, read the same verdict and leave together.
 // ASUM: before that wait it takes the tile's share of the A operand's row sums (asum_tile),
 // using the staging area between the previous tile's epilogue and this tile's.
-template <typename T, int TILE_M, bool ASUM>
+// NSUB = 2 (wide tiles, see the pair kernel): one accumulator buffer instead of two.
+template <typename T, int TILE_M, bool ASUM, int NSUB = 1>
 __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtensorMap* mapA0,
                                              const CUtensorMap* mapA1, int lane, int first_tile,
                                              int tile_stride, int total_tiles, int m_tiles, int n_tiles,
@@ -1006,7 +1007,8 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtenso
   int local = 0;
   uint32_t seq = 0;
   for (int tile = first_tile; tile < total_tiles; tile += tile_stride, ++local) {
-    const int acc = local & 1;
+    const int acc = NSUB == 2 ? 0 : (local & 1);
+    const uint32_t acc_parity = NSUB == 2 ? (local & 1) : ((local >> 1) & 1);
     bool ok = true;
     if constexpr (ASUM) {
       const TileCoord tc = decode_tile(tile, m_tiles, n_tiles, args.group_m);
@@ -1016,7 +1018,7 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtenso
         ok = asum_tile<T>(args, tc.batch ? mapA1 : mapA0, tc, lane, n_tiles, mn0, m_tiles * TILE_M, epi_smem,
                           asum_bar0, seq, abortp);
     }
-    ok = mbar_wait_warp<WATCHER_SLEEP_NS>(tfull0 + 8u * acc, (local >> 1) & 1, abortp, lane) && ok;
+    ok = mbar_wait_warp<WATCHER_SLEEP_NS>(tfull0 + 8u * acc, acc_parity, abortp, lane) && ok;
     tc_fence_after_sync();
     if (lane == 0) {
       epi_go[acc] = ok ? 1 : 0;
@@ -1037,13 +1039,15 @@ __device__ __forceinline__ void watcher_role(const GemmArgs& args, const CUtenso
 //   tempty0    shared::cta address of tempty[0] ([1] is 8 bytes on)
 //   REMOTE     tempty lives in the pair's leader CTA: arrive through the cluster
 //   epi_smem   this CTA's epilogue staging area
-template <int BN, int EPI, typename T, int TILE_M, bool REMOTE, bool ASUM>
+//   NSUB       accumulator sub-tiles of BN columns per tile (2 = wide tiles, one accumulator buffer)
+template <int BN, int EPI, typename T, int TILE_M, bool REMOTE, bool ASUM, int NSUB = 1>
 __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMaps& maps, int warp,
                                               int lane, int first_tile, int tile_stride,
                                               int total_tiles, int m_tiles, int n_tiles, int row_off,
                                               uint32_t tmem_base, uint32_t tempty0, uint32_t epi_smem,
                                               volatile int* epi_go) {
-  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  static_assert(NSUB == 1 || EPI == EPI_STORE, "wide tiles are for the plain store");
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : NSUB * BN;
   const int ew = warp - 2;       // epilogue warp index 0..15
   const int quarter = warp & 3;  // TMEM lanes this warp may read
   const int col_part = ew >> 2;
@@ -1078,19 +1082,23 @@ __device__ __forceinline__ void epilogue_role(const GemmArgs& args, const OutMap
       next_row0 = nx.m_tile * TILE_M + row_off + quarter * 32;
       next_n0 = nx.n_tile * TILE_N;
     }
-    const int acc = local & 1;
+    const int acc = NSUB == 2 ? 0 : (local & 1);
     __syncwarp();
     named_bar_sync(EPI_BAR_ID0 + acc, EPI_BAR_THREADS);  // asleep until the watcher arrives
     if (epi_go[acc] == 0) break;                         // the same verdict for all sixteen warps
     tc_fence_after_sync();
-    const uint32_t taddr = tmem_base + acc * BN + lane_addr;
+    const uint32_t taddr = tmem_base + (NSUB == 2 ? 0 : acc * BN) + lane_addr;
     const int row0 = tc.m_tile * TILE_M + row_off + quarter * 32;
-    if (EPI != EPI_STORE && args.act == ACT_SILU)
+    if (EPI != EPI_STORE && args.act == ACT_SILU) {
       epilogue_tile<BN, EPI, T, ACT_SILU>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
                                           stage, bias0, bias1, drop_on, next_row0, next_n0);
-    else
-      epilogue_tile<BN, EPI, T, -1>(args, maps, taddr, row0, lane, tc.batch, tc.n_tile * TILE_N, col_part, bv,
-                                    stage, bias0, bias1, drop_on, next_row0, next_n0);
+    } else {
+#pragma unroll
+      for (int sub = 0; sub < NSUB; ++sub)  // a wide tile leaves as NSUB tiles of BN columns
+        epilogue_tile<BN, EPI, T, -1>(args, maps, taddr + sub * BN, row0, lane, tc.batch,
+                                      tc.n_tile * TILE_N + sub * BN, col_part, bv, stage, bias0, bias1, drop_on,
+                                      next_row0, next_n0);
+    }
     // Every tcgen05.ld of this tile was followed by tcgen05.wait::ld, so the data is in
     // registers: hand the TMEM buffer back to the MMA issuer. The arrive has release
     // semantics; no fence is placed here on purpose, since a fence would also wait for
@@ -1324,7 +1332,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA0,
 //   empty[s], tfull[a]   exist in both CTAs; the leader's MMA thread commits to
 //              both copies at once.
 //   tempty[a]  lives in the leader, 32 arrivals: the 16 epilogue warps of each CTA.
-template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES, bool ASUM>
+//
+// NSUB = 2, "wide tiles" (plain store only): the pair computes a 256 x 512 tile with two N = 256 MMAs per
+// reduction step that share A, so 96 KB of operands cross from L2 per 256 x 512 x 64 block instead of 128 KB
+// (the GEMMs are bound by that stream). The accumulator then fills all 512 TMEM columns: there is one buffer,
+// the epilogue of a tile does not overlap the next tile's main loop, and the ring has 3 stages of 48 KB. Pays
+// where the reduction is long (the epilogue is a few percent of a tile).
+template <int BN, bool A_MN, bool B_MN, int EPI, typename T, int STAGES, bool ASUM, int NSUB = 1>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
                          const __grid_constant__ CUtensorMap tmA1,
@@ -1342,9 +1356,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
   constexpr int HALF_N = BN / 2;  // B columns staged by each CTA
   constexpr uint32_t A_BYTES = BM * 128;
   constexpr uint32_t B_BYTES = HALF_N * 128;
-  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = tmem_cols_for(BN);
-  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  static_assert(NSUB == 1 || (NSUB == 2 && BN == 256 && EPI == EPI_STORE), "wide tiles: 2 x 256 columns");
+  constexpr uint32_t STAGE_BYTES = A_BYTES + NSUB * B_BYTES;
+  constexpr uint32_t TMEM_COLS = NSUB == 2 ? 512 : tmem_cols_for(BN);
+  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : NSUB * BN;
   constexpr int PAIR_M = 2 * BM;
   constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, B_LBO = B_MN ? BK * 128 : 16;
   constexpr uint32_t A_KSTEP = (A_MN ? 2048 : 32) >> 4, B_KSTEP = (B_MN ? 2048 : 32) >> 4;
@@ -1435,11 +1450,15 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
             tma_load_2d_pair(sb, rank == 0 ? &tmB0 : &tmB1, fb, k0, n0);
           } else if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < HALF_N / 64; ++j)
-              tma_load_2d_pair(sb + j * (BK * 128), mb, fb,
-                               n0 + static_cast<int>(rank) * HALF_N + 64 * j, k0);
+            for (int sub = 0; sub < NSUB; ++sub)
+#pragma unroll
+              for (int j = 0; j < HALF_N / 64; ++j)
+                tma_load_2d_pair(sb + sub * B_BYTES + j * (BK * 128), mb, fb,
+                                 n0 + sub * BN + static_cast<int>(rank) * HALF_N + 64 * j, k0);
           } else {
-            tma_load_2d_pair(sb, mb, fb, k0, n0 + static_cast<int>(rank) * HALF_N);
+#pragma unroll
+            for (int sub = 0; sub < NSUB; ++sub)
+              tma_load_2d_pair(sb + sub * B_BYTES, mb, fb, k0, n0 + sub * BN + static_cast<int>(rank) * HALF_N);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -1460,14 +1479,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       int local = 0;
       bool ok = true;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++local) {
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
+        const int acc = NSUB == 2 ? 0 : (local & 1);
+        const uint32_t acc_phase = NSUB == 2 ? (local & 1) : ((local >> 1) & 1);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abortp)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + (NSUB == 2 ? 0 : acc * BN);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abortp)) {
             ok = false;
@@ -1476,16 +1495,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
           tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
-          const uint64_t bdesc = make_smem_desc(sa + A_BYTES, B_LBO, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            if (sizeof(T) == 4)
-              umma_tf32_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
-                             bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              umma_f16_pair(d_tmem, adesc + static_cast<uint64_t>(k * A_KSTEP),
-                            bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
-                            (kb | k) != 0 ? 1u : 0u);
+          for (int sub = 0; sub < NSUB; ++sub) {
+            const uint64_t bdesc = make_smem_desc(sa + A_BYTES + sub * B_BYTES, B_LBO, 1024);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              if (sizeof(T) == 4)
+                umma_tf32_pair(d_tmem + sub * BN, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                               bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc, (kb | k) != 0 ? 1u : 0u);
+              else
+                umma_f16_pair(d_tmem + sub * BN, adesc + static_cast<uint64_t>(k * A_KSTEP),
+                              bdesc + static_cast<uint64_t>(k * B_KSTEP), args.idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit_pair(empty_bar(stage));
           if (++stage == STAGES) {
@@ -1501,13 +1523,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA0,
       }
     }
   } else if (warp == WATCHER_WARP) {
-    watcher_role<T, PAIR_M, ASUM>(args, &tmA0, &tmA1, lane, pair, num_pairs, total_tiles, m_tiles, n_tiles,
+    watcher_role<T, PAIR_M, ASUM, NSUB>(args, &tmA0, &tmA1, lane, pair, num_pairs, total_tiles, m_tiles, n_tiles,
                                   static_cast<int>(rank) * BM, tfull_bar(0), bar_base + 8u * (2 * STAGES + 4),
                                   smem_base + STAGES * STAGE_BYTES, epi_go, &abort_flag);
   } else {
     // ------------------------------------------------------------ epilogue --
     const OutMaps maps{&tmO0, &tmO1, &tmO2};
-    epilogue_role<BN, EPI, T, PAIR_M, true, ASUM>(args, maps, warp, lane, pair, num_pairs, total_tiles, m_tiles,
+    epilogue_role<BN, EPI, T, PAIR_M, true, ASUM, NSUB>(args, maps, warp, lane, pair, num_pairs, total_tiles, m_tiles,
                                             n_tiles, static_cast<int>(rank) * BM, tmem_base, tempty_bar(0),
                                             smem_base + STAGES * STAGE_BYTES, epi_go);
   }

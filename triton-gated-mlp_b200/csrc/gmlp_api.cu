@@ -228,6 +228,7 @@ static std::atomic<int> g_sm_limit{0};
 
 struct Tuning {
   int pair_mode, group_m, sm_limit;
+  bool narrow_tiles;
 };
 // Field layout of the per-call word: see GMLP_TUNE_* in gmlp.h.
 static Tuning resolve_tuning(uint32_t word) {
@@ -235,6 +236,7 @@ static Tuning resolve_tuning(uint32_t word) {
   t.pair_mode = static_cast<int>(word & 3u);
   t.group_m = static_cast<int>((word >> 2) & 0xFFFu);
   t.sm_limit = static_cast<int>((word >> 14) & 0xFFFu);
+  t.narrow_tiles = (word & (1u << 27)) != 0;  // GMLP_TUNE_NARROW_TILES
   if (t.pair_mode == 0 || t.pair_mode == 3) t.pair_mode = g_pair_mode.load(std::memory_order_relaxed);
   if (t.group_m == 0) t.group_m = g_group_m.load(std::memory_order_relaxed);
   if (t.sm_limit == 0) t.sm_limit = g_sm_limit.load(std::memory_order_relaxed);
@@ -347,7 +349,22 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   args.push_rank = ep.push_rank;
   args.push_world = ep.push_world;
 
-  constexpr int TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  // Wide tiles (256 x 512 per CTA pair, one accumulator buffer): a quarter fewer operand bytes per flop, no overlap
+  // of a tile's epilogue with the next main loop. For plain-store GEMMs whose reduction is long.
+  constexpr bool WIDE_OK = EPI == EPI_STORE && sizeof(T) == 2 && BN == 256;
+  bool wide = false;
+#ifndef GMLP_NO_WIDE
+  if (WIDE_OK && pair && !tune.narrow_tiles && (args.kb0 + args.kb1) >= 32 && N >= 2 * BN) {
+    // Taken when it shortens the schedule: a wide tile costs about 1.76 narrow ones (a quarter fewer operand
+    // bytes, no overlap of its epilogue), and the tiles run in waves of one per CTA pair.
+    const int64_t pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;
+    const int64_t mt = (M + 2 * BM - 1) / (2 * BM);
+    const int64_t narrow_tiles = mt * ((N + BN - 1) / BN) * batches, wide_tiles = mt * ((N + 2 * BN - 1) / (2 * BN)) * batches;
+    const int64_t narrow_waves = (narrow_tiles + pairs - 1) / pairs, wide_waves = (wide_tiles + pairs - 1) / pairs;
+    wide = pairs > 0 && 176 * wide_waves < 98 * narrow_waves;
+  }
+#endif
+  const int64_t TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : (wide ? 2 * BN : BN);
   const int64_t tile_m = pair ? 2 * BM : BM;
   const int64_t m_tiles = (M + tile_m - 1) / tile_m;
   const int64_t n_tiles = (N + TILE_N - 1) / TILE_N;
@@ -362,7 +379,20 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // fewer bytes.
   args.group_m = tune.group_m > 0 ? tune.group_m : (pair ? (EPI == EPI_SWIGLU ? 16 : 8) : 32);
   cudaError_t e;
-  if (pair) {
+  if (pair && wide) {
+    if constexpr (WIDE_OK) {
+      const int64_t max_pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;
+      const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+      constexpr int WIDE_STAGES = gemm_stages<2 * B_ROWS_PAIR, EPI>();
+      static_assert(WIDE_STAGES >= 3, "operand ring too shallow");
+      constexpr size_t smem = gemm_smem_bytes<2 * B_ROWS_PAIR, EPI, WIDE_STAGES>();
+      static_assert(smem + 512 <= SMEM_LIMIT, "wide pair kernel exceeds the shared memory of an SM");
+      auto kfn = gemm_tcgen05_pair_kernel<BN, A_MN, B_MN, EPI, T, WIDE_STAGES, ASUM, 2>;
+      static std::atomic<uint64_t> attr_done{0};
+      if ((rc = ensure_smem_attr(kfn, smem, attr_done))) return rc;
+      kfn<<<grid, GEMM_THREADS, smem, stream>>>(mA0, mA1, mB0, mB1, mO0, mO1, mO2, args);
+    }
+  } else if (pair) {
     const int64_t max_pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
     constexpr size_t smem = gemm_smem_bytes<B_ROWS_PAIR, EPI, PAIR_STAGES>();
@@ -744,6 +774,14 @@ static AsumLayout asum_layout(int64_t mn, int64_t cols, int batches) {
   return l;
 }
 
+// The two weight-gradient kernels of a module share one scratch buffer, one after the other: their arrival
+// counters (which each kernel leaves at zero) sit in a common region at the front, sized for the larger of
+// the two, and the fp32 partial sums (scratch proper) behind it, so that neither kernel's partial sums can
+// ever land on the other's counters.
+static size_t asum_common_cnt_bytes(const gmlp_problem_t* p) {
+  return std::max(asum_layout(p->N, p->K, 2).cnt_bytes, asum_layout(p->K, p->N, 1).cnt_bytes);
+}
+
 static int dw_gate_up_impl(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
                            const void* x, void* dw_gate, void* dw_up, void* db_gate, void* db_up,
                            void* scratch, size_t scratch_bytes, void* stream) {
@@ -769,13 +807,14 @@ static int dw_gate_up_impl(const gmlp_problem_t* p, const void* d_gate, const vo
   if ((db_gate && !aligned16(db_gate)) || (db_up && !aligned16(db_up)))
     return fail(GMLP_ERR_ALIGN, "bias gradient buffers must be 16-byte aligned");
   const AsumLayout l = asum_layout(p->N, p->K, 2);
-  if (!scratch || !aligned16(scratch) || scratch_bytes < l.cnt_bytes + l.part_bytes)
+  const size_t cnt_bytes = asum_common_cnt_bytes(p);
+  if (!scratch || !aligned16(scratch) || scratch_bytes < cnt_bytes + l.part_bytes)
     return fail(GMLP_ERR_SCRATCH, "bias-gradient scratch holds %zu bytes, %zu needed", scratch_bytes,
-                l.cnt_bytes + l.part_bytes);
+                cnt_bytes + l.part_bytes);
   ep.asum_out[0] = db_gate;
   ep.asum_out[1] = db_up;
   ep.asum_cnt = static_cast<int*>(scratch);
-  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + l.cnt_bytes);
+  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + cnt_bytes);
   return launch_gemm<256, true, true, EPI_STORE, true>(dev, p->dtype, p->N, p->K, a0, &a1, b, nullptr,
                                                        0, 2, ep, p->tuning, st);
 }
@@ -799,12 +838,13 @@ static int dw_down_impl(const gmlp_problem_t* p, const void* dy, const void* h, 
                                                    0, 1, ep, p->tuning, st);
   if (!aligned16(db_down)) return fail(GMLP_ERR_ALIGN, "bias gradient buffer must be 16-byte aligned");
   const AsumLayout l = asum_layout(p->K, p->N, 1);
-  if (!scratch || !aligned16(scratch) || scratch_bytes < l.cnt_bytes + l.part_bytes)
+  const size_t cnt_bytes = asum_common_cnt_bytes(p);
+  if (!scratch || !aligned16(scratch) || scratch_bytes < cnt_bytes + l.part_bytes)
     return fail(GMLP_ERR_SCRATCH, "bias-gradient scratch holds %zu bytes, %zu needed", scratch_bytes,
-                l.cnt_bytes + l.part_bytes);
+                cnt_bytes + l.part_bytes);
   ep.asum_out[0] = db_down;
   ep.asum_cnt = static_cast<int*>(scratch);
-  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + l.cnt_bytes);
+  ep.asum_part = reinterpret_cast<float*>(static_cast<char*>(scratch) + cnt_bytes);
   return launch_gemm<256, true, true, EPI_STORE, true>(dev, p->dtype, p->K, p->N, a, nullptr, b,
                                                        nullptr, 0, 1, ep, p->tuning, st);
 }
@@ -822,7 +862,7 @@ int gmlp_bwd_dw_down(const gmlp_problem_t* p, const void* dy, const void* h, voi
 size_t gmlp_bias_grad_scratch_bytes(const gmlp_problem_t* p) {
   if (!p || p->K <= 0 || p->N <= 0) return 0;
   const AsumLayout a = asum_layout(p->N, p->K, 2), b = asum_layout(p->K, p->N, 1);
-  return std::max(a.cnt_bytes + a.part_bytes, b.cnt_bytes + b.part_bytes);
+  return asum_common_cnt_bytes(p) + std::max(a.part_bytes, b.part_bytes);
 }
 
 int gmlp_bwd_dw_gate_up_bias(const gmlp_problem_t* p, const void* d_gate, const void* d_up,
