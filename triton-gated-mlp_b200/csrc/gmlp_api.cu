@@ -353,7 +353,6 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // of a tile's epilogue with the next main loop. For plain-store GEMMs whose reduction is long.
   constexpr bool WIDE_OK = EPI == EPI_STORE && sizeof(T) == 2 && BN == 256;
   bool wide = false;
-#ifndef GMLP_NO_WIDE
   if (WIDE_OK && pair && !tune.narrow_tiles && (args.kb0 + args.kb1) >= 32 && N >= 2 * BN) {
     // Taken when it shortens the schedule: a wide tile costs about 1.76 narrow ones (a quarter fewer operand
     // bytes, no overlap of its epilogue), and the tiles run in waves of one per CTA pair.
@@ -363,7 +362,6 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
     const int64_t narrow_waves = (narrow_tiles + pairs - 1) / pairs, wide_waves = (wide_tiles + pairs - 1) / pairs;
     wide = pairs > 0 && 176 * wide_waves < 98 * narrow_waves;
   }
-#endif
   const int64_t TILE_N = (EPI == EPI_SWIGLU) ? BN / 2 : (wide ? 2 * BN : BN);
   const int64_t tile_m = pair ? 2 * BM : BM;
   const int64_t m_tiles = (M + tile_m - 1) / tile_m;
