@@ -137,7 +137,9 @@ class FusedGatedMLPFunction(Function):
         want_bg, want_bu, want_bd = need[2] and ctx.has_bias[0], need[4] and ctx.has_bias[1], need[6] and ctx.has_bias[2]
         want_wgu = need[1] or need[3]
         works = []
+        # (an explicit tp_chunk_rows keeps the chunked NCCL overlap, which is the faster of the two at eight ranks)
         use_push = (ctx.tp_group is not None and ctx.peer_sum is not None and need[0] and dy.dtype != torch.float32
+                    and ctx.tp_chunk_rows == 0
                     and ctx.peer_sum.supports_down_sum(x.shape[0], x.shape[1], x.dtype))
         if use_push:
             # dx scattered into the owners' inboxes from its GEMM's epilogue; the sum kernel goes behind the
