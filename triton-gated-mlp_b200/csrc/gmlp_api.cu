@@ -353,7 +353,9 @@ static int launch_gemm_t(const DeviceInfo* dev, int dtype, int64_t M, int64_t N,
   // of a tile's epilogue with the next main loop. For plain-store GEMMs whose reduction is long.
   constexpr bool WIDE_OK = EPI == EPI_STORE && sizeof(T) == 2 && BN == 256;
   bool wide = false;
-  if (WIDE_OK && pair && !tune.narrow_tiles && (args.kb0 + args.kb1) >= 32 && N >= 2 * BN) {
+  // (not for the pushing epilogue: its peer stores take longer than a TMA store and want the next tile's main
+  // loop to hide behind)
+  if (WIDE_OK && pair && !tune.narrow_tiles && ep.push_world == 0 && (args.kb0 + args.kb1) >= 32 && N >= 2 * BN) {
     // Taken when it shortens the schedule: a wide tile costs about 1.76 narrow ones (a quarter fewer operand
     // bytes, no overlap of its epilogue), and the tiles run in waves of one per CTA pair.
     const int64_t pairs = gemm_cta_budget(dev->sm_count, tune.sm_limit) / 2;
